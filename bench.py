@@ -1,0 +1,360 @@
+#!/usr/bin/env python
+"""Benchmark of the block-sparse attention hot path: fwd+bwd Mtokens/s at L=4096.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+Workload (default ``sweep_L4096_bs64_d05``): one attention layer, forward + backward, of the
+isolated-kernel sweep shape B=8, H=8, L=4096, d_head=64, bf16, block 64, mask = diagonal band of
+2 blocks + uniformly random blocks to 5 % density; Q, K, V, dO ~ N(0,1) from a seed.  A step is
+one fwd+bwd over that batch; tokens per step = B*L per rank.  With N > 1 (torchrun, one rank per
+GPU) every rank runs its own shard of the batch*head work with no data-path collective (weak
+scaling); time = max over ranks.
+
+One JSON line on stdout (rank 0).  ``value``: inputs resident in HBM, C ABI called directly.
+``e2e``: same metric through the public module with pinned host buffers, host<->device copies
+inside the timed region.  ``roofline``: the dominant kernel, timed live with CUDA events on the
+launch stream (``spion_profile``).  ``cpu_baseline``: the oracle's dense-masked PyTorch path on
+the host cores, on a bounded sample (N=1 only).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (B, H, L, d, bs, density, dtype)
+    "sweep_L4096_bs64_d05": (8, 8, 4096, 64, 64, 0.05, "bf16"),
+    "sweep_L4096_bs32_d05": (8, 8, 4096, 64, 32, 0.05, "bf16"),
+    "sweep_L4096_bs64_d10": (8, 8, 4096, 64, 64, 0.10, "bf16"),
+    "sweep_L4096_bs64_d30": (8, 8, 4096, 64, 64, 0.30, "bf16"),
+    "sweep_L1024_bs64_d10": (8, 8, 1024, 64, 64, 0.10, "bf16"),
+    "sweep_L16384_bs64_d02": (8, 8, 16384, 64, 64, 0.02, "bf16"),
+    "config1_L1024_fp32": (8, 2, 1024, 32, 32, 0.15, "fp32"),
+    "tiny": (2, 2, 512, 64, 64, 0.25, "bf16"),
+}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons sampled while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.idx = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.idx), f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for ln in self.proc.stdout:
+            self.lines.append(ln.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            pass
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def algorithmic(B, H, L, d, bs, nnzb, esz):
+    """Algorithmic work of one fwd+bwd step (per rank)."""
+    BH = B * H
+    nnz = nnzb * bs * bs
+    flops = 12.0 * nnz * d * BH                                     # 2 SDDMM + 4 SpMM, 2*nnz*d each
+    fused_bytes = 12.0 * L * d * esz * BH                            # Q,K,V,O fwd; Q,K,V,O,dO in, dQ,dK,dV out bwd
+    return flops, fused_bytes, nnz
+
+
+# per-launch algorithmic bytes of each stage (p = bytes of a stored P/dS element, 4 for fp32 scratch)
+def stage_bytes(stage, BH, L, d, nnz, esz, psz):
+    ld = BH * L * d * esz
+    v = BH * nnz
+    return {
+        "sddmm_s": 2 * ld + 4 * v, "softmax_fwd": 4 * v + psz * v, "spmm_o": psz * v + 2 * ld,
+        "sddmm_dp": 2 * ld + 4 * v, "softmax_bwd": 4 * v + psz * v + psz * v, "spmm_dq": psz * v + 2 * ld,
+        "spmm_dk": psz * v + 2 * ld, "spmm_dv": psz * v + 2 * ld,
+        "fused_s_p": 2 * ld + psz * v, "fused_dp_ds": 2 * ld + 2 * psz * v + 4 * BH * L,
+        "delta": 2 * ld + 4 * BH * L, "spmm_dkdv": 2 * psz * v + 4 * ld, "structure": 0,
+    }[stage]
+
+
+def stage_flops(stage, BH, d, nnz):
+    if stage in ("sddmm_s", "spmm_o", "sddmm_dp", "spmm_dq", "spmm_dk", "spmm_dv", "fused_s_p", "fused_dp_ds"):
+        return 2.0 * nnz * d * BH
+    if stage == "spmm_dkdv":
+        return 4.0 * nnz * d * BH
+    return 0.0
+
+
+def run_reference(args, rank):
+    """--impl reference: the oracle's dense-masked PyTorch path on the host cores (the reference has
+    no CPU implementation of the sparse kernels; this restates models/block_attn.cu:453-545)."""
+    if rank != 0:
+        return
+    from oracle import attention as oatt
+    from spion_b200 import synthetic
+    B, H, L, d, bs, dens, dt = WORKLOADS[args.workload]
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    Bs = 1                                                   # bounded sample: one batch element (H heads)
+    mat = synthetic.band_random_mask(2024, L // bs, dens)
+    M = oatt.expand_mask(mat, bs)
+    Q, K, V, dO = synthetic.qkv(99, Bs, H, L, d)
+    for _ in range(max(1, min(args.warmup, 1))):
+        oatt.fwd_bwd_step(Q, K, V, dO, M)
+    steps = max(1, min(args.steps, 3))
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        oatt.fwd_bwd_step(Q, K, V, dO, M)
+    dt_s = (time.perf_counter() - t0) / steps
+    val = Bs * L / dt_s / 1e6
+    sample = f"B={Bs} of {B} batch elements (H={H}, L={L}, d={d}), fp32, {steps} timed steps"
+    print(json.dumps({
+        "impl": "reference", "metric": "sparse-attn fwd+bwd Mtokens/s at L=%d" % L, "value": val, "unit": "Mtokens/s",
+        "n_gpus": args.gpus, "steps": steps, "warmup": 1, "ms_per_step": dt_s * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": args.workload, "B": Bs, "H": H, "L": L, "d_head": d, "block": bs, "density": dens},
+        "cpu_baseline": {"value": val, "unit": "Mtokens/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "Mtokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="sweep_L4096_bs64_d05", choices=sorted(WORKLOADS))
+    ap.add_argument("--engine", default="auto", choices=["auto", "simt", "tcgen05"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+
+    from spion_b200 import _lib, dp, synthetic
+    from spion_b200._lib import check, lib, ptr
+    from spion_b200.native import BlockSparseAttention
+    import torch.distributed as dist
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: spion_b200 has no CPU path")
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dp.init_from_env("nccl")
+    dev = torch.device("cuda", local_rank)
+
+    B, H, L, d, bs, dens, dt = WORKLOADS[args.workload]
+    tdt = torch.bfloat16 if dt == "bf16" else torch.float32
+    esz = 2 if dt == "bf16" else 4
+    BH, nb = B * H, L // bs
+    cfg = {"head_dim": d, "num_head": H, "max_seq_len": L, "batch_size": B, "block_size": bs,
+           "transformer_dim": H * d, "task": "sweep"}
+    engine = {"auto": _lib.ENGINE_AUTO, "simt": _lib.ENGINE_SIMT, "tcgen05": _lib.ENGINE_TCGEN05}[args.engine]
+    mod = BlockSparseAttention(cfg, dtype=tdt, engine=engine, device=dev)
+    mat = synthetic.band_random_mask(2024, nb, dens)          # same mask on every rank (one layer)
+    nnzb = mod.set_mask(torch.as_tensor(mat).to(dev))
+    flops, fused_bytes, nnz = algorithmic(B, H, L, d, bs, nnzb, esz)
+
+    # rank-specific shard of the batch*head work
+    hQ, hK, hV, hdO = [t.to(tdt).pin_memory() for t in synthetic.qkv(99 + rank, B, H, L, d)]
+    Q, K, V, dO = [t.to(dev) for t in (hQ, hK, hV, hdO)]
+    n = BH * nnz
+    P = torch.empty(n, dtype=tdt, device=dev); dS = torch.empty(n, dtype=tdt, device=dev)
+    O = torch.empty_like(Q); dQ = torch.empty_like(Q); dK = torch.empty_like(Q); dV = torch.empty_like(Q)
+    scr = torch.empty(n, dtype=torch.float32, device=dev)
+    delta = torch.empty(BH * L, dtype=torch.float32, device=dev)
+    check(lib.spion_set_stream(mod.handle, _lib.current_stream_ptr()))
+
+    def step_device():
+        check(lib.spion_attn_forward_ex(mod.handle, ptr(Q), ptr(K), ptr(V), None, ptr(P), ptr(O), ptr(scr)))
+        check(lib.spion_attn_backward_ex(mod.handle, ptr(Q), ptr(K), ptr(V), ptr(P), ptr(O), ptr(dO), ptr(dS),
+                                         ptr(scr), ptr(delta), ptr(dQ), ptr(dK), ptr(dV)))
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms):
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---------------- value: inputs resident in HBM, C ABI -------------------------------------
+    for _ in range(args.warmup):
+        step_device()
+    mod.check_device_status()
+    sampler = ClockSampler(local_rank)
+    barrier()
+    if rank == 0:
+        sampler.start()
+    l0 = mod.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step_device()
+    e1.record()
+    barrier()
+    launches = mod.launch_count() - l0
+    ms_total = max_over_ranks(e0.elapsed_time(e1))
+    clocks = sampler.stop() if rank == 0 else None
+    ms_step = ms_total / args.steps
+    value = world * B * L / (ms_step * 1e-3) / 1e6
+
+    # ---------------- per-kernel times, live, CUDA events on the launch stream -----------------
+    check(lib.spion_profile_reset(mod.handle)); check(lib.spion_profile(mod.handle, 1))
+    for _ in range(args.steps):
+        step_device()
+    stages = {}
+    for s in range(_lib.STAGE_COUNT):
+        tot = _lib.ctypes.c_double(0); cnt = _lib.ctypes.c_longlong(0)
+        check(lib.spion_profile_get(mod.handle, s, _lib.ctypes.byref(tot), _lib.ctypes.byref(cnt)))
+        if cnt.value:
+            stages[lib.spion_stage_name(s).decode()] = tot.value / cnt.value
+    check(lib.spion_profile(mod.handle, 0))
+    peaks = load_peaks()
+    psz = esz
+    kern = {}
+    for name, ms in stages.items():
+        by = stage_bytes(name, BH, L, d, nnz, esz, psz)
+        fl = stage_flops(name, BH, d, nnz)
+        kern[name] = {"ms": ms, "GBps": by / (ms * 1e-3) / 1e9 if ms > 0 else None,
+                      "TFLOPs": fl / (ms * 1e-3) / 1e12 if ms > 0 else None}
+    dom = max((k for k in stages if k != "structure"), key=lambda k: stages[k])
+    dom_bytes = stage_bytes(dom, BH, L, d, nnz, esz, psz)
+    achieved = dom_bytes / (stages[dom] * 1e-3) / 1e9
+    roofline = {"kernel": dom, "bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
+                "algorithmic_bytes_per_launch": dom_bytes, "ms_per_launch": stages[dom]}
+    step_bound_ms = max(flops / (peaks["bf16_tflops"] * 1e12), fused_bytes / (peaks["hbm_gbs"] * 1e9)) * 1e3
+
+    # ---------------- e2e: public module, pinned host buffers, copies inside the timed region ---
+    hO = torch.empty_like(hQ).pin_memory(); hdQ = torch.empty_like(hQ).pin_memory()
+    hdK = torch.empty_like(hQ).pin_memory(); hdV = torch.empty_like(hQ).pin_memory()
+
+    def step_e2e():
+        q = hQ.to(dev, non_blocking=True).requires_grad_(True)
+        k = hK.to(dev, non_blocking=True).requires_grad_(True)
+        v = hV.to(dev, non_blocking=True).requires_grad_(True)
+        g = hdO.to(dev, non_blocking=True)
+        out, _ = mod(q, k, v)
+        out.backward(g)
+        hO.copy_(out.detach(), non_blocking=True); hdQ.copy_(q.grad, non_blocking=True)
+        hdK.copy_(k.grad, non_blocking=True); hdV.copy_(v.grad, non_blocking=True)
+
+    for _ in range(3):
+        step_e2e()
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        step_e2e()
+    e1.record()
+    barrier()
+    e2e_ms = max_over_ranks(e0.elapsed_time(e1)) / args.steps
+    h2d = 4 * hQ.numel() * esz
+    d2h = 4 * hQ.numel() * esz
+    e2e = {"value": world * B * L / (e2e_ms * 1e-3) / 1e6, "unit": "Mtokens/s", "ms_per_step": e2e_ms,
+           "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
+    mod.check_device_status()
+
+    # ---------------- CPU baseline (rank 0, N=1 only): bounded sample of the same workload ------
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        from oracle import attention as oatt
+        cores = os.cpu_count() or 1
+        torch.set_num_threads(cores)
+        Bs = 1
+        M = oatt.expand_mask(mat, bs)
+        cQ, cK, cV, cdO = synthetic.qkv(99, Bs, H, L, d)
+        oatt.fwd_bwd_step(cQ, cK, cV, cdO, M)
+        reps = 3
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            oatt.fwd_bwd_step(cQ, cK, cV, cdO, M)
+        cs = (time.perf_counter() - t0) / reps
+        cpu = {"value": Bs * L / cs / 1e6, "unit": "Mtokens/s", "cores": cores, "kind": "port",
+               "sample": f"B={Bs} of {B} batch elements (H={H}, L={L}, d={d}), fp32 dense-masked torch, {reps} timed steps",
+               "s_per_step": cs}
+
+    if rank == 0:
+        line = {
+            "metric": "sparse-attn fwd+bwd Mtokens/s at L=%d" % L, "value": value, "unit": "Mtokens/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16" if dt == "bf16" else "f32", "data": "synthetic",
+            "config": {"workload": args.workload, "B_per_gpu": B, "H": H, "L": L, "d_head": d, "block": bs,
+                       "density": nnzb / float(nb * nb), "nnzb": nnzb, "engine": args.engine,
+                       "l2_policy": "inputs larger than L2 (Q,K,V,dO = %.0f MB, P+dS = %.0f MB per step)"
+                                    % (4 * hQ.numel() * esz / 1e6, 2 * n * esz / 1e6)},
+            "roofline": roofline, "kernels": kern,
+            "step_bound": {"ms": step_bound_ms, "frac": step_bound_ms / ms_step,
+                           "note": "max(12*nnz*d*BH flop / bf16 peak, 12*L*d*e*BH bytes / HBM peak): fully fused bound"},
+            "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,216 @@
+/*
+ * spion_b200 - C ABI of the B200 (sm_100a) implementation of SPION's layer-wise
+ * block-sparse attention path.
+ *
+ * Every pointer below is a DEVICE pointer unless its name starts with host_.  All
+ * buffers (inputs, outputs, scratch) are allocated by the caller (PyTorch in the
+ * reference); the library allocates only its own per-context workspace, at context
+ * creation / spion_set_pattern time, never inside a forward or backward call.
+ * Every call is asynchronous on the context's stream (spion_set_stream; default:
+ * the legacy default stream, like the reference) unless stated otherwise.
+ * Functions return 0 on success and a negative SPION_ERR_* code otherwise (the
+ * reference's entry points return void and ignore every CUDA / cuSPARSE status).
+ *
+ * Citations name files of the reference project (mlsys-lab-sogang/SPION).
+ */
+#ifndef SPION_B200_H
+#define SPION_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct spion_ctx spion_ctx;
+
+enum {
+  SPION_OK = 0,
+  SPION_ERR_ARG = -1,          /* null pointer / bad enum / size mismatch            */
+  SPION_ERR_SHAPE = -2,        /* unsupported shape (e.g. seq_len % block_size != 0)   */
+  SPION_ERR_CUDA = -3,         /* a CUDA runtime call or kernel launch failed          */
+  SPION_ERR_TIMEOUT = -4,      /* a bounded device-side wait gave up (status word)     */
+  SPION_ERR_UNSUPPORTED = -5,  /* combination not built (dtype / head_dim / block)     */
+  SPION_ERR_ALLOC = -6,        /* workspace allocation failed                          */
+  SPION_ERR_STATE = -7         /* call order (e.g. native forward before set_pattern)  */
+};
+
+enum { SPION_F32 = 0, SPION_BF16 = 1 };
+enum { SPION_CONV_DIAG = 0, SPION_CONV_BOX = 1 };
+enum { SPION_SELECT_PATHS = 0, SPION_SELECT_TOPK = 1 };
+enum { SPION_KIND_DENSE = 0, SPION_KIND_DENSE_KPM = 1, SPION_KIND_BLOCK = 2, SPION_KIND_BLOCK_KPM = 3 };
+enum { SPION_ENGINE_AUTO = 0, SPION_ENGINE_SIMT = 1, SPION_ENGINE_TCGEN05 = 2 };
+
+const char* spion_status_string(int status);
+int spion_version(void);
+
+/* ------------------------------------------------------------------ contexts ---- */
+
+/* Replaces `Attention* init(int emb_dim, int seq_len, int num_batches, int block_size)`
+ * of models/block_attn.cu:547 and models/block_attn_mask.cu:655 (kind = BLOCK / BLOCK_KPM)
+ * and `init(int emb_dim, int seq_len, int num_batches)` of models/attn.cu:265 and
+ * models/attn_mask.cu:280 (kind = DENSE / DENSE_KPM, block_size ignored).
+ * num_batches = heads * per-device batch.  dtype: SPION_F32 for the reference's layouts;
+ * SPION_BF16 is accepted by the native (_ex) calls only.  device < 0: current device.
+ * Returns NULL on failure. */
+spion_ctx* spion_create(int kind, int head_dim, int seq_len, int num_batches, int block_size,
+                        int dtype, int device);
+
+/* Replaces `void destroy(Attention*)` (models/block_attn.cu:565, models/attn.cu:278). */
+void spion_destroy(spion_ctx* ctx);
+
+/* The reference runs everything on the legacy default stream (models/block_attn.cu:468);
+ * here the caller chooses (pass torch.cuda.current_stream().cuda_stream). */
+int spion_set_stream(spion_ctx* ctx, void* cuda_stream);
+
+/* SPION_ENGINE_AUTO picks tcgen05 kernels where they exist (bf16, block 64/32, head_dim 64/32),
+ * otherwise the SIMT kernels.  Forcing an engine that cannot run the shape gives UNSUPPORTED. */
+int spion_set_engine(spion_ctx* ctx, int engine);
+
+/* Reads the context's device status word (synchronises the stream).  Non-zero means a
+ * bounded wait inside a kernel gave up; the word is cleared. */
+int spion_check_device_status(spion_ctx* ctx);
+
+/* Number of kernels this context has launched since creation (bench bookkeeping). */
+long long spion_launch_count(const spion_ctx* ctx);
+
+/* Per-kernel timing of the pipelines (the reference has cudaEvent pairs around every stage,
+ * all commented out: models/block_attn.cu:456-486).  enable != 0: CUDA events are recorded on the
+ * context's stream between the kernels of every forward / backward call.  spion_profile_get
+ * synchronises, folds the pending events in, and returns the total milliseconds and the number
+ * of launches of one stage (SPION_STAGE_*); spion_profile_reset clears the totals. */
+enum {
+  SPION_STAGE_STRUCTURE = 0,   /* block CSR/CSC (re)build                         */
+  SPION_STAGE_SDDMM_S = 1,     /* S = Q K^T on the mask                            */
+  SPION_STAGE_SOFTMAX_FWD = 2, /* sparse row softmax                               */
+  SPION_STAGE_SPMM_O = 3,      /* O = P V                                          */
+  SPION_STAGE_SDDMM_DP = 4,    /* dP = dO V^T on the mask                          */
+  SPION_STAGE_SOFTMAX_BWD = 5, /* dS from dP, P                                    */
+  SPION_STAGE_SPMM_DQ = 6,     /* dQ = dS K                                        */
+  SPION_STAGE_SPMM_DK = 7,     /* dK = dS^T Q                                      */
+  SPION_STAGE_SPMM_DV = 8,     /* dV = P^T dO                                      */
+  SPION_STAGE_FUSED_S_P = 9,   /* tcgen05: S tiles + softmax -> P                  */
+  SPION_STAGE_FUSED_DP_DS = 10,/* tcgen05: dP tiles + softmax backward -> dS       */
+  SPION_STAGE_DELTA = 11,      /* row sums of dO*O                                 */
+  SPION_STAGE_SPMM_DKDV = 12,  /* tcgen05: dK and dV in one kernel                 */
+  SPION_STAGE_COUNT = 13
+};
+int spion_profile(spion_ctx* ctx, int enable);
+int spion_profile_get(spion_ctx* ctx, int stage, double* total_ms, long long* launches);
+int spion_profile_reset(spion_ctx* ctx);
+const char* spion_stage_name(int stage);
+
+/* ------------------------------------------ reference-layout sparse attention ---- */
+
+/* Replaces `attn_forward` of models/block_attn.cu:552-556 (keypad == NULL) and of
+ * models/block_attn_mask.cu:660-663 (keypad = the `mask` argument, already multiplied
+ * by 1e6: models/attention_blockcuda_mask.py:42-43; flat index bh*L + column).
+ *   Q [BH,L,d]  Kt [BH,d,L]  V [BH,L,d]  attn [BH*nnz] (out: P in element-CSR order)
+ *   out [BH,L,d]  offsets [L+1]  columns [>= nnz]  sum_mat [L]   (all int32)
+ * nnz = selected elements per (b,h) matrix = Offsets[L]. */
+int spion_block_attn_forward(spion_ctx* ctx, const float* Q, const float* Kt, const float* V,
+                             const float* keypad, float* attn, float* out,
+                             const int* offsets, const int* columns, const int* sum_mat, int nnz);
+
+/* Replaces `attn_backward` of models/block_attn.cu:558-563 / models/block_attn_mask.cu:665-670.
+ *   Q [BH,L,d]  K [BH,L,d]  Vt [BH,d,L]  P [BH*nnz]  dO [BH,L,d]
+ *   dP_scratch, dS_scratch [BH*nnz] (caller-allocated, contents destroyed)
+ *   dQ, dK, dV [BH,L,d] (out). */
+int spion_block_attn_backward(spion_ctx* ctx, const float* Q, const float* K, const float* Vt,
+                              const float* P, const float* dO, float* dP_scratch, float* dS_scratch,
+                              float* dQ, float* dK, float* dV,
+                              const int* offsets, const int* columns, const int* sum_mat, int nnz);
+
+/* ------------------------------------------- reference-layout dense attention ---- */
+
+/* Replaces `attn_forward` of models/attn.cu:269 (keypad == NULL) and models/attn_mask.cu:284.
+ * Layouts as the reference's Python passes them (models/attention_cuda.py:18-36):
+ *   Qt [BH,d,L]  K [BH,L,d]  Vt [BH,d,L]  attn [BH,L,L] stored transposed (attn[bh,j,i] = P[i,j])
+ *   out [BH,d,L]. */
+int spion_dense_attn_forward(spion_ctx* ctx, const float* Qt, const float* K, const float* Vt,
+                             const float* keypad, float* attn, float* out);
+
+/* Replaces `attn_backward` of models/attn.cu:273 / models/attn_mask.cu:288
+ * (models/attention_cuda.py:39-74):
+ *   Qt [BH,d,L]  Kt [BH,d,L]  V [BH,L,d]  attn [BH,L,L] (as written by forward)  dOt [BH,d,L]
+ *   s1, s2, s3 [BH*L*L] caller scratch (s1 receives dP, s3 receives dS; s2 is not touched)
+ *   dQt, dKt, dVt [BH,d,L] (out). */
+int spion_dense_attn_backward(spion_ctx* ctx, const float* Qt, const float* Kt, const float* V,
+                              const float* attn, const float* dOt, float* s1, float* s2, float* s3,
+                              float* dQt, float* dKt, float* dVt);
+
+/* Head/batch mean of the dense attention tensor (models/model_transformer.py:137):
+ * A[i,j] = mean_h mean_b P[b,h,i,j].  `attn` is [B*H, L, L]; transposed != 0 means it is
+ * stored as spion_dense_attn_forward writes it. */
+int spion_mean_attention_map(const float* attn, int batch, int heads, int L, int transposed,
+                             float* A, void* cuda_stream);
+
+/* ------------------------------------------------------------ pattern discovery ---- */
+
+/* Replaces the inline driver block main_conv_ff.py:255-279 (and its flood_fill, :35-62):
+ *   pooled = avg_pool(conv(A)) ; thresh = quantile(pooled, param) ; 2*nb greedy walkers ;
+ *   binarise ; force the diagonal ; block CSR + CSC.
+ * select = SPION_SELECT_TOPK replaces main_conv.py:246-251 (param = density).
+ * F = 1 skips the convolution (main_ff.py:255).
+ *   A [L,L] fp32            mat [nb*nb] uint8 (out)       pooled [nb*nb] fp32 (out)
+ *   thresh [1] fp32 (out)   nnzb [1] int32 (out)
+ *   row_ptr [nb+1], col_idx [nb*nb], blk_row [nb*nb]      block CSR (out; first nnzb entries valid)
+ *   col_ptr [nb+1], row_idx [nb*nb], csc_pos [nb*nb]      block CSC (out; csc_pos = CSR block id)
+ *   work [nb*nb] int32 scratch
+ * host_nnzb: if not NULL the call synchronises the stream and stores the block count. */
+int spion_discover_pattern(const float* A, int L, int block_size, int conv_kind, int F,
+                           int select, double param,
+                           uint8_t* mat, float* pooled, float* thresh, int32_t* nnzb,
+                           int32_t* row_ptr, int32_t* col_idx, int32_t* blk_row,
+                           int32_t* col_ptr, int32_t* row_idx, int32_t* csc_pos,
+                           int32_t* work, int32_t* host_nnzb, void* cuda_stream);
+
+/* Block CSR + CSC of a given 0/1 mask (e.g. one loaded from the reference's pickle,
+ * main_inference.py:164-166).  Same outputs as above. */
+int spion_build_structure(const uint8_t* mat, int nb, int32_t* nnzb,
+                          int32_t* row_ptr, int32_t* col_idx, int32_t* blk_row,
+                          int32_t* col_ptr, int32_t* row_idx, int32_t* csc_pos,
+                          int32_t* work, int32_t* host_nnzb, void* cuda_stream);
+
+/* Replaces the per-call CSR construction of models/attention_blockcuda.py:31-43:
+ *   sum_mat [L], offsets [L+1], columns [repeat * nnz]  (int32), nnz = nnzb * bs^2. */
+int spion_expand_csr(const int32_t* row_ptr, const int32_t* col_idx, int nb, int block_size,
+                     int nnzb, int repeat, int32_t* sum_mat, int32_t* offsets, int32_t* columns,
+                     void* cuda_stream);
+
+/* ------------------------------------------------------- native (block-tile) API ---- */
+
+/* Fix the layer's block mask for the native calls (done once per layer at discovery,
+ * where the reference calls reconstruct_for_blocksparse, models/attention.py:105).
+ * mat [nb*nb] uint8 device.  Synchronises once to learn the block count. */
+int spion_set_pattern(spion_ctx* ctx, const uint8_t* mat);
+int spion_pattern_nnzb(const spion_ctx* ctx);
+
+/* Native forward.  dtype = the context's (fp32 or bf16 elements).
+ *   Q, K, V, O  [BH,L,d] row-major (no transposed copies: compare attention_blockcuda.py:48)
+ *   P           [BH, nnzb, bs, bs] block tiles in CSR block order (out; needed by backward)
+ *   keypad      [BH*L] fp32 penalty (1e6 on padded keys) or NULL
+ *   S_scratch   [BH*nnzb*bs*bs] fp32, used by the SIMT engine only (may be NULL otherwise). */
+int spion_attn_forward_ex(spion_ctx* ctx, const void* Q, const void* K, const void* V,
+                          const float* keypad, void* P, void* O, float* S_scratch);
+
+/* Native backward.
+ *   dS          [BH, nnzb, bs, bs] elements of the context dtype (scratch, written)
+ *   dP_scratch  [BH*nnzb*bs*bs] fp32, used by the SIMT engine only
+ *   delta       [BH*L] fp32 scratch (row sums of dO*O), used by the tcgen05 engine only
+ *   dQ, dK, dV  [BH,L,d] (out). */
+int spion_attn_backward_ex(spion_ctx* ctx, const void* Q, const void* K, const void* V,
+                           const void* P, const void* O, const void* dO,
+                           void* dS, float* dP_scratch, float* delta,
+                           void* dQ, void* dK, void* dV);
+
+/* Stand-alone sparse row softmax on block tiles (the kernels of models/block_attn.cu:33-130):
+ * forward S (fp32 tiles) -> P (context dtype), backward (dP fp32, P) -> dS (context dtype). */
+int spion_softmax_forward_ex(spion_ctx* ctx, const float* S, const float* keypad, void* P);
+int spion_softmax_backward_ex(spion_ctx* ctx, const float* dP, const void* P, void* dS);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SPION_B200_H */

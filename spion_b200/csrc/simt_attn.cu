@@ -1,0 +1,386 @@
+// SIMT (CUDA-core, fp32 accumulate) kernels of the block-sparse attention path.
+//
+// They serve (1) the reference's fp32 layouts behind the drop-in entry points, where the
+// 1e-4 max-abs parity bound rules out TF32/BF16 tensor-core inputs, and (2) every shape the
+// tcgen05 engine does not cover.  Each kernel works on whole bs x bs blocks of the layer's
+// mask; value tiles and dense operands are addressed through strides so that the reference's
+// element-CSR layout, its transposed operands (models/attention_blockcuda.py:48,80), its
+// S^T-stored dense attention (models/attention_cuda.py:36) and the native block-tile layout
+// all go through the same code.
+//
+//   simt_sddmm        replaces cusparseSDDMM      (models/block_attn.cu:145-224, calls :459,:498)
+//   simt_spmm         replaces cusparseSpMM N / T (models/block_attn.cu:236-393, calls :478,:516,:526,:536)
+//   softmax_fwd_rows  replaces scale_softmax_kernel            (models/block_attn.cu:33-88, _mask.cu:88-140)
+//   softmax_bwd_rows  replaces softmax_scale_backward_kernel   (models/block_attn.cu:90-130)
+//   softmax_*_dense_t replace max_sum_exp_kernel[_large] / softmax_scale_backward_kernel[_large]
+//                     (models/attn.cu:9-112, models/attn_mask.cu:8-122)
+#include "common.cuh"
+
+namespace {
+
+constexpr int KC = 32;   // contraction chunk held in shared memory
+
+template <typename T>
+__device__ __forceinline__ float load_op(const T* base, long long idx) { return to_f32(base[idx]); }
+
+// ------------------------------------------------------------------------------ SDDMM
+// One CTA per (block, bh): vals(i,j) = sum_n A[r*bs+i, n] * B[c*bs+j, n].
+template <typename TI, typename TV, int TM>
+__global__ void __launch_bounds__(256) sddmm_kernel(const TI* __restrict__ A, OperandLayout la, const TI* __restrict__ B,
+                                                    OperandLayout lb, TV* __restrict__ vals, ValueLayout vl, Pattern p,
+                                                    int d) {
+  constexpr int BS = TM * 16;
+  __shared__ float As[KC][BS + 1];
+  __shared__ float Bs[KC][BS + 1];
+  const int blk = blockIdx.x, bh = blockIdx.y;
+  const int r = p.blk_row[blk], c = p.col_idx[blk];
+  const TI* Ab = A + (long long)bh * la.bh_stride + (long long)r * BS * la.sl;
+  const TI* Bb = B + (long long)bh * lb.bh_stride + (long long)c * BS * lb.sl;
+  const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
+  float acc[TM][TM];
+#pragma unroll
+  for (int a = 0; a < TM; ++a)
+#pragma unroll
+    for (int b = 0; b < TM; ++b) acc[a][b] = 0.f;
+
+  for (int n0 = 0; n0 < d; n0 += KC) {
+    for (int idx = tid; idx < BS * KC; idx += 256) {
+      int i, n;
+      if (la.sd == 1) { n = idx % KC; i = idx / KC; } else { i = idx % BS; n = idx / BS; }
+      As[n][i] = load_op(Ab, (long long)i * la.sl + (long long)(n0 + n) * la.sd);
+      if (lb.sd == 1) { n = idx % KC; i = idx / KC; } else { i = idx % BS; n = idx / BS; }
+      Bs[n][i] = load_op(Bb, (long long)i * lb.sl + (long long)(n0 + n) * lb.sd);
+    }
+    __syncthreads();
+#pragma unroll 8
+    for (int k = 0; k < KC; ++k) {
+      float a[TM], b[TM];
+#pragma unroll
+      for (int m = 0; m < TM; ++m) a[m] = As[k][ty * TM + m];
+#pragma unroll
+      for (int m = 0; m < TM; ++m) b[m] = Bs[k][tx * TM + m];
+#pragma unroll
+      for (int x = 0; x < TM; ++x)
+#pragma unroll
+        for (int y = 0; y < TM; ++y) acc[x][y] = fmaf(a[x], b[y], acc[x][y]);
+    }
+    __syncthreads();
+  }
+  long long base, si, sj;
+  tile_address(vl, p, r, c, blk, base, si, sj);
+  TV* out = vals + (long long)bh * vl.bh_stride + base;
+#pragma unroll
+  for (int x = 0; x < TM; ++x)
+#pragma unroll
+    for (int y = 0; y < TM; ++y) out[(long long)(ty * TM + x) * si + (long long)(tx * TM + y) * sj] = from_f32<TV>(acc[x][y]);
+}
+
+// ------------------------------------------------------------------------------ SpMM
+// TRANS == false: one CTA per (block row r, bh):  out[r*bs+i, :] = sum_{c in row r} vals_{r,c}(i,j) * Bop[c*bs+j, :]
+// TRANS == true : one CTA per (block col c, bh):  out[c*bs+j, :] = sum_{r in col c} vals_{r,c}(i,j) * Bop[r*bs+i, :]
+// Output columns are produced 32 at a time (grid.z chunks of the head dimension).
+template <typename TV, typename TO, int TM, bool TRANS>
+__global__ void __launch_bounds__(256) spmm_kernel(const TV* __restrict__ vals, ValueLayout vl, const TO* __restrict__ Bop,
+                                                   OperandLayout lb, TO* __restrict__ out, OperandLayout lo, Pattern p) {
+  constexpr int BS = TM * 16;
+  constexpr int TN = 2;                 // 16 thread columns x 2 = 32 output columns per chunk
+  __shared__ float As[BS][BS + 1];      // As[k][m]
+  __shared__ float Bs[BS][32 + 1];      // Bs[k][n]
+  const int line = blockIdx.x, bh = blockIdx.y, n0 = blockIdx.z * 32;
+  const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
+  const int beg = TRANS ? p.col_ptr[line] : p.row_ptr[line];
+  const int end = TRANS ? p.col_ptr[line + 1] : p.row_ptr[line + 1];
+  const TV* vb = vals + (long long)bh * vl.bh_stride;
+  const TO* Bb = Bop + (long long)bh * lb.bh_stride;
+  float acc[TM][TN];
+#pragma unroll
+  for (int a = 0; a < TM; ++a)
+#pragma unroll
+    for (int b = 0; b < TN; ++b) acc[a][b] = 0.f;
+
+  for (int e = beg; e < end; ++e) {
+    int r, c, blk;
+    if (TRANS) { c = line; r = p.row_idx[e]; blk = p.csc_pos[e]; } else { r = line; blk = e; c = p.col_idx[e]; }
+    long long base, si, sj;
+    tile_address(vl, p, r, c, blk, base, si, sj);
+    const TV* tile = vb + base;
+    for (int idx = tid; idx < BS * BS; idx += 256) {
+      int i, j;
+      if (sj == 1) { j = idx % BS; i = idx / BS; } else { i = idx % BS; j = idx / BS; }
+      const float v = to_f32(tile[(long long)i * si + (long long)j * sj]);
+      if (TRANS) As[i][j] = v; else As[j][i] = v;
+    }
+    const int krow0 = (TRANS ? r : c) * BS;
+    for (int idx = tid; idx < BS * 32; idx += 256) {
+      int k, n;
+      if (lb.sd == 1) { n = idx % 32; k = idx / 32; } else { k = idx % BS; n = idx / BS; }
+      Bs[k][n] = to_f32(Bb[(long long)(krow0 + k) * lb.sl + (long long)(n0 + n) * lb.sd]);
+    }
+    __syncthreads();
+#pragma unroll 8
+    for (int k = 0; k < BS; ++k) {
+      float a[TM], b[TN];
+#pragma unroll
+      for (int m = 0; m < TM; ++m) a[m] = As[k][ty * TM + m];
+#pragma unroll
+      for (int n = 0; n < TN; ++n) b[n] = Bs[k][tx * TN + n];
+#pragma unroll
+      for (int x = 0; x < TM; ++x)
+#pragma unroll
+        for (int y = 0; y < TN; ++y) acc[x][y] = fmaf(a[x], b[y], acc[x][y]);
+    }
+    __syncthreads();
+  }
+  TO* ob = out + (long long)bh * lo.bh_stride + (long long)line * BS * lo.sl;
+#pragma unroll
+  for (int x = 0; x < TM; ++x)
+#pragma unroll
+    for (int y = 0; y < TN; ++y)
+      ob[(long long)(ty * TM + x) * lo.sl + (long long)(n0 + tx * TN + y) * lo.sd] = from_f32<TO>(acc[x][y]);
+}
+
+// ------------------------------------------------------------------------------ row softmax
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// One warp per element row.  Values of a row: for each block k of block row r, bs consecutive
+// elements at tile base + ii*si (sj == 1 layouts only).
+//   v = S*scale - keypad[col];  m = max(floor, max v);  Z = sum exp(v-m) + (L-n_i) exp(-m);  P = exp(v-m)/Z
+template <typename TP>
+__global__ void __launch_bounds__(256) softmax_fwd_rows_kernel(const float* S, ValueLayout vin,   // S may alias P
+                                                               TP* P, ValueLayout vout, Pattern p, int BH,
+                                                               int L, float scale, const float* __restrict__ keypad,
+                                                               float floor_v) {
+  const long long row_g = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row_g >= (long long)BH * L) return;
+  const int lane = threadIdx.x & 31;
+  const int bh = (int)(row_g / L), row = (int)(row_g % L);
+  const int bs = p.bs, r = row / bs, ii = row % bs;
+  const int rp = p.row_ptr[r], nblk = p.row_ptr[r + 1] - rp;
+  const float* Sb = S + (long long)bh * vin.bh_stride;
+  TP* Pb = P + (long long)bh * vout.bh_stride;
+  const float* kp = keypad ? keypad + (long long)bh * L : nullptr;
+
+  float m = floor_v;
+  for (int k = 0; k < nblk; ++k) {
+    const int blk = rp + k, c = p.col_idx[blk];
+    long long base, si, sj;
+    tile_address(vin, p, r, c, blk, base, si, sj);
+    const float* src = Sb + base + (long long)ii * si;
+    for (int j = lane; j < bs; j += 32) {
+      float v = src[j] * scale;
+      if (kp) v -= kp[c * bs + j];
+      m = fmaxf(m, v);
+    }
+  }
+  m = warp_max(m);
+  float sum = 0.f;
+  for (int k = 0; k < nblk; ++k) {
+    const int blk = rp + k, c = p.col_idx[blk];
+    long long base, si, sj;
+    tile_address(vin, p, r, c, blk, base, si, sj);
+    const float* src = Sb + base + (long long)ii * si;
+    for (int j = lane; j < bs; j += 32) {
+      float v = src[j] * scale;
+      if (kp) v -= kp[c * bs + j];
+      sum += expf(v - m);
+    }
+  }
+  sum = warp_sum(sum);
+  sum += (float)(L - nblk * bs) * expf(-m);
+  const float inv = 1.0f / sum;
+  for (int k = 0; k < nblk; ++k) {
+    const int blk = rp + k, c = p.col_idx[blk];
+    long long base, si, sj, obase, osi, osj;
+    tile_address(vin, p, r, c, blk, base, si, sj);
+    tile_address(vout, p, r, c, blk, obase, osi, osj);
+    const float* src = Sb + base + (long long)ii * si;
+    TP* dst = Pb + obase + (long long)ii * osi;
+    for (int j = lane; j < bs; j += 32) {
+      float v = src[j] * scale;
+      if (kp) v -= kp[c * bs + j];
+      const float pv = (inv == 0.f) ? 0.f : expf(v - m) * inv;
+      dst[j] = from_f32<TP>(pv);
+    }
+  }
+}
+
+//   t = dP*P ; s = sum_row t ; dS = (t - P*s) * scale
+template <typename TP>
+__global__ void __launch_bounds__(256) softmax_bwd_rows_kernel(const float* __restrict__ dP, ValueLayout vdp,
+                                                               const TP* __restrict__ P, ValueLayout vp,
+                                                               TP* __restrict__ dS, ValueLayout vds, Pattern p, int BH,
+                                                               int L, float scale) {
+  const long long row_g = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row_g >= (long long)BH * L) return;
+  const int lane = threadIdx.x & 31;
+  const int bh = (int)(row_g / L), row = (int)(row_g % L);
+  const int bs = p.bs, r = row / bs, ii = row % bs;
+  const int rp = p.row_ptr[r], nblk = p.row_ptr[r + 1] - rp;
+  const float* dPb = dP + (long long)bh * vdp.bh_stride;
+  const TP* Pb = P + (long long)bh * vp.bh_stride;
+  TP* dSb = dS + (long long)bh * vds.bh_stride;
+  float s = 0.f;
+  for (int k = 0; k < nblk; ++k) {
+    const int blk = rp + k, c = p.col_idx[blk];
+    long long b1, s1, t1, b2, s2, t2;
+    tile_address(vdp, p, r, c, blk, b1, s1, t1);
+    tile_address(vp, p, r, c, blk, b2, s2, t2);
+    const float* a = dPb + b1 + (long long)ii * s1;
+    const TP* q = Pb + b2 + (long long)ii * s2;
+    for (int j = lane; j < bs; j += 32) s += a[j] * to_f32(q[j]);
+  }
+  s = warp_sum(s);
+  for (int k = 0; k < nblk; ++k) {
+    const int blk = rp + k, c = p.col_idx[blk];
+    long long b1, s1, t1, b2, s2, t2, b3, s3, t3;
+    tile_address(vdp, p, r, c, blk, b1, s1, t1);
+    tile_address(vp, p, r, c, blk, b2, s2, t2);
+    tile_address(vds, p, r, c, blk, b3, s3, t3);
+    const float* a = dPb + b1 + (long long)ii * s1;
+    const TP* q = Pb + b2 + (long long)ii * s2;
+    TP* o = dSb + b3 + (long long)ii * s3;
+    for (int j = lane; j < bs; j += 32) {
+      const float pv = to_f32(q[j]);
+      o[j] = from_f32<TP>((a[j] * pv - pv * s) * scale);
+    }
+  }
+}
+
+// Dense attention stored transposed (value(i,j) at j*L + i): one thread per query row i, so that
+// consecutive threads touch consecutive addresses while walking the keys j.
+__global__ void softmax_fwd_dense_t_kernel(float* __restrict__ S, int L, float scale, const float* __restrict__ keypad,
+                                           float floor_v) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  const int bh = blockIdx.y;
+  if (i >= L) return;
+  float* Sb = S + (long long)bh * L * L + i;
+  const float* kp = keypad ? keypad + (long long)bh * L : nullptr;
+  float m = floor_v, sum = 0.f;
+  for (int j = 0; j < L; ++j) {                          // online max / sum
+    float v = Sb[(long long)j * L] * scale;
+    if (kp) v -= kp[j];
+    if (v > m) { sum *= expf(m - v); m = v; }
+    sum += expf(v - m);
+  }
+  const float inv = 1.0f / sum;
+  for (int j = 0; j < L; ++j) {
+    float v = Sb[(long long)j * L] * scale;
+    if (kp) v -= kp[j];
+    Sb[(long long)j * L] = expf(v - m) * inv;
+  }
+}
+
+__global__ void softmax_bwd_dense_t_kernel(const float* __restrict__ dP, const float* __restrict__ P,
+                                           float* __restrict__ dS, int L, float scale) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  const int bh = blockIdx.y;
+  if (i >= L) return;
+  const long long o = (long long)bh * L * L + i;
+  float s = 0.f;
+  for (int j = 0; j < L; ++j) s += dP[o + (long long)j * L] * P[o + (long long)j * L];
+  for (int j = 0; j < L; ++j) {
+    const float pv = P[o + (long long)j * L];
+    dS[o + (long long)j * L] = (dP[o + (long long)j * L] * pv - pv * s) * scale;
+  }
+}
+
+}  // namespace
+
+// ================================================================================ launchers
+template <typename TI, typename TV>
+static int sddmm_dispatch(const void* A, OperandLayout la, const void* B, OperandLayout lb, void* vals, ValueLayout vl,
+                          Pattern p, int nnzb, int BH, int d, cudaStream_t st) {
+  dim3 grid(nnzb, BH);
+  if (p.bs == 64)
+    sddmm_kernel<TI, TV, 4><<<grid, 256, 0, st>>>((const TI*)A, la, (const TI*)B, lb, (TV*)vals, vl, p, d);
+  else if (p.bs == 32)
+    sddmm_kernel<TI, TV, 2><<<grid, 256, 0, st>>>((const TI*)A, la, (const TI*)B, lb, (TV*)vals, vl, p, d);
+  else
+    return SPION_ERR_UNSUPPORTED;
+  SPION_LAUNCH_CHECK();
+  return SPION_OK;
+}
+
+int simt_sddmm(int dtype_in, int dtype_val, const void* A, OperandLayout la, const void* B, OperandLayout lb, void* vals,
+               ValueLayout vl, Pattern p, int nnzb, int BH, int d, cudaStream_t st) {
+  if (d % KC != 0 || BH > 65535) return SPION_ERR_UNSUPPORTED;
+  if (nnzb == 0) return SPION_OK;
+  if (dtype_in == SPION_F32 && dtype_val == SPION_F32)
+    return sddmm_dispatch<float, float>(A, la, B, lb, vals, vl, p, nnzb, BH, d, st);
+  if (dtype_in == SPION_BF16 && dtype_val == SPION_F32)
+    return sddmm_dispatch<__nv_bfloat16, float>(A, la, B, lb, vals, vl, p, nnzb, BH, d, st);
+  return SPION_ERR_UNSUPPORTED;
+}
+
+template <typename TV, typename TO>
+static int spmm_dispatch(bool trans, const void* vals, ValueLayout vl, const void* Bop, OperandLayout lb, void* out,
+                         OperandLayout lo, Pattern p, int BH, int d, cudaStream_t st) {
+  dim3 grid(p.nb, BH, d / 32);
+#define SPION_SPMM(TMv, TR) \
+  spmm_kernel<TV, TO, TMv, TR><<<grid, 256, 0, st>>>((const TV*)vals, vl, (const TO*)Bop, lb, (TO*)out, lo, p)
+  if (p.bs == 64) { if (trans) SPION_SPMM(4, true); else SPION_SPMM(4, false); }
+  else if (p.bs == 32) { if (trans) SPION_SPMM(2, true); else SPION_SPMM(2, false); }
+  else return SPION_ERR_UNSUPPORTED;
+#undef SPION_SPMM
+  SPION_LAUNCH_CHECK();
+  return SPION_OK;
+}
+
+int simt_spmm(int dtype_val, int dtype_op, bool trans, const void* vals, ValueLayout vl, const void* Bop,
+              OperandLayout lb, void* out, OperandLayout lo, Pattern p, int BH, int d, cudaStream_t st) {
+  if (d % 32 != 0 || BH > 65535) return SPION_ERR_UNSUPPORTED;
+  if (dtype_val == SPION_F32 && dtype_op == SPION_F32)
+    return spmm_dispatch<float, float>(trans, vals, vl, Bop, lb, out, lo, p, BH, d, st);
+  if (dtype_val == SPION_BF16 && dtype_op == SPION_BF16)
+    return spmm_dispatch<__nv_bfloat16, __nv_bfloat16>(trans, vals, vl, Bop, lb, out, lo, p, BH, d, st);
+  return SPION_ERR_UNSUPPORTED;
+}
+
+int softmax_fwd_rows(int dtype_out, const float* S, ValueLayout vin, void* P, ValueLayout vout, Pattern p, int BH, int L,
+                     float scale, const float* keypad, float floor_v, cudaStream_t st) {
+  const long long rows = (long long)BH * L;
+  const unsigned grid = (unsigned)((rows + 7) / 8);
+  if (dtype_out == SPION_F32)
+    softmax_fwd_rows_kernel<float><<<grid, 256, 0, st>>>(S, vin, (float*)P, vout, p, BH, L, scale, keypad, floor_v);
+  else
+    softmax_fwd_rows_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(S, vin, (__nv_bfloat16*)P, vout, p, BH, L, scale,
+                                                                 keypad, floor_v);
+  SPION_LAUNCH_CHECK();
+  return SPION_OK;
+}
+
+int softmax_bwd_rows(int dtype_p, const float* dP, ValueLayout vdp, const void* P, ValueLayout vp, void* dS,
+                     ValueLayout vds, Pattern p, int BH, int L, float scale, cudaStream_t st) {
+  const long long rows = (long long)BH * L;
+  const unsigned grid = (unsigned)((rows + 7) / 8);
+  if (dtype_p == SPION_F32)
+    softmax_bwd_rows_kernel<float><<<grid, 256, 0, st>>>(dP, vdp, (const float*)P, vp, (float*)dS, vds, p, BH, L, scale);
+  else
+    softmax_bwd_rows_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(dP, vdp, (const __nv_bfloat16*)P, vp,
+                                                                 (__nv_bfloat16*)dS, vds, p, BH, L, scale);
+  SPION_LAUNCH_CHECK();
+  return SPION_OK;
+}
+
+int softmax_fwd_dense_t(float* S, int BH, int L, float scale, const float* keypad, float floor_v, cudaStream_t st) {
+  if (BH > 65535) return SPION_ERR_UNSUPPORTED;
+  softmax_fwd_dense_t_kernel<<<dim3((L + 127) / 128, BH), 128, 0, st>>>(S, L, scale, keypad, floor_v);
+  SPION_LAUNCH_CHECK();
+  return SPION_OK;
+}
+
+int softmax_bwd_dense_t(const float* dP, const float* P, float* dS, int BH, int L, float scale, cudaStream_t st) {
+  if (BH > 65535) return SPION_ERR_UNSUPPORTED;
+  softmax_bwd_dense_t_kernel<<<dim3((L + 127) / 128, BH), 128, 0, st>>>(dP, P, dS, L, scale);
+  SPION_LAUNCH_CHECK();
+  return SPION_OK;
+}

@@ -1,0 +1,160 @@
+"""Synthetic-data training harness around the attention path (stock torch.nn everywhere else).
+
+The encoder, task heads and training loop of the reference (models/model_transformer.py,
+models/model_LRA.py, main_conv_ff.py:132-318) are not part of the accelerated path; this file
+is the thin stand-in that lets the end-to-end benchmark configs run: a 2-layer pre-LN encoder
+classifier (single or dual tower) whose attention is ``spion_b200.attention.Attention``, with
+the reference's phase structure -- dense warm-up steps that return the per-layer mean
+attention map, pattern discovery, then sparse steps -- and data parallelism from
+``spion_b200.dp``.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+
+from . import dp
+from .attention import Attention
+from .pattern import discover_layers
+
+
+def task_config(task: str, batch_size: int, native: bool = True, dtype: str = "fp32"):
+    """Model dictionaries with the reference's keys and values (config.py) for the three
+    benchmark shapes; max_seq_len is rounded up to a power of two as main_conv_ff.py:385 does."""
+    base = dict(learn_pos_emb=True, tied_weights=False, embedding_dim=64, transformer_dim=64,
+                transformer_hidden_dim=128, head_dim=32, num_head=2, num_layers=2, dropout_prob=0.1,
+                attention_dropout=0.1, pooling_mode="MEAN", mixed_precision=(dtype == "bf16"),
+                batch_size=batch_size, native=native, dtype=dtype)
+    if task == "image":
+        base.update(task="lra-image", vocab_size=256, max_seq_len=1024, num_classes=10, block_size=32,
+                    threshold=0.96, density=0.04, dual=False)
+    elif task == "text":
+        base.update(task="lra-text", vocab_size=256, max_seq_len=4096, num_classes=2, block_size=64,
+                    threshold=0.99, density=0.03, dual=False)
+    elif task == "retrieval":
+        base.update(task="lra-retrieval", vocab_size=256, max_seq_len=4096, num_classes=2, block_size=64,
+                    threshold=0.99, density=0.021, dual=True)
+    else:
+        raise ValueError(task)
+    return base
+
+
+class Embeddings(nn.Module):
+    def __init__(self, config):
+        super().__init__()
+        self.tok = nn.Embedding(config["vocab_size"], config["embedding_dim"])
+        self.pos = nn.Embedding(config["max_seq_len"], config["embedding_dim"])
+        nn.init.normal_(self.tok.weight, std=0.02)
+        nn.init.normal_(self.pos.weight, std=0.02)
+        self.drop = nn.Dropout(config["dropout_prob"])
+
+    def forward(self, ids):
+        pos = torch.arange(ids.shape[1], device=ids.device)
+        return self.drop(self.tok(ids) + self.pos(pos)[None])
+
+
+class TransformerLayer(nn.Module):
+    def __init__(self, config):
+        super().__init__()
+        dim, hid, p = config["transformer_dim"], config["transformer_hidden_dim"], config["dropout_prob"]
+        self.norm1 = nn.LayerNorm(dim)
+        self.mha = Attention(config)
+        self.dropout1 = nn.Dropout(p)
+        self.norm2 = nn.LayerNorm(dim)
+        self.mlpblock = nn.Sequential(nn.Linear(dim, hid), nn.GELU(), nn.Dropout(p), nn.Linear(hid, dim), nn.Dropout(p))
+
+    def forward(self, X, mask, mat=None):
+        out, attn = self.mha(self.norm1(X), mask, mat)
+        X = self.dropout1(out) + X
+        return self.mlpblock(self.norm2(X)) + X, attn
+
+
+class Encoder(nn.Module):
+    def __init__(self, config):
+        super().__init__()
+        self.embeddings = Embeddings(config)
+        self.layers = nn.ModuleList(TransformerLayer(config) for _ in range(config["num_layers"]))
+        self.norm = nn.LayerNorm(config["transformer_dim"])
+
+    def forward(self, ids, mask, mat_lst=None, is_attn=False):
+        from .pattern import mean_attention_map
+        X = self.embeddings(ids)
+        maps = []
+        for i, layer in enumerate(self.layers):
+            if mat_lst is None:
+                X, attn = layer(X, mask)
+                if is_attn:
+                    # attn is the permuted view of the S^T-stored tensor: its base is contiguous
+                    maps.append(mean_attention_map(attn.permute(0, 1, 3, 2), transposed_storage=True))
+            else:
+                X, _ = layer(X, mask, mat_lst[0][i])
+        return self.norm(X) * mask[:, :, None], maps
+
+
+class Classifier(nn.Module):
+    """Single tower (image / text) or dual tower sharing one encoder (retrieval)."""
+
+    def __init__(self, config):
+        super().__init__()
+        self.config = config
+        self.dual = bool(config.get("dual", False))
+        self.amp = bool(config.get("mixed_precision", False))
+        self.model = Encoder(config)
+        dim, hid = config["transformer_dim"], config["transformer_hidden_dim"]
+        self.head = nn.Sequential(nn.Linear(dim * (4 if self.dual else 1), hid), nn.ReLU(),
+                                  nn.Linear(hid, config["num_classes"]))
+
+    def forward(self, ids, label, mat_lst=None, is_attn=False):
+        with torch.autocast(device_type="cuda", dtype=torch.bfloat16, enabled=self.amp):
+            if self.dual:
+                m0, m1 = (ids[0] != 0).float(), (ids[1] != 0).float()        # models/dataset_LRA.py:34
+                t0, maps = self.model(ids[0], m0, mat_lst, is_attn)
+                t1, _ = self.model(ids[1], m1, mat_lst, False)
+                x0, x1 = t0.mean(1), t1.mean(1)
+                scores = self.head(torch.cat([x0, x1, x0 * x1, x0 - x1], dim=-1))
+            else:
+                mask = (ids != 0).float()
+                t, maps = self.model(ids, mask, mat_lst, is_attn)
+                scores = self.head(t.mean(1))
+            loss = nn.functional.cross_entropy(scores.float(), label)
+        return loss, maps
+
+
+class Trainer:
+    """dense step(s) -> discover -> sparse steps, with one flat-bucket all-reduce per step."""
+
+    def __init__(self, config, lr: float = 1e-4, device=None, seed: int = 0):
+        self.config = config
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+        torch.manual_seed(seed)                      # identical initial weights on every rank
+        self.model = Classifier(config).to(self.device)
+        self.bucket = dp.FlatGradBucket(self.model.parameters())
+        self.opt = torch.optim.AdamW(self.model.parameters(), lr=lr, weight_decay=0.0)
+        self.mat_lst = None
+        self.patterns = None
+
+    def step(self, ids, label, is_attn=False):
+        self.bucket.zero()
+        loss, maps = self.model(ids, label, self.mat_lst, is_attn)
+        loss.backward()
+        self.bucket.allreduce_mean()
+        torch.nn.utils.clip_grad_value_(self.model.parameters(), 1.0)   # main_conv_ff.py:186
+        self.opt.step()
+        return loss.detach(), maps
+
+    def discover(self, maps, threshold=None):
+        cfg = dict(self.config)
+        if threshold is not None:
+            cfg["threshold"] = threshold
+        bs = cfg["block_size"]
+
+        def disc(A):
+            from .pattern import discover_pattern
+            return discover_pattern(A, bs, cfg["threshold"]).mat
+
+        masks = dp.agree_on_masks(maps, disc)
+        mats = torch.stack([m.to(torch.float32) for m in masks], 0)
+        self.mat_lst = torch.stack([mats, mats, mats, mats], 0)          # main_conv_ff.py:298-299
+        for layer in self.model.model.layers:
+            layer.mha.reconstruct_for_blocksparse(cfg)
+        return self.mat_lst

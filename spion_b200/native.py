@@ -1,0 +1,137 @@
+"""Native (block-tile) sparse attention module: the B200-first entry point.
+
+Same call shape as the reference's sparse modules -- ``forward(query, key, value, mask, mat)``
+-> ``(out, attn)`` with ``[B, H, L, d]`` tensors -- but without the reference's per-call costs:
+
+* fp32 *or* bf16 elements (the reference forces fp32, models/attention.py:88-92);
+* no transposed copies of K (forward) and V (backward) (models/attention_blockcuda.py:48,80);
+* block CSR/CSC fixed once per layer (``set_mask``), not rebuilt per call (:26-43);
+* P is kept as ``[BH, nnzb, bs, bs]`` tiles, which is what TMA and the tensor cores want.
+
+``attn`` is returned in that tile layout (use ``to_reference_order`` to compare with the
+reference's element-CSR order).
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+
+from . import _lib
+from ._lib import check, lib, ptr
+
+_DTYPES = {torch.float32: _lib.F32, torch.bfloat16: _lib.BF16}
+
+
+class BlockSparseAttention(nn.Module):
+    def __init__(self, config, dtype=torch.float32, keypad: bool = False, engine: int = _lib.ENGINE_AUTO,
+                 device=None):
+        super().__init__()
+        self.d = config["head_dim"]
+        self.H = config["num_head"]
+        self.L = config["max_seq_len"]
+        self.B = config["batch_size"]
+        self.bs = config["block_size"]
+        self.BH = self.B * self.H
+        self.dtype = dtype
+        self.keypad = keypad
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        kind = _lib.KIND_BLOCK_KPM if keypad else _lib.KIND_BLOCK
+        h = lib.spion_create(kind, self.d, self.L, self.BH, self.bs, _DTYPES[dtype], self.device.index or 0)
+        if not h:
+            raise _lib.SpionError("spion_create failed (unsupported shape, or no CUDA device)")
+        self.handle = _lib.c_void_p(h)
+        check(lib.spion_set_engine(self.handle, engine), "spion_set_engine")
+        self.engine = engine
+        self.nnzb = -1
+        self._mask_key = None
+        self._fn = _make_function(self)
+
+    def __del__(self):
+        h = getattr(self, "handle", None)
+        if h:
+            lib.spion_destroy(h)
+            self.handle = None
+
+    # ------------------------------------------------------------------ pattern
+    def set_mask(self, mat: torch.Tensor) -> int:
+        """Fix the layer's block mask ([nb, nb], non-zero = selected).  Called once per layer at the
+        dense->sparse switch, where the reference calls reconstruct_for_blocksparse."""
+        m8 = (mat != 0).to(torch.uint8).contiguous().to(self.device)
+        check(lib.spion_set_stream(self.handle, _lib.current_stream_ptr()))
+        check(lib.spion_set_pattern(self.handle, ptr(m8)), "spion_set_pattern")
+        self.nnzb = int(lib.spion_pattern_nnzb(self.handle))
+        self._mask_key = (mat.data_ptr(), mat._version)
+        return self.nnzb
+
+    @property
+    def nnz(self) -> int:
+        return self.nnzb * self.bs * self.bs
+
+    def launch_count(self) -> int:
+        return int(lib.spion_launch_count(self.handle))
+
+    def check_device_status(self) -> None:
+        check(lib.spion_check_device_status(self.handle), "device status")
+
+    def to_reference_order(self, P_tiles: torch.Tensor, mat: torch.Tensor) -> torch.Tensor:
+        """[BH, nnzb, bs, bs] tiles -> the reference's [BH, nnz] element-CSR order."""
+        nb = self.L // self.bs
+        m = (mat != 0).to("cpu")
+        out = []
+        t = P_tiles.reshape(self.BH, self.nnzb, self.bs, self.bs)
+        blk = 0
+        for r in range(nb):
+            n = int(m[r].sum())
+            rows = t[:, blk:blk + n]                       # [BH, n, bs, bs]
+            out.append(rows.permute(0, 2, 1, 3).reshape(self.BH, -1))
+            blk += n
+        return torch.cat(out, dim=1)
+
+    # ------------------------------------------------------------------ call
+    def forward(self, query, key, value, mask=None, mat=None):
+        if mat is not None and (mat.data_ptr(), mat._version) != self._mask_key:
+            self.set_mask(mat)
+        if self.nnzb < 0:
+            raise _lib.SpionError("no block mask set (call set_mask or pass mat)")
+        pen = None
+        if self.keypad:
+            pen = (1e6 * (1 - mask.to(torch.float32)))[:, None, :].expand(self.B, self.H, self.L).contiguous()
+        return self._fn.apply(query, key, value, pen)
+
+
+def _make_function(mod: BlockSparseAttention):
+    class NativeBlockAttnFunction(torch.autograd.Function):
+        @staticmethod
+        def forward(ctx, query, key, value, pen):
+            q = query.to(mod.dtype).contiguous()
+            k = key.to(mod.dtype).contiguous()
+            v = value.to(mod.dtype).contiguous()
+            dev = q.device
+            n = mod.BH * mod.nnz
+            P = torch.empty(n, dtype=mod.dtype, device=dev)
+            O = torch.empty_like(q)
+            scratch = torch.empty(n, dtype=torch.float32, device=dev) if mod.engine != _lib.ENGINE_TCGEN05 else None
+            check(lib.spion_set_stream(mod.handle, _lib.current_stream_ptr()))
+            check(lib.spion_attn_forward_ex(mod.handle, ptr(q), ptr(k), ptr(v), ptr(pen), ptr(P), ptr(O), ptr(scratch)),
+                  "spion_attn_forward_ex")
+            ctx.save_for_backward(q, k, v, P, O)
+            ctx.mark_non_differentiable(P)
+            return O, P
+
+        @staticmethod
+        def backward(ctx, grad_output, grad_p):
+            q, k, v, P, O = ctx.saved_tensors
+            dev = q.device
+            go = grad_output.to(mod.dtype).contiguous()
+            n = mod.BH * mod.nnz
+            dS = torch.empty(n, dtype=mod.dtype, device=dev)
+            scratch = torch.empty(n, dtype=torch.float32, device=dev) if mod.engine != _lib.ENGINE_TCGEN05 else None
+            delta = torch.empty(mod.BH * mod.L, dtype=torch.float32, device=dev)
+            dq, dk, dv = torch.empty_like(q), torch.empty_like(q), torch.empty_like(q)
+            check(lib.spion_set_stream(mod.handle, _lib.current_stream_ptr()))
+            check(lib.spion_attn_backward_ex(mod.handle, ptr(q), ptr(k), ptr(v), ptr(P), ptr(O), ptr(go), ptr(dS),
+                                             ptr(scratch), ptr(delta), ptr(dq), ptr(dk), ptr(dv)),
+                  "spion_attn_backward_ex")
+            return dq, dk, dv, None
+
+    return NativeBlockAttnFunction
