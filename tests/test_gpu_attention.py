@@ -190,8 +190,8 @@ def test_edge_masks_full_and_diagonal_only():
         O, Pd, gQ, gK, gV = oatt.sparse_attention(Q, K, V, mat, bs, None, dO)
         assert maxabs(out, O) <= FP32_TOL and maxabs(dq, gQ) <= FP32_TOL
         assert maxabs(dk, gK) <= FP32_TOL and maxabs(dv, gV) <= FP32_TOL
-    # dense mask == ordinary softmax attention: rows of P sum to one
-    assert abs(float(P.view(B * H, 64, bs, bs).float().sum() / (B * H * L)) - 1.0) < 1e-4
+        if mat.all():   # full mask == ordinary softmax attention: rows of P sum to one
+            assert abs(float(P.float().sum() / (B * H * L)) - 1.0) < 1e-4
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
