@@ -210,6 +210,23 @@ int spion_attn_backward_ex(spion_ctx* ctx, const void* Q, const void* K, const v
 int spion_softmax_forward_ex(spion_ctx* ctx, const float* S, const float* keypad, void* P);
 int spion_softmax_backward_ex(spion_ctx* ctx, const float* dP, const void* P, void* dS);
 
+/* ---------------------------------------------------------- no-allocation forward ---- */
+
+/* No counterpart in the reference.  Native forward (same math and layouts as
+ * spion_attn_forward_ex on the SIMT engine) for callers that must not allocate device memory
+ * -- a plugin inside a process whose GPU memory is fully budgeted, a real-time loop, code that
+ * runs where cudaMalloc is off limits: no context, no caller scratch.  The fp32 score scratch
+ * lives in a fixed array inside the library (spion_static_scratch_capacity() floats, 64 MiB,
+ * held by every GPU that loads the library).  num_batches*nnzb*block_size^2 beyond that is
+ * refused with SPION_ERR_SHAPE.  The array is shared by all calls on a device: calls that overlap
+ * on the GPU race.  The first call on each device looks up the array's address; make it outside
+ * stream capture.  row_ptr [nb+1], col_idx [nnzb], blk_row [nnzb]: block CSR (device). */
+size_t spion_static_scratch_capacity(void);
+int spion_attn_forward_static(const void* Q, const void* K, const void* V, const float* keypad,
+                              void* P, void* O, const int32_t* row_ptr, const int32_t* col_idx,
+                              const int32_t* blk_row, int head_dim, int seq_len, int num_batches,
+                              int block_size, int nnzb, int dtype, void* cuda_stream);
+
 #ifdef __cplusplus
 }
 #endif

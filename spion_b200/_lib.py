@@ -47,6 +47,8 @@ SIGNATURES = {
     "spion_attn_backward_ex": (c_int, [c_void_p] * 13),
     "spion_softmax_forward_ex": (c_int, [c_void_p] * 4),
     "spion_softmax_backward_ex": (c_int, [c_void_p] * 4),
+    "spion_static_scratch_capacity": (ctypes.c_size_t, []),
+    "spion_attn_forward_static": (c_int, [c_void_p] * 9 + [c_int] * 6 + [c_void_p]),
 }
 
 
