@@ -351,7 +351,7 @@ extern "C" int spion_attn_forward_ex(spion_ctx* c, const void* Q, const void* K,
   if (!c || !Q || !K || !V || !P || !O) return SPION_ERR_ARG;
   if (is_dense(c) || c->nnzb < 0) return SPION_ERR_STATE;
   DeviceGuard guard(c->device);
-  if (use_tc(c)) return tc_engine_forward(c, Q, K, V, keypad, P, O);
+  if (use_tc(c)) return tc_engine_forward(c, Q, K, V, keypad, P, O, S_scratch);
   if (!S_scratch) return SPION_ERR_ARG;
   const Pattern p = ctx_pattern(c);
   const long long nnz = (long long)c->nnzb * c->bs * c->bs;
@@ -378,8 +378,9 @@ extern "C" int spion_attn_backward_ex(spion_ctx* c, const void* Q, const void* K
   if (is_dense(c) || c->nnzb < 0) return SPION_ERR_STATE;
   DeviceGuard guard(c->device);
   if (use_tc(c)) {
-    if (!O || !delta) return SPION_ERR_ARG;
-    return tc_engine_backward(c, Q, K, V, P, O, dO, dS, delta, dQ, dK, dV);
+    if (!O) return SPION_ERR_ARG;
+    (void)delta;
+    return tc_engine_backward(c, Q, K, V, P, O, dO, dS, dP_scratch, dQ, dK, dV);
   }
   if (!dP_scratch) return SPION_ERR_ARG;
   const Pattern p = ctx_pattern(c);

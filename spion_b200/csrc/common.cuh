@@ -148,6 +148,7 @@ int softmax_bwd_dense_t(const float* dP, const float* P, float* dS, int BH, int 
 bool tc_engine_supports(const spion_ctx* c);
 int tc_engine_prepare(spion_ctx* c);       // after the pattern is set
 void tc_engine_release(spion_ctx* c);
-int tc_engine_forward(spion_ctx* c, const void* Q, const void* K, const void* V, const float* keypad, void* P, void* O);
+int tc_engine_forward(spion_ctx* c, const void* Q, const void* K, const void* V, const float* keypad, void* P, void* O,
+                      float* S_scratch);
 int tc_engine_backward(spion_ctx* c, const void* Q, const void* K, const void* V, const void* P, const void* O,
-                       const void* dO, void* dS, float* delta, void* dQ, void* dK, void* dV);
+                       const void* dO, void* dS, float* dP_scratch, void* dQ, void* dK, void* dV);

@@ -1,7 +1,611 @@
-// placeholder replaced below
+// Tensor-core engine (sm_100a): block-sparse attention on bf16 block tiles with TMA-fed
+// tcgen05.mma, accumulators in tensor memory (TMEM), fp32 softmax math in the epilogues.
+//
+// Replaces, for the native (block-tile) API, the reference's cuSPARSE calls and SIMT softmax
+// kernels (models/block_attn.cu:453-545):
+//   k_sddmm_fused<MODE 0>   S = Q K^T on the mask  + sparse row softmax  -> P      (:459, :468)
+//   k_spmm<false>           O = P V ; dQ = dS K                                      (:478, :516)
+//   k_sddmm_fused<MODE 1>   dP = dO V^T on the mask + softmax backward   -> dS      (:498, :507)
+//   k_spmm<true>            dK = dS^T Q and dV = P^T dO in one pass over a block column (:526, :536)
+//
+// Every 64x64 block of the mask is one dense contraction: M = 64 rows (MMA M = 64, accumulator
+// row m lives in TMEM lane (m % 16) + 32 * (m / 16)), N = 64 keys or the head dimension, K in
+// steps of 16.  Operands are staged by TMA with the hardware swizzle (128 B rows: SWIZZLE_128B,
+// 64 B rows: SWIZZLE_64B) and described to the MMA by shared-memory matrix descriptors; transposed
+// products need no transposed copies: P/dS tiles and Q/K/V/dO tiles are read as MN-major operands.
+// The softmax backward uses  sum_j dP_ij P_ij = sum_n dO_in O_in  (delta), so every dS tile is
+// independent of the others and no second pass over the row is needed.
+//
+// All waits on mbarriers are bounded; on a time-out the CTA records a code in the context's
+// status word, frees its TMEM and returns.
+#include <cuda.h>
+
 #include "common.cuh"
-bool tc_engine_supports(const spion_ctx*) { return false; }
-int tc_engine_prepare(spion_ctx*) { return SPION_OK; }
-void tc_engine_release(spion_ctx*) {}
-int tc_engine_forward(spion_ctx*, const void*, const void*, const void*, const float*, void*, void*) { return SPION_ERR_UNSUPPORTED; }
-int tc_engine_backward(spion_ctx*, const void*, const void*, const void*, const void*, const void*, const void*, void*, float*, void*, void*, void*) { return SPION_ERR_UNSUPPORTED; }
+#include "tc_ptx.cuh"
+
+using namespace tc;
+
+namespace {
+
+constexpr int BS = 64;                  // block size of the engine
+constexpr int VT_BYTES = BS * BS * 2;   // one bf16 value tile (P or dS)
+constexpr float LOG2E = 1.4426950408889634f;
+
+enum : int { ERR_LOAD_WAIT = 1, ERR_MMA_WAIT = 2 };
+
+__device__ __forceinline__ void report(int* status, int code) { atomicOr(status, code); }
+
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+
+template <int D> struct OpTile {
+  static constexpr int ROW_BYTES = D * 2;                        // 128 (D=64) or 64 (D=32)
+  static constexpr int BYTES = BS * ROW_BYTES;
+  static constexpr uint32_t LAYOUT = (D == 64) ? LAYOUT_SW128 : LAYOUT_SW64;
+  static constexpr uint32_t SBO = 8 * ROW_BYTES;                 // 8-row swizzle atom
+  // K-major use (contraction over the head dimension): 16 elements = 32 bytes per K step
+  __device__ static uint64_t kmajor(uint32_t saddr, int kk) { return make_smem_desc(saddr + kk * 32, 16, SBO, LAYOUT); }
+  // MN-major use (contraction over the 64 rows of the tile): 16 rows per K step
+  __device__ static uint64_t mnmajor(uint32_t saddr, int kk) {
+    return make_smem_desc(saddr + kk * 16 * ROW_BYTES, BYTES, SBO, LAYOUT);
+  }
+};
+// bf16 value tile [64 x 64], 128-byte rows, SWIZZLE_128B
+struct ValTile {
+  __device__ static uint64_t kmajor(uint32_t saddr, int kk) { return make_smem_desc(saddr + kk * 32, 16, 1024, LAYOUT_SW128); }
+  __device__ static uint64_t mnmajor(uint32_t saddr, int kk) {
+    return make_smem_desc(saddr + kk * 2048, VT_BYTES, 1024, LAYOUT_SW128);
+  }
+};
+
+// =====================================================================================
+// S (or dP) tiles of one block row + fused epilogue.  One CTA per (block row, bh), 128 threads.
+//   MODE 0: P  = softmax row-wise over the selected blocks (reference semantics: the L - n_i
+//                non-selected keys add exp(0 - m) each to the denominator)
+//   MODE 1: dS = P * (dP - delta) * scale,  delta_i = sum_n dO_in O_in
+// NCH tiles (64 TMEM columns each) are produced per chunk.
+template <int D, int MODE, int NCH>
+__global__ void __launch_bounds__(128) k_sddmm_fused(const __grid_constant__ CUtensorMap tmA,
+                                                     const __grid_constant__ CUtensorMap tmB,
+                                                     __nv_bfloat16* __restrict__ out,
+                                                     const __nv_bfloat16* __restrict__ Pin,
+                                                     const __nv_bfloat16* __restrict__ dOg,
+                                                     const __nv_bfloat16* __restrict__ Og,
+                                                     const float* __restrict__ keypad,
+                                                     const int* __restrict__ row_ptr, const int* __restrict__ col_idx,
+                                                     int L, int nnzb, float scale, float floor_v, int* status) {
+  using T = OpTile<D>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t sA = sbase;
+  const uint32_t sB = sbase + T::BYTES;
+  const uint32_t bar_load = sB + NCH * T::BYTES;
+  const uint32_t bar_mma = bar_load + 8;
+  const uint32_t slot = bar_mma + 8;
+  uint32_t* slot_ptr = reinterpret_cast<uint32_t*>(smem_raw + (slot - smem_u32(smem_raw)));
+
+  const int r = blockIdx.x, bh = blockIdx.y;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  constexpr uint32_t TMEM_COLS = NCH * 64 < 32 ? 32 : NCH * 64;
+  __shared__ int s_abort;                                         // an earlier CTA gave up: do not pile on
+  if (tid == 0) s_abort = *reinterpret_cast<volatile int*>(status);
+  __syncthreads();
+  if (s_abort != 0) return;
+
+  if (warp == 0) {
+    tmem_alloc(slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  if (tid == 0) {
+    mbar_init(bar_load, 1);
+    mbar_init(bar_mma, 1);
+    fence_barrier_init();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *slot_ptr;
+
+  const int rp = row_ptr[r];
+  const int nblk = row_ptr[r + 1] - rp;
+  const int nchunks = (nblk + NCH - 1) / NCH;
+  const bool active = lane < 16;
+  const int row = warp * 16 + (lane & 15);                       // accumulator row held by this thread
+  const uint32_t tlane = tmem + ((uint32_t)(warp * 32) << 16);
+  constexpr uint32_t IDESC = make_idesc_bf16(64, 64, 0, 0);
+  uint32_t ph_load = 0, ph_mma = 0;
+  bool ok = true;
+  bool a_loaded = false;
+
+  // produce the S tiles of chunk ch into TMEM
+  auto produce = [&](int ch) -> bool {
+    const int t0 = ch * NCH;
+    const int nt = min(NCH, nblk - t0);
+    if (tid == 0) {
+      mbar_expect_tx(bar_load, (a_loaded ? 0 : T::BYTES) + nt * T::BYTES);
+      if (!a_loaded) tma_load_2d(sA, &tmA, bar_load, 0, bh * L + r * BS);
+      for (int t = 0; t < nt; ++t) tma_load_2d(sB + t * T::BYTES, &tmB, bar_load, 0, bh * L + col_idx[rp + t0 + t] * BS);
+    }
+    a_loaded = true;
+    if (!__syncthreads_and(mbar_wait(bar_load, ph_load))) { if (tid == 0) report(status, ERR_LOAD_WAIT); return false; }
+    ph_load ^= 1;
+    if (tid == 0) {
+      tc_fence_after();
+      for (int t = 0; t < nt; ++t) {
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          mma_bf16(tmem + t * 64, T::kmajor(sA, kk), T::kmajor(sB + t * T::BYTES, kk), IDESC, kk > 0);
+      }
+      mma_commit(bar_mma);
+    }
+    if (!__syncthreads_and(mbar_wait(bar_mma, ph_mma))) { if (tid == 0) report(status, ERR_MMA_WAIT); return false; }
+    ph_mma ^= 1;
+    tc_fence_after();
+    return true;
+  };
+  // all threads are done reading TMEM / smem of the current chunk
+  auto release = [&]() {
+    tc_fence_before();
+    __syncthreads();
+  };
+
+  if (MODE == 0) {
+    const float sc2 = scale * LOG2E;
+    const float* kp = keypad ? keypad + (size_t)bh * L : nullptr;
+    float m2 = floor_v * LOG2E, l = 0.f;
+    // ---- pass 1: row maximum and denominator
+    for (int ch = 0; ch < nchunks && ok; ++ch) {
+      ok = produce(ch);
+      if (!ok) break;
+      const int t0 = ch * NCH, nt = min(NCH, nblk - t0);
+      float cm = m2;
+      for (int t = 0; t < nt; ++t) {
+        const int c = col_idx[rp + t0 + t];
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t v[32];
+          tmem_ld32(tlane + t * 64 + half * 32, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            float x = __uint_as_float(v[j]) * sc2;
+            if (kp) x -= kp[c * BS + half * 32 + j] * LOG2E;
+            cm = fmaxf(cm, x);
+          }
+        }
+      }
+      l *= exp2f(m2 - cm);
+      m2 = cm;
+      for (int t = 0; t < nt; ++t) {
+        const int c = col_idx[rp + t0 + t];
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t v[32];
+          tmem_ld32(tlane + t * 64 + half * 32, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            float x = __uint_as_float(v[j]) * sc2;
+            if (kp) x -= kp[c * BS + half * 32 + j] * LOG2E;
+            l += exp2f(x - m2);
+          }
+        }
+      }
+      if (nchunks > 1) release();
+    }
+    l += (float)(L - nblk * BS) * exp2f(-m2);
+    const float inv = 1.0f / l;
+    // ---- pass 2: write P (TMEM still holds the tiles when the row fits in one chunk)
+    for (int ch = 0; ch < nchunks && ok; ++ch) {
+      if (nchunks > 1) { ok = produce(ch); if (!ok) break; }
+      const int t0 = ch * NCH, nt = min(NCH, nblk - t0);
+      for (int t = 0; t < nt; ++t) {
+        const int blk = rp + t0 + t, c = col_idx[blk];
+        __nv_bfloat16* dst = out + (((size_t)bh * nnzb + blk) * BS + row) * BS;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t v[32];
+          tmem_ld32(tlane + t * 64 + half * 32, v);
+          tmem_ld_wait();
+          uint32_t w[16];
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) {
+            float x0 = __uint_as_float(v[j]) * sc2, x1 = __uint_as_float(v[j + 1]) * sc2;
+            if (kp) { x0 -= kp[c * BS + half * 32 + j] * LOG2E; x1 -= kp[c * BS + half * 32 + j + 1] * LOG2E; }
+            w[j >> 1] = pack_bf16(exp2f(x0 - m2) * inv, exp2f(x1 - m2) * inv);
+          }
+          if (active) {
+            uint4* d4 = reinterpret_cast<uint4*>(dst + half * 32);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) d4[q] = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
+          }
+        }
+      }
+      if (nchunks > 1) release();
+    }
+  } else {
+    // delta of this thread's row
+    float delta = 0.f;
+    if (active) {
+      const uint4* a4 = reinterpret_cast<const uint4*>(dOg + ((size_t)bh * L + r * BS + row) * D);
+      const uint4* b4 = reinterpret_cast<const uint4*>(Og + ((size_t)bh * L + r * BS + row) * D);
+#pragma unroll
+      for (int q = 0; q < D / 8; ++q) {
+        const uint4 a = a4[q], b = b4[q];
+        delta += bf16_lo(a.x) * bf16_lo(b.x) + bf16_hi(a.x) * bf16_hi(b.x) + bf16_lo(a.y) * bf16_lo(b.y) +
+                 bf16_hi(a.y) * bf16_hi(b.y) + bf16_lo(a.z) * bf16_lo(b.z) + bf16_hi(a.z) * bf16_hi(b.z) +
+                 bf16_lo(a.w) * bf16_lo(b.w) + bf16_hi(a.w) * bf16_hi(b.w);
+      }
+    }
+    for (int ch = 0; ch < nchunks && ok; ++ch) {
+      ok = produce(ch);
+      if (!ok) break;
+      const int t0 = ch * NCH, nt = min(NCH, nblk - t0);
+      for (int t = 0; t < nt; ++t) {
+        const int blk = rp + t0 + t;
+        const size_t off = (((size_t)bh * nnzb + blk) * BS + row) * BS;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t v[32];
+          tmem_ld32(tlane + t * 64 + half * 32, v);
+          tmem_ld_wait();
+          if (active) {
+            const uint4* p4 = reinterpret_cast<const uint4*>(Pin + off + half * 32);
+            uint4* d4 = reinterpret_cast<uint4*>(out + off + half * 32);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const uint4 pw = p4[q];
+              const uint32_t pws[4] = {pw.x, pw.y, pw.z, pw.w};
+              uint32_t o[4];
+#pragma unroll
+              for (int u = 0; u < 4; ++u) {
+                const float p0 = bf16_lo(pws[u]), p1 = bf16_hi(pws[u]);
+                const float g0 = __uint_as_float(v[q * 8 + 2 * u]), g1 = __uint_as_float(v[q * 8 + 2 * u + 1]);
+                o[u] = pack_bf16(p0 * (g0 - delta) * scale, p1 * (g1 - delta) * scale);
+              }
+              d4[q] = make_uint4(o[0], o[1], o[2], o[3]);
+            }
+          }
+        }
+      }
+      release();
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, TMEM_COLS);
+}
+
+// =====================================================================================
+// Block SpMM.  128 threads, one CTA per (line, bh); NST value/operand tile pairs per chunk.
+//   DUAL == false: line = block row r.   out0[r*64.., :] = sum_k  vals0(r, c_k)   * B0[c_k*64.., :]
+//   DUAL == true : line = block column c.
+//                  out0[c*64.., :] = sum_r vals0(r, c)^T * B0[r*64.., :]      (dK = dS^T Q)
+//                  out1[c*64.., :] = sum_r vals1(r, c)^T * B1[r*64.., :]      (dV = P^T dO)
+template <int D, bool DUAL, int NST>
+__global__ void __launch_bounds__(128) k_spmm(const __grid_constant__ CUtensorMap tmV0,
+                                              const __grid_constant__ CUtensorMap tmV1,
+                                              const __grid_constant__ CUtensorMap tmB0,
+                                              const __grid_constant__ CUtensorMap tmB1,
+                                              __nv_bfloat16* __restrict__ out0, __nv_bfloat16* __restrict__ out1,
+                                              const int* __restrict__ line_ptr, const int* __restrict__ idx,
+                                              const int* __restrict__ pos, int L, int nnzb, int* status) {
+  using T = OpTile<D>;
+  constexpr int NP = DUAL ? 2 : 1;                                // products per entry
+  constexpr int STAGE_BYTES = NP * (VT_BYTES + T::BYTES);
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bar_load = sbase + NST * STAGE_BYTES;
+  const uint32_t bar_mma = bar_load + 8;
+  const uint32_t slot = bar_mma + 8;
+  uint32_t* slot_ptr = reinterpret_cast<uint32_t*>(smem_raw + (slot - smem_u32(smem_raw)));
+
+  const int line = blockIdx.x, bh = blockIdx.y;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  constexpr uint32_t TMEM_COLS = (NP * D) < 32 ? 32 : (NP * D);   // 32, 64 or 128: powers of two
+  __shared__ int s_abort;                                         // an earlier CTA gave up: do not pile on
+  if (tid == 0) s_abort = *reinterpret_cast<volatile int*>(status);
+  __syncthreads();
+  if (s_abort != 0) return;
+
+  if (warp == 0) {
+    tmem_alloc(slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  if (tid == 0) {
+    mbar_init(bar_load, 1);
+    mbar_init(bar_mma, 1);
+    fence_barrier_init();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *slot_ptr;
+
+  const int beg = line_ptr[line], end = line_ptr[line + 1];
+  constexpr uint32_t IDESC = make_idesc_bf16(64, D, DUAL ? 1 : 0, 1);
+  uint32_t ph_load = 0, ph_mma = 0;
+  bool ok = true;
+
+  for (int e0 = beg; e0 < end && ok; e0 += NST) {
+    const int nt = min(NST, end - e0);
+    if (tid == 0) {
+      mbar_expect_tx(bar_load, nt * STAGE_BYTES);
+      for (int t = 0; t < nt; ++t) {
+        const int e = e0 + t;
+        const int other = idx[e];                                  // block column (CSR) or block row (CSC)
+        const int blk = DUAL ? pos[e] : e;                         // CSR block id of the value tile
+        const uint32_t st = sbase + t * STAGE_BYTES;
+        const int vrow = (int)(((size_t)bh * nnzb + blk) * BS);
+        tma_load_2d(st, &tmV0, bar_load, 0, vrow);
+        tma_load_2d(st + VT_BYTES, &tmB0, bar_load, 0, bh * L + other * BS);
+        if (DUAL) {
+          tma_load_2d(st + VT_BYTES + T::BYTES, &tmV1, bar_load, 0, vrow);
+          tma_load_2d(st + 2 * VT_BYTES + T::BYTES, &tmB1, bar_load, 0, bh * L + other * BS);
+        }
+      }
+    }
+    if (!__syncthreads_and(mbar_wait(bar_load, ph_load))) { if (tid == 0) report(status, ERR_LOAD_WAIT); ok = false; break; }
+    ph_load ^= 1;
+    if (tid == 0) {
+      tc_fence_after();
+      for (int t = 0; t < nt; ++t) {
+        const uint32_t st = sbase + t * STAGE_BYTES;
+        const uint32_t first = (e0 == beg && t == 0) ? 0u : 1u;
+#pragma unroll
+        for (int kk = 0; kk < BS / 16; ++kk) {
+          const uint64_t a0 = DUAL ? ValTile::mnmajor(st, kk) : ValTile::kmajor(st, kk);
+          mma_bf16(tmem, a0, T::mnmajor(st + VT_BYTES, kk), IDESC, (kk > 0) ? 1u : first);
+        }
+        if (DUAL) {
+#pragma unroll
+          for (int kk = 0; kk < BS / 16; ++kk)
+            mma_bf16(tmem + D, ValTile::mnmajor(st + VT_BYTES + T::BYTES, kk),
+                     T::mnmajor(st + 2 * VT_BYTES + T::BYTES, kk), IDESC, (kk > 0) ? 1u : first);
+        }
+      }
+      mma_commit(bar_mma);
+    }
+    if (!__syncthreads_and(mbar_wait(bar_mma, ph_mma))) { if (tid == 0) report(status, ERR_MMA_WAIT); ok = false; break; }
+    ph_mma ^= 1;
+    tc_fence_after();
+  }
+
+  // epilogue: TMEM -> bf16 rows of the output(s)
+  const bool active = lane < 16;
+  const int row = warp * 16 + (lane & 15);
+  const uint32_t tlane = tmem + ((uint32_t)(warp * 32) << 16);
+  if (ok) {
+#pragma unroll
+    for (int pi = 0; pi < NP; ++pi) {
+      __nv_bfloat16* dst = (pi == 0 ? out0 : out1) + ((size_t)bh * L + (size_t)line * BS + row) * D;
+#pragma unroll
+      for (int h = 0; h < D / 32; ++h) {
+        uint32_t v[32];
+        if (end > beg) {
+          tmem_ld32(tlane + pi * D + h * 32, v);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = 0u;
+        }
+        if (active) {
+          uint4* d4 = reinterpret_cast<uint4*>(dst + h * 32);
+#pragma unroll
+          for (int q = 0; q < 4; ++q)
+            d4[q] = make_uint4(pack_bf16(__uint_as_float(v[8 * q]), __uint_as_float(v[8 * q + 1])),
+                               pack_bf16(__uint_as_float(v[8 * q + 2]), __uint_as_float(v[8 * q + 3])),
+                               pack_bf16(__uint_as_float(v[8 * q + 4]), __uint_as_float(v[8 * q + 5])),
+                               pack_bf16(__uint_as_float(v[8 * q + 6]), __uint_as_float(v[8 * q + 7])));
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, TMEM_COLS);
+}
+
+// =====================================================================================
+// host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+struct TcState {
+  EncodeTiledFn encode = nullptr;
+  int stages = 0x1f;            // bit0 S->P, bit1 O, bit2 dP->dS, bit3 dQ, bit4 dK+dV
+  bool attr_done = false;
+};
+
+constexpr int NCH_FWD = 4, NCH_BWD = 4, NST_N = 4, NST_T = 2;
+
+template <int D> constexpr size_t smem_sddmm(int nch) { return 1024 + (size_t)(1 + nch) * OpTile<D>::BYTES + 64; }
+template <int D> constexpr size_t smem_spmm(int nst, int np) { return 1024 + (size_t)nst * np * (VT_BYTES + OpTile<D>::BYTES) + 64; }
+
+int make_map(TcState* s, CUtensorMap* m, const void* base, uint64_t rows, uint32_t cols, uint32_t box_rows) {
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+  const cuuint32_t box[2] = {cols, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUtensorMapSwizzle sw = (cols * 2 == 128) ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+  CUresult r = s->encode(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    fprintf(stderr, "spion_b200: cuTensorMapEncodeTiled failed (%d) rows=%llu cols=%u\n", (int)r,
+            (unsigned long long)rows, cols);
+    return SPION_ERR_CUDA;
+  }
+  return SPION_OK;
+}
+
+template <int D>
+int set_attrs() {
+  SPION_CUDA_TRY(cudaFuncSetAttribute(k_sddmm_fused<D, 0, NCH_FWD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      (int)smem_sddmm<D>(NCH_FWD)));
+  SPION_CUDA_TRY(cudaFuncSetAttribute(k_sddmm_fused<D, 1, NCH_BWD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      (int)smem_sddmm<D>(NCH_BWD)));
+  SPION_CUDA_TRY(cudaFuncSetAttribute(k_spmm<D, false, NST_N>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      (int)smem_spmm<D>(NST_N, 1)));
+  SPION_CUDA_TRY(cudaFuncSetAttribute(k_spmm<D, true, NST_T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      (int)smem_spmm<D>(NST_T, 2)));
+  return SPION_OK;
+}
+
+template <int D>
+int run_forward(spion_ctx* c, TcState* s, const void* Q, const void* K, const void* V, const float* keypad, void* P,
+                void* O, float* S_scratch) {
+  const Pattern p = ctx_pattern(c);
+  const uint64_t rows = (uint64_t)c->BH * c->L, vrows = (uint64_t)c->BH * c->nnzb * BS;
+  const long long nnz = (long long)c->nnzb * BS * BS;
+  const ValueLayout vl{VAL_BLOCKTILE, c->L, nnz};
+  const OperandLayout rm = row_major_operand(c->L, c->d);
+  const dim3 grid(c->nb, c->BH);
+  int rc;
+  prof_mark(c, -1);
+  if (s->stages & 1) {
+    CUtensorMap mq, mk;
+    if ((rc = make_map(s, &mq, Q, rows, D, BS)) || (rc = make_map(s, &mk, K, rows, D, BS))) return rc;
+    k_sddmm_fused<D, 0, NCH_FWD><<<grid, 128, smem_sddmm<D>(NCH_FWD), c->stream>>>(
+        mq, mk, (__nv_bfloat16*)P, nullptr, nullptr, nullptr, keypad, c->row_ptr, c->col_idx, c->L, c->nnzb, c->scale,
+        keypad ? 0.0f : -100.0f, c->status_dev);
+    SPION_LAUNCH_CHECK();
+    c->launches += 1;
+    prof_mark(c, SPION_STAGE_FUSED_S_P);
+  } else {
+    if (!S_scratch) return SPION_ERR_ARG;
+    if ((rc = simt_sddmm(SPION_BF16, SPION_F32, Q, rm, K, rm, S_scratch, vl, p, c->nnzb, c->BH, c->d, c->stream))) return rc;
+    prof_mark(c, SPION_STAGE_SDDMM_S);
+    if ((rc = softmax_fwd_rows(SPION_BF16, S_scratch, vl, P, vl, p, c->BH, c->L, c->scale, keypad,
+                               keypad ? 0.0f : -100.0f, c->stream))) return rc;
+    prof_mark(c, SPION_STAGE_SOFTMAX_FWD);
+    c->launches += 2;
+  }
+  if (s->stages & 2) {
+    CUtensorMap mp, mv;
+    if ((rc = make_map(s, &mp, P, vrows, BS, BS)) || (rc = make_map(s, &mv, V, rows, D, BS))) return rc;
+    k_spmm<D, false, NST_N><<<grid, 128, smem_spmm<D>(NST_N, 1), c->stream>>>(
+        mp, mp, mv, mv, (__nv_bfloat16*)O, nullptr, c->row_ptr, c->col_idx, nullptr, c->L, c->nnzb, c->status_dev);
+    SPION_LAUNCH_CHECK();
+  } else {
+    if ((rc = simt_spmm(SPION_BF16, SPION_BF16, false, P, vl, V, rm, O, rm, p, c->BH, c->d, c->stream))) return rc;
+  }
+  c->launches += 1;
+  prof_mark(c, SPION_STAGE_SPMM_O);
+  return SPION_OK;
+}
+
+template <int D>
+int run_backward(spion_ctx* c, TcState* s, const void* Q, const void* K, const void* V, const void* P, const void* O,
+                 const void* dO, void* dS, float* dP_scratch, void* dQ, void* dK, void* dV) {
+  const Pattern p = ctx_pattern(c);
+  const uint64_t rows = (uint64_t)c->BH * c->L, vrows = (uint64_t)c->BH * c->nnzb * BS;
+  const long long nnz = (long long)c->nnzb * BS * BS;
+  const ValueLayout vl{VAL_BLOCKTILE, c->L, nnz};
+  const OperandLayout rm = row_major_operand(c->L, c->d);
+  const dim3 grid(c->nb, c->BH);
+  int rc;
+  prof_mark(c, -1);
+  if (s->stages & 4) {
+    CUtensorMap mdo, mv;
+    if ((rc = make_map(s, &mdo, dO, rows, D, BS)) || (rc = make_map(s, &mv, V, rows, D, BS))) return rc;
+    k_sddmm_fused<D, 1, NCH_BWD><<<grid, 128, smem_sddmm<D>(NCH_BWD), c->stream>>>(
+        mdo, mv, (__nv_bfloat16*)dS, (const __nv_bfloat16*)P, (const __nv_bfloat16*)dO, (const __nv_bfloat16*)O,
+        nullptr, c->row_ptr, c->col_idx, c->L, c->nnzb, c->scale, 0.f, c->status_dev);
+    SPION_LAUNCH_CHECK();
+    c->launches += 1;
+    prof_mark(c, SPION_STAGE_FUSED_DP_DS);
+  } else {
+    if (!dP_scratch) return SPION_ERR_ARG;
+    if ((rc = simt_sddmm(SPION_BF16, SPION_F32, dO, rm, V, rm, dP_scratch, vl, p, c->nnzb, c->BH, c->d, c->stream))) return rc;
+    prof_mark(c, SPION_STAGE_SDDMM_DP);
+    if ((rc = softmax_bwd_rows(SPION_BF16, dP_scratch, vl, P, vl, dS, vl, p, c->BH, c->L, c->scale, c->stream))) return rc;
+    prof_mark(c, SPION_STAGE_SOFTMAX_BWD);
+    c->launches += 2;
+  }
+  CUtensorMap mds, mp, mq, mk, mdo;
+  if ((rc = make_map(s, &mds, dS, vrows, BS, BS)) || (rc = make_map(s, &mp, P, vrows, BS, BS)) ||
+      (rc = make_map(s, &mq, Q, rows, D, BS)) || (rc = make_map(s, &mk, K, rows, D, BS)) ||
+      (rc = make_map(s, &mdo, dO, rows, D, BS)))
+    return rc;
+  if (s->stages & 8) {
+    k_spmm<D, false, NST_N><<<grid, 128, smem_spmm<D>(NST_N, 1), c->stream>>>(
+        mds, mds, mk, mk, (__nv_bfloat16*)dQ, nullptr, c->row_ptr, c->col_idx, nullptr, c->L, c->nnzb, c->status_dev);
+    SPION_LAUNCH_CHECK();
+  } else {
+    if ((rc = simt_spmm(SPION_BF16, SPION_BF16, false, dS, vl, K, rm, dQ, rm, p, c->BH, c->d, c->stream))) return rc;
+  }
+  c->launches += 1;
+  prof_mark(c, SPION_STAGE_SPMM_DQ);
+  if (s->stages & 16) {
+    k_spmm<D, true, NST_T><<<grid, 128, smem_spmm<D>(NST_T, 2), c->stream>>>(
+        mds, mp, mq, mdo, (__nv_bfloat16*)dK, (__nv_bfloat16*)dV, c->col_ptr, c->row_idx, c->csc_pos, c->L, c->nnzb,
+        c->status_dev);
+    SPION_LAUNCH_CHECK();
+    c->launches += 1;
+    prof_mark(c, SPION_STAGE_SPMM_DKDV);
+  } else {
+    if ((rc = simt_spmm(SPION_BF16, SPION_BF16, true, dS, vl, Q, rm, dK, rm, p, c->BH, c->d, c->stream))) return rc;
+    prof_mark(c, SPION_STAGE_SPMM_DK);
+    if ((rc = simt_spmm(SPION_BF16, SPION_BF16, true, P, vl, dO, rm, dV, rm, p, c->BH, c->d, c->stream))) return rc;
+    prof_mark(c, SPION_STAGE_SPMM_DV);
+    c->launches += 2;
+  }
+  return SPION_OK;
+}
+
+}  // namespace
+
+bool tc_engine_supports(const spion_ctx* c) {
+  return c->dtype == SPION_BF16 && c->bs == BS && (c->d == 64 || c->d == 32) &&
+         (c->kind == SPION_KIND_BLOCK || c->kind == SPION_KIND_BLOCK_KPM) && c->BH <= 65535 &&
+         (unsigned long long)c->BH * c->L < 0x7fffffffULL;
+}
+
+int tc_engine_prepare(spion_ctx* c) {
+  if (c->tc) return SPION_OK;
+  TcState* s = new TcState();
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+  if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || !fn) {
+    fprintf(stderr, "spion_b200: cuTensorMapEncodeTiled is not available from this driver\n");
+    delete s;
+    return SPION_ERR_CUDA;
+  }
+  s->encode = (EncodeTiledFn)fn;
+  const char* env = getenv("SPION_TC_STAGES");
+  if (env) s->stages = atoi(env) & 0x1f;
+  int rc = (c->d == 64) ? set_attrs<64>() : set_attrs<32>();
+  if (rc) { delete s; return rc; }
+  c->tc = s;
+  return SPION_OK;
+}
+
+void tc_engine_release(spion_ctx* c) {
+  if (c->tc) { delete (TcState*)c->tc; c->tc = nullptr; }
+}
+
+int tc_engine_forward(spion_ctx* c, const void* Q, const void* K, const void* V, const float* keypad, void* P, void* O,
+                      float* S_scratch) {
+  if (!c->tc) return SPION_ERR_STATE;
+  TcState* s = (TcState*)c->tc;
+  if (c->nnzb == 0) return SPION_ERR_SHAPE;
+  return c->d == 64 ? run_forward<64>(c, s, Q, K, V, keypad, P, O, S_scratch)
+                    : run_forward<32>(c, s, Q, K, V, keypad, P, O, S_scratch);
+}
+
+int tc_engine_backward(spion_ctx* c, const void* Q, const void* K, const void* V, const void* P, const void* O,
+                       const void* dO, void* dS, float* dP_scratch, void* dQ, void* dK, void* dV) {
+  if (!c->tc) return SPION_ERR_STATE;
+  TcState* s = (TcState*)c->tc;
+  if (c->nnzb == 0) return SPION_ERR_SHAPE;
+  return c->d == 64 ? run_backward<64>(c, s, Q, K, V, P, O, dO, dS, dP_scratch, dQ, dK, dV)
+                    : run_backward<32>(c, s, Q, K, V, P, O, dO, dS, dP_scratch, dQ, dK, dV);
+}
