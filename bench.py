@@ -69,7 +69,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.idx), f"--query-gpu={self.Q}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "50"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.t = threading.Thread(target=self._read, daemon=True)
             self.t.start()
@@ -171,12 +171,13 @@ def run_reference(args, rank):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=500)
+    ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="sweep_L4096_bs64_d05", choices=sorted(WORKLOADS))
     ap.add_argument("--engine", default="auto", choices=["auto", "simt", "tcgen05"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-clocks", action="store_true", help="do not sample nvidia-smi (profiler runs)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -240,13 +241,19 @@ def main():
         return float(t.item())
 
     # ---------------- value: inputs resident in HBM, C ABI -------------------------------------
+    sampler = ClockSampler(local_rank)
+    if rank == 0 and not args.no_clocks:
+        sampler.start()
     for _ in range(args.warmup):
         step_device()
     mod.check_device_status()
-    sampler = ClockSampler(local_rank)
+    # keep the GPU under the same load until nvidia-smi has produced a few samples
+    t_load = time.perf_counter()
+    while rank == 0 and sampler.proc and len(sampler.lines) < 4 and time.perf_counter() - t_load < 3.0:
+        for _ in range(20):
+            step_device()
+        torch.cuda.synchronize()
     barrier()
-    if rank == 0:
-        sampler.start()
     l0 = mod.launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
