@@ -115,7 +115,7 @@ def algorithmic(B, H, L, d, bs, nnzb, esz):
 
 
 # per-launch algorithmic bytes of each stage (p = bytes of a stored P/dS element, 4 for fp32 scratch)
-def stage_bytes(stage, BH, L, d, nnz, esz, psz):
+def stage_bytes(stage, BH, L, d, nnz, esz, psz, p_stored=False):
     ld = BH * L * d * esz
     v = BH * nnz
     return {
@@ -124,14 +124,21 @@ def stage_bytes(stage, BH, L, d, nnz, esz, psz):
         "spmm_dk": psz * v + 2 * ld, "spmm_dv": psz * v + 2 * ld,
         "fused_s_p": 2 * ld + psz * v, "fused_dp_ds": 2 * ld + 2 * psz * v + 4 * BH * L,
         "delta": 2 * ld + 4 * BH * L, "spmm_dkdv": 2 * psz * v + 4 * ld, "structure": 0,
+        # fused kernels: operands once, no S/P/dP/dS (P written only when the staged backward needs it)
+        "fused_fwd": 4 * ld + 4 * BH * L + (psz * v if p_stored else 0),
+        "fused_bwd_row": 6 * ld + 8 * BH * L, "fused_bwd_col": 6 * ld + 8 * BH * L,
     }[stage]
 
 
 def stage_flops(stage, BH, d, nnz):
     if stage in ("sddmm_s", "spmm_o", "sddmm_dp", "spmm_dq", "spmm_dk", "spmm_dv", "fused_s_p", "fused_dp_ds"):
         return 2.0 * nnz * d * BH
-    if stage == "spmm_dkdv":
+    if stage in ("spmm_dkdv", "fused_fwd"):
         return 4.0 * nnz * d * BH
+    if stage == "fused_bwd_row":
+        return 6.0 * nnz * d * BH
+    if stage == "fused_bwd_col":
+        return 8.0 * nnz * d * BH
     return 0.0
 
 
@@ -176,6 +183,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="sweep_L4096_bs64_d05", choices=sorted(WORKLOADS))
     ap.add_argument("--engine", default="auto", choices=["auto", "simt", "tcgen05"])
+    ap.add_argument("--mode", default="auto", choices=["auto", "fused", "staged"],
+                    help="fused: S/P/dP/dS stay on chip (tcgen05 engine); staged: one kernel per stage")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-clocks", action="store_true", help="do not sample nvidia-smi (profiler runs)")
     args = ap.parse_args()
@@ -207,7 +216,11 @@ def main():
     cfg = {"head_dim": d, "num_head": H, "max_seq_len": L, "batch_size": B, "block_size": bs,
            "transformer_dim": H * d, "task": "sweep"}
     engine = {"auto": _lib.ENGINE_AUTO, "simt": _lib.ENGINE_SIMT, "tcgen05": _lib.ENGINE_TCGEN05}[args.engine]
-    mod = BlockSparseAttention(cfg, dtype=tdt, engine=engine, device=dev)
+    mod = BlockSparseAttention(cfg, dtype=tdt, engine=engine, device=dev,
+                               fused=None if args.mode == "auto" else (args.mode == "fused"), return_attn=False)
+    from spion_b200 import native as _native
+    fused_fwd = mod.fused
+    fused_bwd = mod.fused and _native.FUSED_BACKWARD
     mat = synthetic.band_random_mask(2024, nb, dens)          # same mask on every rank (one layer)
     nnzb = mod.set_mask(torch.as_tensor(mat).to(dev))
     flops, fused_bytes, nnz = algorithmic(B, H, L, d, bs, nnzb, esz)
@@ -222,10 +235,20 @@ def main():
     delta = torch.empty(BH * L, dtype=torch.float32, device=dev)
     check(lib.spion_set_stream(mod.handle, _lib.current_stream_ptr()))
 
+    lse = torch.empty(BH * L, dtype=torch.float32, device=dev)
+
     def step_device():
-        check(lib.spion_attn_forward_ex(mod.handle, ptr(Q), ptr(K), ptr(V), None, ptr(P), ptr(O), ptr(scr)))
-        check(lib.spion_attn_backward_ex(mod.handle, ptr(Q), ptr(K), ptr(V), ptr(P), ptr(O), ptr(dO), ptr(dS),
-                                         ptr(scr), ptr(delta), ptr(dQ), ptr(dK), ptr(dV)))
+        if fused_fwd:
+            check(lib.spion_attn_forward_fused(mod.handle, ptr(Q), ptr(K), ptr(V), None, ptr(O), ptr(lse),
+                                               None if fused_bwd else ptr(P)))
+        else:
+            check(lib.spion_attn_forward_ex(mod.handle, ptr(Q), ptr(K), ptr(V), None, ptr(P), ptr(O), ptr(scr)))
+        if fused_bwd:
+            check(lib.spion_attn_backward_fused(mod.handle, ptr(Q), ptr(K), ptr(V), None, ptr(O), ptr(lse), ptr(dO),
+                                                ptr(delta), ptr(dQ), ptr(dK), ptr(dV)))
+        else:
+            check(lib.spion_attn_backward_ex(mod.handle, ptr(Q), ptr(K), ptr(V), ptr(P), ptr(O), ptr(dO), ptr(dS),
+                                             ptr(scr), ptr(delta), ptr(dQ), ptr(dK), ptr(dV)))
 
     def barrier():
         torch.cuda.synchronize()
@@ -282,12 +305,12 @@ def main():
     psz = esz
     kern = {}
     for name, ms in stages.items():
-        by = stage_bytes(name, BH, L, d, nnz, esz, psz)
+        by = stage_bytes(name, BH, L, d, nnz, esz, psz, p_stored=not fused_bwd)
         fl = stage_flops(name, BH, d, nnz)
         kern[name] = {"ms": ms, "GBps": by / (ms * 1e-3) / 1e9 if ms > 0 else None,
                       "TFLOPs": fl / (ms * 1e-3) / 1e12 if ms > 0 else None}
     dom = max((k for k in stages if k != "structure"), key=lambda k: stages[k])
-    dom_bytes = stage_bytes(dom, BH, L, d, nnz, esz, psz)
+    dom_bytes = stage_bytes(dom, BH, L, d, nnz, esz, psz, p_stored=not fused_bwd)
     achieved = dom_bytes / (stages[dom] * 1e-3) / 1e9
     roofline = {"kernel": dom, "bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                 "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
@@ -350,6 +373,7 @@ def main():
             "dtype": "bf16" if dt == "bf16" else "f32", "data": "synthetic",
             "config": {"workload": args.workload, "B_per_gpu": B, "H": H, "L": L, "d_head": d, "block": bs,
                        "density": nnzb / float(nb * nb), "nnzb": nnzb, "engine": args.engine,
+                       "mode": ("fused" if fused_bwd else "fused-forward+staged-backward") if fused_fwd else "staged",
                        "l2_policy": "inputs larger than L2 (Q,K,V,dO = %.0f MB, P+dS = %.0f MB per step)"
                                     % (4 * hQ.numel() * esz / 1e6, 2 * n * esz / 1e6)},
             "roofline": roofline, "kernels": kern,

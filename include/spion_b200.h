@@ -72,6 +72,10 @@ int spion_set_engine(spion_ctx* ctx, int engine);
  * bounded wait inside a kernel gave up; the word is cleared. */
 int spion_check_device_status(spion_ctx* ctx);
 
+/* Debugging aid: the fused kernels write 8 nanosecond timestamps (%globaltimer) per CTA, at their
+ * phase boundaries, into this device buffer (8 * grid size uint64; NULL switches it off). */
+int spion_set_trace_buffer(spion_ctx* ctx, void* device_buffer);
+
 /* Number of kernels this context has launched since creation (bench bookkeeping). */
 long long spion_launch_count(const spion_ctx* ctx);
 
@@ -94,7 +98,10 @@ enum {
   SPION_STAGE_FUSED_DP_DS = 10,/* tcgen05: dP tiles + softmax backward -> dS       */
   SPION_STAGE_DELTA = 11,      /* row sums of dO*O                                 */
   SPION_STAGE_SPMM_DKDV = 12,  /* tcgen05: dK and dV in one kernel                 */
-  SPION_STAGE_COUNT = 13
+  SPION_STAGE_FUSED_FWD = 13,  /* tcgen05: S, softmax, P V in one kernel            */
+  SPION_STAGE_FUSED_BWD_ROW = 14, /* tcgen05: recompute P, dP, dS, dQ per block row */
+  SPION_STAGE_FUSED_BWD_COL = 15, /* tcgen05: transposed tiles, dK and dV per block column */
+  SPION_STAGE_COUNT = 16
 };
 int spion_profile(spion_ctx* ctx, int enable);
 int spion_profile_get(spion_ctx* ctx, int stage, double* total_ms, long long* launches);
@@ -204,6 +211,18 @@ int spion_attn_backward_ex(spion_ctx* ctx, const void* Q, const void* K, const v
                            const void* P, const void* O, const void* dO,
                            void* dS, float* dP_scratch, float* delta,
                            void* dQ, void* dK, void* dV);
+
+/* Fused native forward / backward (tcgen05 engine only; UNSUPPORTED otherwise).  S, P, dP and dS
+ * never reach HBM: forward writes O and one fp32 log-sum-exp value per row (lse [BH*L], log2 domain,
+ * including the reference's non-selected-key term of models/block_attn.cu:71); backward recomputes
+ * P from Q, K and lse.  P_optional: if not NULL the [BH, nnzb, bs, bs] probabilities are also
+ * stored (what the reference returns as `attn`).  delta [BH*L] fp32 is scratch for backward. */
+int spion_supports_fused(const spion_ctx* ctx);   /* 1 if the fused calls can run this context */
+int spion_attn_forward_fused(spion_ctx* ctx, const void* Q, const void* K, const void* V,
+                             const float* keypad, void* O, float* lse, void* P_optional);
+int spion_attn_backward_fused(spion_ctx* ctx, const void* Q, const void* K, const void* V,
+                              const float* keypad, const void* O, const float* lse, const void* dO,
+                              float* delta, void* dQ, void* dK, void* dV);
 
 /* Stand-alone sparse row softmax on block tiles (the kernels of models/block_attn.cu:33-130):
  * forward S (fp32 tiles) -> P (context dtype), backward (dP fp32, P) -> dS (context dtype). */

@@ -17,7 +17,7 @@ CONV_DIAG, CONV_BOX = 0, 1
 SELECT_PATHS, SELECT_TOPK = 0, 1
 KIND_DENSE, KIND_DENSE_KPM, KIND_BLOCK, KIND_BLOCK_KPM = 0, 1, 2, 3
 ENGINE_AUTO, ENGINE_SIMT, ENGINE_TCGEN05 = 0, 1, 2
-STAGE_COUNT = 13
+STAGE_COUNT = 16
 
 # name -> (restype, argtypes); every symbol include/spion_b200.h declares
 SIGNATURES = {
@@ -28,6 +28,7 @@ SIGNATURES = {
     "spion_set_stream": (c_int, [c_void_p, c_void_p]),
     "spion_set_engine": (c_int, [c_void_p, c_int]),
     "spion_check_device_status": (c_int, [c_void_p]),
+    "spion_set_trace_buffer": (c_int, [c_void_p, c_void_p]),
     "spion_launch_count": (c_longlong, [c_void_p]),
     "spion_profile": (c_int, [c_void_p, c_int]),
     "spion_profile_get": (c_int, [c_void_p, c_int, c_void_p, c_void_p]),
@@ -45,6 +46,9 @@ SIGNATURES = {
     "spion_pattern_nnzb": (c_int, [c_void_p]),
     "spion_attn_forward_ex": (c_int, [c_void_p] * 8),
     "spion_attn_backward_ex": (c_int, [c_void_p] * 13),
+    "spion_supports_fused": (c_int, [c_void_p]),
+    "spion_attn_forward_fused": (c_int, [c_void_p] * 8),
+    "spion_attn_backward_fused": (c_int, [c_void_p] * 12),
     "spion_softmax_forward_ex": (c_int, [c_void_p] * 4),
     "spion_softmax_backward_ex": (c_int, [c_void_p] * 4),
     "spion_static_scratch_capacity": (ctypes.c_size_t, []),

@@ -74,6 +74,7 @@ extern "C" spion_ctx* spion_create(int kind, int head_dim, int seq_len, int num_
   c->nnzb = -1;
   c->launches = 0;
   c->tc = nullptr;
+  c->trace = nullptr;
   c->prof_on = 0; c->prof_n = 0;
   for (int i = 0; i < SPION_PROF_MAX_MARKS; ++i) { c->prof_ev[i] = nullptr; c->prof_stage[i] = -1; }
   for (int i = 0; i < SPION_STAGE_COUNT; ++i) { c->prof_ms[i] = 0; c->prof_cnt[i] = 0; }
@@ -125,6 +126,12 @@ extern "C" int spion_check_device_status(spion_ctx* c) {
     fprintf(stderr, "spion_b200: device status word = 0x%x (a bounded wait gave up)\n", word);
     return SPION_ERR_TIMEOUT;
   }
+  return SPION_OK;
+}
+
+extern "C" int spion_set_trace_buffer(spion_ctx* c, void* device_buffer) {
+  if (!c) return SPION_ERR_ARG;
+  c->trace = device_buffer;
   return SPION_OK;
 }
 
@@ -189,7 +196,7 @@ extern "C" int spion_profile_reset(spion_ctx* c) {
 extern "C" const char* spion_stage_name(int stage) {
   static const char* names[SPION_STAGE_COUNT] = {
       "structure", "sddmm_s", "softmax_fwd", "spmm_o", "sddmm_dp", "softmax_bwd", "spmm_dq", "spmm_dk", "spmm_dv",
-      "fused_s_p", "fused_dp_ds", "delta", "spmm_dkdv"};
+      "fused_s_p", "fused_dp_ds", "delta", "spmm_dkdv", "fused_fwd", "fused_bwd_row", "fused_bwd_col"};
   return (stage >= 0 && stage < SPION_STAGE_COUNT) ? names[stage] : "?";
 }
 
@@ -404,6 +411,29 @@ extern "C" int spion_attn_backward_ex(spion_ctx* c, const void* Q, const void* K
   if (!rc) prof_mark(c, SPION_STAGE_SPMM_DV);
   c->launches += 5;
   return rc;
+}
+
+extern "C" int spion_supports_fused(const spion_ctx* c) {
+  return (c && !is_dense(c) && use_tc(c)) ? 1 : 0;
+}
+
+extern "C" int spion_attn_forward_fused(spion_ctx* c, const void* Q, const void* K, const void* V, const float* keypad,
+                                        void* O, float* lse, void* P_optional) {
+  if (!c || !Q || !K || !V || !O || !lse) return SPION_ERR_ARG;
+  if (is_dense(c) || c->nnzb < 0) return SPION_ERR_STATE;
+  if (!use_tc(c)) return SPION_ERR_UNSUPPORTED;
+  DeviceGuard guard(c->device);
+  return tc_engine_forward_fused(c, Q, K, V, keypad, O, lse, P_optional);
+}
+
+extern "C" int spion_attn_backward_fused(spion_ctx* c, const void* Q, const void* K, const void* V, const float* keypad,
+                                         const void* O, const float* lse, const void* dO, float* delta, void* dQ,
+                                         void* dK, void* dV) {
+  if (!c || !Q || !K || !V || !O || !lse || !dO || !delta || !dQ || !dK || !dV) return SPION_ERR_ARG;
+  if (is_dense(c) || c->nnzb < 0) return SPION_ERR_STATE;
+  if (!use_tc(c)) return SPION_ERR_UNSUPPORTED;
+  DeviceGuard guard(c->device);
+  return tc_engine_backward_fused(c, Q, K, V, keypad, O, lse, dO, delta, dQ, dK, dV);
 }
 
 extern "C" int spion_softmax_forward_ex(spion_ctx* c, const float* S, const float* keypad, void* P) {

@@ -80,6 +80,7 @@ struct spion_ctx {
   int nnzb;                 // block count of the current pattern (host copy), -1 if none
   int* status_dev;          // device status word written by bounded waits
   long long launches;
+  void* trace;              // optional device buffer for per-CTA phase timestamps (debugging aid)
   void* tc;                 // tensor-core engine state (tensor maps, ...), owned by tc_engine.cu
   // per-stage timing (off by default): events recorded between the kernels of a pipeline
   int prof_on;
@@ -152,3 +153,8 @@ int tc_engine_forward(spion_ctx* c, const void* Q, const void* K, const void* V,
                       float* S_scratch);
 int tc_engine_backward(spion_ctx* c, const void* Q, const void* K, const void* V, const void* P, const void* O,
                        const void* dO, void* dS, float* dP_scratch, void* dQ, void* dK, void* dV);
+int tc_engine_forward_fused(spion_ctx* c, const void* Q, const void* K, const void* V, const float* keypad, void* O,
+                            float* lse, void* P_optional);
+int tc_engine_backward_fused(spion_ctx* c, const void* Q, const void* K, const void* V, const float* keypad,
+                             const void* O, const float* lse, const void* dO, float* delta, void* dQ, void* dK,
+                             void* dV);

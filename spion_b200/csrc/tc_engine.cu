@@ -21,46 +21,11 @@
 #include <cuda.h>
 
 #include "common.cuh"
-#include "tc_ptx.cuh"
+#include "tc_tiles.cuh"
 
 using namespace tc;
 
 namespace {
-
-constexpr int BS = 64;                  // block size of the engine
-constexpr int VT_BYTES = BS * BS * 2;   // one bf16 value tile (P or dS)
-constexpr float LOG2E = 1.4426950408889634f;
-
-enum : int { ERR_LOAD_WAIT = 1, ERR_MMA_WAIT = 2 };
-
-__device__ __forceinline__ void report(int* status, int code) { atomicOr(status, code); }
-
-__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
-  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
-  return *reinterpret_cast<uint32_t*>(&v);
-}
-__device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
-__device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
-
-template <int D> struct OpTile {
-  static constexpr int ROW_BYTES = D * 2;                        // 128 (D=64) or 64 (D=32)
-  static constexpr int BYTES = BS * ROW_BYTES;
-  static constexpr uint32_t LAYOUT = (D == 64) ? LAYOUT_SW128 : LAYOUT_SW64;
-  static constexpr uint32_t SBO = 8 * ROW_BYTES;                 // 8-row swizzle atom
-  // K-major use (contraction over the head dimension): 16 elements = 32 bytes per K step
-  __device__ static uint64_t kmajor(uint32_t saddr, int kk) { return make_smem_desc(saddr + kk * 32, 16, SBO, LAYOUT); }
-  // MN-major use (contraction over the 64 rows of the tile): 16 rows per K step
-  __device__ static uint64_t mnmajor(uint32_t saddr, int kk) {
-    return make_smem_desc(saddr + kk * 16 * ROW_BYTES, BYTES, SBO, LAYOUT);
-  }
-};
-// bf16 value tile [64 x 64], 128-byte rows, SWIZZLE_128B
-struct ValTile {
-  __device__ static uint64_t kmajor(uint32_t saddr, int kk) { return make_smem_desc(saddr + kk * 32, 16, 1024, LAYOUT_SW128); }
-  __device__ static uint64_t mnmajor(uint32_t saddr, int kk) {
-    return make_smem_desc(saddr + kk * 2048, VT_BYTES, 1024, LAYOUT_SW128);
-  }
-};
 
 // =====================================================================================
 // S (or dP) tiles of one block row + fused epilogue.  One CTA per (block row, bh), 128 threads.
@@ -282,6 +247,157 @@ __global__ void __launch_bounds__(128) k_sddmm_fused(const __grid_constant__ CUt
 }
 
 // =====================================================================================
+// dP tiles of one block row + softmax backward -> dS, second generation of MODE 1 above:
+// 4 warps (one per TMEM quadrant), two tiles per 64 columns (lane halves 0-15 / 16-31) so every
+// lane owns a row, operands requested before TMEM is set up, P tiles brought in by TMA and the
+// dS tiles written over them in shared memory and sent out by TMA stores (full-line writes).
+template <int D>
+__global__ void __launch_bounds__(128) k_dp_ds(const __grid_constant__ CUtensorMap tmdO,
+                                               const __grid_constant__ CUtensorMap tmV,
+                                               const __grid_constant__ CUtensorMap tmP,
+                                               const __grid_constant__ CUtensorMap tmdS,
+                                               const __nv_bfloat16* __restrict__ dOg,
+                                               const __nv_bfloat16* __restrict__ Og,
+                                               const int* __restrict__ row_ptr, const int* __restrict__ col_idx,
+                                               int L, int nnzb, float scale, int* status) {
+  using T = OpTile<D>;
+  constexpr int NCH = 4;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t sbase = (raw + 1023u) & ~1023u;
+  const uint32_t sA = sbase;                                   // dO tile
+  const uint32_t sB = sA + T::BYTES;                           // V tiles
+  const uint32_t sP = sB + NCH * T::BYTES;                     // P tiles in, dS tiles out
+  const uint32_t bars = sP + NCH * VT_BYTES;
+  const uint32_t bar_k = bars, bar_p = bars + 8, bar_s = bars + 16, slot = bars + 24;
+  uint32_t* slot_ptr = reinterpret_cast<uint32_t*>(smem_raw + (slot - raw));
+  __shared__ int s_abort;
+
+  const int r = blockIdx.x, bh = blockIdx.y;
+  const int tid = threadIdx.x, q = tid >> 5, lane = tid & 31;
+  const int hf = lane >> 4;
+  const int row = q * 16 + (lane & 15);
+  const int rp = row_ptr[r];
+  const int nblk = row_ptr[r + 1] - rp;
+  const int nchunks = (nblk + NCH - 1) / NCH;
+  bool a_loaded = false;
+
+  auto issue_loads = [&](int ch) {                             // thread 0 only
+    const int t0 = ch * NCH, nt = min(NCH, nblk - t0);
+    mbar_expect_tx(bar_k, (a_loaded ? 0 : T::BYTES) + nt * T::BYTES);
+    if (!a_loaded) tma_load_2d(sA, &tmdO, bar_k, 0, bh * L + r * BS);
+    for (int t = 0; t < nt; ++t) tma_load_2d(sB + t * T::BYTES, &tmV, bar_k, 0, bh * L + col_idx[rp + t0 + t] * BS);
+    mbar_expect_tx(bar_p, nt * VT_BYTES);
+    for (int t = 0; t < nt; ++t)
+      tma_load_2d(sP + t * VT_BYTES, &tmP, bar_p, 0, (int)(((size_t)bh * nnzb + rp + t0 + t) * BS));
+  };
+
+  if (tid == 0) {
+    s_abort = *reinterpret_cast<volatile int*>(status);
+    mbar_init(bar_k, 1);
+    mbar_init(bar_p, 1);
+    mbar_init(bar_s, 1);
+    fence_barrier_init();
+    if (s_abort == 0 && nblk > 0) issue_loads(0);
+  }
+  a_loaded = true;
+  __syncthreads();
+  if (s_abort != 0) return;
+  if (q == 0) {
+    tmem_alloc(slot, 128);
+    tmem_relinquish();
+  }
+  // delta_i = sum_n dO_in O_in: the two owners of a row take one half of the head dimension each
+  float delta;
+  {
+    const size_t off = ((size_t)bh * L + r * BS + row) * D + hf * (D / 2);
+    const uint4* a4 = reinterpret_cast<const uint4*>(dOg + off);
+    const uint4* b4 = reinterpret_cast<const uint4*>(Og + off);
+    float acc = 0.f;
+#pragma unroll
+    for (int u = 0; u < D / 16; ++u) {
+      const uint4 a = a4[u], b = b4[u];
+      acc += bf16_lo(a.x) * bf16_lo(b.x) + bf16_hi(a.x) * bf16_hi(b.x) + bf16_lo(a.y) * bf16_lo(b.y) +
+             bf16_hi(a.y) * bf16_hi(b.y) + bf16_lo(a.z) * bf16_lo(b.z) + bf16_hi(a.z) * bf16_hi(b.z) +
+             bf16_lo(a.w) * bf16_lo(b.w) + bf16_hi(a.w) * bf16_hi(b.w);
+    }
+    delta = acc + __shfl_xor_sync(0xffffffffu, acc, 16);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *slot_ptr;
+  const uint32_t t_lane = tmem + ((uint32_t)(q * 32) << 16);
+  constexpr uint32_t IDESC = make_idesc_bf16(64, 64, 0, 0);
+  uint32_t ph_k = 0, ph_p = 0, ph_s = 0;
+  bool ok = true;
+
+  for (int ch = 0; ch < nchunks && ok; ++ch) {
+    const int t0 = ch * NCH, nt = min(NCH, nblk - t0);
+    if (ch > 0 && tid == 0) {
+      bulk_wait_read_all();                                    // the previous dS tiles have left shared memory
+      issue_loads(ch);
+    }
+    if (!__syncthreads_and(mbar_wait(bar_k, ph_k))) { if (tid == 0) report(status, ERR_LOAD_WAIT); ok = false; break; }
+    ph_k ^= 1;
+    if (tid == 0) {
+      tc_fence_after();
+      for (int t = 0; t < nt; ++t) {
+        const uint32_t d_addr = tmem + ((uint32_t)((t & 1) * 16) << 16) + (t >> 1) * 64;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          mma_bf16(d_addr, T::kmajor(sA, kk), T::kmajor(sB + t * T::BYTES, kk), IDESC, kk > 0);
+      }
+      mma_commit(bar_s);
+    }
+    const bool w1 = mbar_wait(bar_s, ph_s);
+    const bool w2 = mbar_wait(bar_p, ph_p);
+    if (!__syncthreads_and(w1 && w2)) { if (tid == 0) report(status, ERR_MMA_WAIT); ok = false; break; }
+    ph_s ^= 1; ph_p ^= 1;
+    tc_fence_after();
+    for (int p = 0; p < 2; ++p) {
+      const int t = 2 * p + hf;
+      const bool mine = t < nt;
+      const uint32_t tile = sP + t * VT_BYTES;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t v[32];
+        tmem_ld32(t_lane + p * 64 + half * 32, v);
+        tmem_ld_wait();
+        if (mine) {
+#pragma unroll
+          for (int cc = 0; cc < 4; ++cc) {
+            const int c = half * 4 + cc;
+            const uint32_t addr = tile + row * 128 + ((c ^ (row & 7)) << 4);
+            uint32_t w[4];
+            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]) : "r"(addr) : "memory");
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const float p0 = bf16_lo(w[u]), p1 = bf16_hi(w[u]);
+              const float g0 = __uint_as_float(v[cc * 8 + 2 * u]), g1 = __uint_as_float(v[cc * 8 + 2 * u + 1]);
+              w[u] = pack_bf16(p0 * (g0 - delta) * scale, p1 * (g1 - delta) * scale);
+            }
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
+          }
+        }
+      }
+    }
+    fence_proxy_async();
+    tc_fence_before();
+    __syncthreads();
+    if (tid == 0) {
+      for (int t = 0; t < nt; ++t)
+        tma_store_2d(&tmdS, sP + t * VT_BYTES, 0, (int)(((size_t)bh * nnzb + rp + t0 + t) * BS));
+      bulk_commit();
+    }
+  }
+  if (tid == 0) bulk_wait_read_all();
+  tc_fence_before();
+  __syncthreads();
+  if (q == 0) tmem_dealloc(tmem, 128);
+}
+
+// =====================================================================================
 // Block SpMM.  128 threads, one CTA per (line, bh); NST value/operand tile pairs per chunk.
 //   DUAL == false: line = block row r.   out0[r*64.., :] = sum_k  vals0(r, c_k)   * B0[c_k*64.., :]
 //   DUAL == true : line = block column c.
@@ -413,37 +529,11 @@ __global__ void __launch_bounds__(128) k_spmm(const __grid_constant__ CUtensorMa
 
 // =====================================================================================
 // host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-struct TcState {
-  EncodeTiledFn encode = nullptr;
-  int stages = 0x1f;            // bit0 S->P, bit1 O, bit2 dP->dS, bit3 dQ, bit4 dK+dV
-  bool attr_done = false;
-};
-
 constexpr int NCH_FWD = 4, NCH_BWD = 4, NST_N = 4, NST_T = 2;
 
 template <int D> constexpr size_t smem_sddmm(int nch) { return 1024 + (size_t)(1 + nch) * OpTile<D>::BYTES + 64; }
+template <int D> constexpr size_t smem_dp_ds() { return 1024 + (size_t)5 * OpTile<D>::BYTES + 4 * VT_BYTES + 64; }
 template <int D> constexpr size_t smem_spmm(int nst, int np) { return 1024 + (size_t)nst * np * (VT_BYTES + OpTile<D>::BYTES) + 64; }
-
-int make_map(TcState* s, CUtensorMap* m, const void* base, uint64_t rows, uint32_t cols, uint32_t box_rows) {
-  const cuuint64_t dims[2] = {cols, rows};
-  const cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
-  const cuuint32_t box[2] = {cols, box_rows};
-  const cuuint32_t estr[2] = {1, 1};
-  const CUtensorMapSwizzle sw = (cols * 2 == 128) ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
-  CUresult r = s->encode(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                         CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) {
-    fprintf(stderr, "spion_b200: cuTensorMapEncodeTiled failed (%d) rows=%llu cols=%u\n", (int)r,
-            (unsigned long long)rows, cols);
-    return SPION_ERR_CUDA;
-  }
-  return SPION_OK;
-}
 
 template <int D>
 int set_attrs() {
@@ -451,6 +541,7 @@ int set_attrs() {
                                       (int)smem_sddmm<D>(NCH_FWD)));
   SPION_CUDA_TRY(cudaFuncSetAttribute(k_sddmm_fused<D, 1, NCH_BWD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       (int)smem_sddmm<D>(NCH_BWD)));
+  SPION_CUDA_TRY(cudaFuncSetAttribute(k_dp_ds<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dp_ds<D>()));
   SPION_CUDA_TRY(cudaFuncSetAttribute(k_spmm<D, false, NST_N>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       (int)smem_spmm<D>(NST_N, 1)));
   SPION_CUDA_TRY(cudaFuncSetAttribute(k_spmm<D, true, NST_T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -513,11 +604,18 @@ int run_backward(spion_ctx* c, TcState* s, const void* Q, const void* K, const v
   int rc;
   prof_mark(c, -1);
   if (s->stages & 4) {
-    CUtensorMap mdo, mv;
-    if ((rc = make_map(s, &mdo, dO, rows, D, BS)) || (rc = make_map(s, &mv, V, rows, D, BS))) return rc;
-    k_sddmm_fused<D, 1, NCH_BWD><<<grid, 128, smem_sddmm<D>(NCH_BWD), c->stream>>>(
-        mdo, mv, (__nv_bfloat16*)dS, (const __nv_bfloat16*)P, (const __nv_bfloat16*)dO, (const __nv_bfloat16*)O,
-        nullptr, c->row_ptr, c->col_idx, c->L, c->nnzb, c->scale, 0.f, c->status_dev);
+    CUtensorMap mdo, mv, mpp, mdss;
+    if ((rc = make_map(s, &mdo, dO, rows, D, BS)) || (rc = make_map(s, &mv, V, rows, D, BS)) ||
+        (rc = make_map(s, &mpp, P, vrows, BS, BS)) || (rc = make_map(s, &mdss, dS, vrows, BS, BS)))
+      return rc;
+    if (s->stages & 32)     // first-generation kernel, kept for comparison
+      k_sddmm_fused<D, 1, NCH_BWD><<<grid, 128, smem_sddmm<D>(NCH_BWD), c->stream>>>(
+          mdo, mv, (__nv_bfloat16*)dS, (const __nv_bfloat16*)P, (const __nv_bfloat16*)dO, (const __nv_bfloat16*)O,
+          nullptr, c->row_ptr, c->col_idx, c->L, c->nnzb, c->scale, 0.f, c->status_dev);
+    else
+      k_dp_ds<D><<<grid, 128, smem_dp_ds<D>(), c->stream>>>(mdo, mv, mpp, mdss, (const __nv_bfloat16*)dO,
+                                                            (const __nv_bfloat16*)O, c->row_ptr, c->col_idx, c->L,
+                                                            c->nnzb, c->scale, c->status_dev);
     SPION_LAUNCH_CHECK();
     c->launches += 1;
     prof_mark(c, SPION_STAGE_FUSED_DP_DS);
@@ -581,8 +679,9 @@ int tc_engine_prepare(spion_ctx* c) {
   }
   s->encode = (EncodeTiledFn)fn;
   const char* env = getenv("SPION_TC_STAGES");
-  if (env) s->stages = atoi(env) & 0x1f;
+  if (env) s->stages = atoi(env) & 0x3f;
   int rc = (c->d == 64) ? set_attrs<64>() : set_attrs<32>();
+  if (!rc) rc = fused_set_attrs(c->d);
   if (rc) { delete s; return rc; }
   c->tc = s;
   return SPION_OK;
@@ -608,4 +707,42 @@ int tc_engine_backward(spion_ctx* c, const void* Q, const void* K, const void* V
   if (c->nnzb == 0) return SPION_ERR_SHAPE;
   return c->d == 64 ? run_backward<64>(c, s, Q, K, V, P, O, dO, dS, dP_scratch, dQ, dK, dV)
                     : run_backward<32>(c, s, Q, K, V, P, O, dO, dS, dP_scratch, dQ, dK, dV);
+}
+
+namespace tc {
+int tc_engine_probabilities(spion_ctx* c, const void* Q, const void* K, const float* keypad, void* P) {
+  TcState* s = (TcState*)c->tc;
+  const uint64_t rows = (uint64_t)c->BH * c->L;
+  CUtensorMap mq, mk;
+  int rc;
+  if ((rc = make_map(s, &mq, Q, rows, (uint32_t)c->d, BS)) || (rc = make_map(s, &mk, K, rows, (uint32_t)c->d, BS))) return rc;
+  const dim3 grid(c->nb, c->BH);
+  if (c->d == 64)
+    k_sddmm_fused<64, 0, NCH_FWD><<<grid, 128, smem_sddmm<64>(NCH_FWD), c->stream>>>(
+        mq, mk, (__nv_bfloat16*)P, nullptr, nullptr, nullptr, keypad, c->row_ptr, c->col_idx, c->L, c->nnzb, c->scale,
+        keypad ? 0.0f : -100.0f, c->status_dev);
+  else
+    k_sddmm_fused<32, 0, NCH_FWD><<<grid, 128, smem_sddmm<32>(NCH_FWD), c->stream>>>(
+        mq, mk, (__nv_bfloat16*)P, nullptr, nullptr, nullptr, keypad, c->row_ptr, c->col_idx, c->L, c->nnzb, c->scale,
+        keypad ? 0.0f : -100.0f, c->status_dev);
+  SPION_LAUNCH_CHECK();
+  c->launches += 1;
+  prof_mark(c, SPION_STAGE_FUSED_S_P);
+  return SPION_OK;
+}
+}  // namespace tc
+
+int tc_engine_forward_fused(spion_ctx* c, const void* Q, const void* K, const void* V, const float* keypad, void* O,
+                            float* lse, void* P_optional) {
+  if (!c->tc) return SPION_ERR_STATE;
+  if (c->nnzb == 0) return SPION_ERR_SHAPE;
+  return fused_forward(c, (TcState*)c->tc, Q, K, V, keypad, O, lse, P_optional);
+}
+
+int tc_engine_backward_fused(spion_ctx* c, const void* Q, const void* K, const void* V, const float* keypad,
+                             const void* O, const float* lse, const void* dO, float* delta, void* dQ, void* dK,
+                             void* dV) {
+  if (!c->tc) return SPION_ERR_STATE;
+  if (c->nnzb == 0) return SPION_ERR_SHAPE;
+  return fused_backward(c, (TcState*)c->tc, Q, K, V, keypad, O, lse, dO, delta, dQ, dK, dV);
 }

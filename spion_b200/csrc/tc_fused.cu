@@ -1,0 +1,435 @@
+// Fused block-sparse attention kernels (sm_100a, bf16, 64x64 blocks): S, the sparse row softmax
+// and the products that follow stay on chip; only Q, K, V, dO, O, the gradients and one fp32
+// log-sum-exp per row cross HBM (P is written only when the caller asks for it).
+//
+//   k_fwd_fused   per block row:   S = Q K^T (tcgen05, TMEM) -> row softmax (fp32, registers)
+//                                  -> P (bf16, swizzled shared memory) -> O = P V (tcgen05)
+//                 replaces the three forward stages of models/block_attn.cu:453-487.
+//   k_bwd_row     per block row:   recompute P from Q, K and the stored log-sum-exp, dP = dO V^T,
+//                                  dS = P (dP - delta) scale -> dQ = dS K          (:498-516)
+//   k_bwd_col     per block column: the same tiles transposed (S^T = K Q^T, dP^T = V dO^T)
+//                                  -> dV = P^T dO, dK = dS^T Q                     (:526-536)
+//
+// Softmax semantics are the reference's (models/block_attn.cu:48-87): every non-selected key of a
+// row adds exp(0 - m) to the denominator.  lse2_i = m_i*log2(e) + log2(Z_i) is stored so that
+// P_ij = exp2(s_ij*scale*log2(e) - lse2_i) can be recomputed by the backward kernels.
+//
+// Accumulator placement: an MMA with M = 64 fills TMEM lanes (m%16) + 32*(m/16); a second tile is
+// placed in the same columns at lane offset 16, so that all 32 lanes of every warp hold a row
+// (lanes 0-15: even tile of a pair, lanes 16-31: odd tile).
+#include "tc_tiles.cuh"
+
+using namespace tc;
+
+namespace {
+
+constexpr int FWD_THREADS = 128;
+constexpr int FWD_NCH = 4;                 // tiles of a row that fits in one chunk
+constexpr uint32_t FWD_TMEM_COLS = 128;    // S pairs at columns [0,64) and [64,128); O reuses [0,64)
+
+template <int D> constexpr size_t fwd_smem_bytes() {
+  // Q | K x4 | V x4 | (P x4 only when a K tile is smaller than a P tile) | barriers
+  return 1024 + (size_t)(1 + 2 * FWD_NCH) * OpTile<D>::BYTES + (D == 64 ? 0 : (size_t)FWD_NCH * VT_BYTES) + 64;
+}
+
+// Store one 64-value bf16 row into a [64 x 64] K-major SWIZZLE_128B tile (16-byte chunk c of row i
+// sits at chunk c ^ (i & 7)): the image TMA would have produced, readable by tcgen05.mma.
+__device__ __forceinline__ void store_row_swizzled(uint32_t tile, int i, const uint32_t (&w)[32]) {
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    const uint32_t addr = tile + i * 128 + ((c ^ (i & 7)) << 4);
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[4 * c]), "r"(w[4 * c + 1]),
+                 "r"(w[4 * c + 2]), "r"(w[4 * c + 3])
+                 : "memory");
+  }
+}
+
+// One CTA (4 warps, one per TMEM quadrant) per (block row, bh).  A row of the block is owned by
+// two threads of one warp (lane l: even tiles, lane l+16: odd tiles), so the row statistics need
+// only one warp shuffle.  Rows with at most 4 blocks are done in one chunk (S in all 128 columns,
+// O then overwrites the first 64); longer rows stream chunks of 2 tiles through columns [64,128)
+// in two passes (row maximum, then exp / P / O).  P is kept unnormalised (exp2(x - m) <= 1) and
+// the output row is divided by the denominator at the end.
+// STORE_P: also write the normalised probabilities as [64 x 64] bf16 tiles (TMA store from the shared
+// memory tiles the second product reads): rows of one chunk are rescaled in place once the
+// denominator is known; longer rows accumulate the denominator on line in pass A instead.
+template <int D, bool STORE_P>
+__global__ void __launch_bounds__(FWD_THREADS) k_fwd_fused(const __grid_constant__ CUtensorMap tmQ,
+                                                           const __grid_constant__ CUtensorMap tmK,
+                                                           const __grid_constant__ CUtensorMap tmV,
+                                                           const __grid_constant__ CUtensorMap tmP,
+                                                           __nv_bfloat16* __restrict__ O, float* __restrict__ lse_out,
+                                                           const float* __restrict__ keypad,
+                                                           const int* __restrict__ row_ptr,
+                                                           const int* __restrict__ col_idx, int L, int nnzb,
+                                                           float scale, float floor_v, int* status,
+                                                           unsigned long long* trace) {
+  using T = OpTile<D>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t sbase = (raw + 1023u) & ~1023u;
+  const uint32_t sQ = sbase;
+  const uint32_t sK = sQ + T::BYTES;
+  const uint32_t sV = sK + FWD_NCH * T::BYTES;
+  const uint32_t sP = (D == 64) ? sK : sV + FWD_NCH * T::BYTES;            // P tiles reuse the K buffers
+  const uint32_t bars = sV + FWD_NCH * T::BYTES + (D == 64 ? 0 : FWD_NCH * VT_BYTES);
+  const uint32_t bar_k = bars, bar_v = bars + 8, bar_s = bars + 16, bar_o = bars + 24, slot = bars + 32;
+  uint32_t* slot_ptr = reinterpret_cast<uint32_t*>(smem_raw + (slot - raw));
+  __shared__ int s_abort;
+  // optional phase timestamps (ns) of this CTA: 8 slots per CTA, written by thread 0
+  auto stamp = [&](int k) {
+    if (trace && threadIdx.x == 0) {
+      unsigned long long t;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)::"memory");
+      trace[((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 8 + k] = t;
+    }
+  };
+  stamp(0);
+
+  const int r = blockIdx.x, bh = blockIdx.y;
+  const int tid = threadIdx.x, q = tid >> 5, lane = tid & 31;
+  const int hf = lane >> 4;                                    // 0: even tiles, 1: odd tiles
+  const int row = q * 16 + (lane & 15);                        // row of the block this thread owns
+
+  const int rp = row_ptr[r];
+  const int nblk = row_ptr[r + 1] - rp;
+  const bool single = nblk <= FWD_NCH;
+  const int CH = single ? FWD_NCH : 2;                         // tiles per chunk
+  const int nchunks = (nblk + CH - 1) / CH;
+  bool q_loaded = false;
+
+  // tile t of a chunk: accumulator columns and buffers
+  auto s_col = [&](int t) -> uint32_t { return single ? (uint32_t)(t >> 1) * 64u : 64u; };
+  auto issue_loads = [&](int ch, bool with_v) {                // thread 0 only
+    const int t0 = ch * CH, nt = min(CH, nblk - t0);
+    mbar_expect_tx(bar_k, (q_loaded ? 0 : T::BYTES) + nt * T::BYTES);
+    if (!q_loaded) tma_load_2d(sQ, &tmQ, bar_k, 0, bh * L + r * BS);
+    for (int t = 0; t < nt; ++t) tma_load_2d(sK + t * T::BYTES, &tmK, bar_k, 0, bh * L + col_idx[rp + t0 + t] * BS);
+    if (with_v) {
+      mbar_expect_tx(bar_v, nt * T::BYTES);
+      for (int t = 0; t < nt; ++t) tma_load_2d(sV + t * T::BYTES, &tmV, bar_v, 0, bh * L + col_idx[rp + t0 + t] * BS);
+    }
+  };
+
+  if (tid == 0) {
+    s_abort = *reinterpret_cast<volatile int*>(status);
+    mbar_init(bar_k, 1);
+    mbar_init(bar_v, 1);
+    mbar_init(bar_s, 1);
+    mbar_init(bar_o, 1);
+    fence_barrier_init();
+    if (s_abort == 0 && nblk > 0) issue_loads(0, single);      // operands are on their way before TMEM is set up
+  }
+  q_loaded = true;
+  __syncthreads();
+  if (s_abort != 0) return;
+  if (q == 0) {
+    tmem_alloc(slot, FWD_TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *slot_ptr;
+  stamp(1);
+
+  const uint32_t t_lane = tmem + ((uint32_t)(q * 32) << 16);
+  constexpr uint32_t IDESC_S = make_idesc_bf16(64, 64, 0, 0);
+  constexpr uint32_t IDESC_O = make_idesc_bf16(64, D, 0, 1);
+  const float sc2 = scale * LOG2E;
+  const float* kp = keypad ? keypad + (size_t)bh * L : nullptr;
+  uint32_t ph_k = 0, ph_v = 0, ph_s = 0, ph_o = 0;
+  bool ok = true;
+
+  // wait for the K tiles of chunk ch (already requested), run the S MMAs, wait for them
+  auto produce_s = [&](int ch) -> bool {
+    const int t0 = ch * CH, nt = min(CH, nblk - t0);
+    if (!__syncthreads_and(mbar_wait(bar_k, ph_k))) { if (tid == 0) report(status, ERR_LOAD_WAIT); return false; }
+    ph_k ^= 1;
+    stamp(2);
+    if (tid == 0) {
+      tc_fence_after();
+      for (int t = 0; t < nt; ++t) {
+        const uint32_t d_addr = tmem + ((uint32_t)((t & 1) * 16) << 16) + s_col(t);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          mma_bf16(d_addr, T::kmajor(sQ, kk), T::kmajor(sK + t * T::BYTES, kk), IDESC_S, kk > 0);
+      }
+      mma_commit(bar_s);
+    }
+    if (!__syncthreads_and(mbar_wait(bar_s, ph_s))) { if (tid == 0) report(status, ERR_MMA_WAIT); return false; }
+    ph_s ^= 1;
+    tc_fence_after();
+    stamp(3);
+    return true;
+  };
+
+  // ------------------------------------------------------------------ pass A: row maximum
+  float m2 = floor_v * LOG2E;
+  float l_part = 0.f;
+  const int npairs = single ? 2 : 1;
+  const bool online = STORE_P && !single;                        // denominator needed before P is written
+  for (int ch = 0; ch < nchunks; ++ch) {
+    if (ch > 0 && tid == 0) issue_loads(ch, false);
+    ok = produce_s(ch);
+    if (!ok) break;
+    const int t0 = ch * CH, nt = min(CH, nblk - t0);
+    if (!online) {
+      for (int p = 0; p < npairs; ++p) {
+        const int t = 2 * p + hf;
+        const bool mine = t < nt;
+        const int c = mine ? col_idx[rp + t0 + t] : 0;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t v[32];
+          tmem_ld32(t_lane + s_col(2 * p) + half * 32, v);
+          tmem_ld_wait();
+          if (mine) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              float x = __uint_as_float(v[j]) * sc2;
+              if (kp) x -= kp[c * BS + half * 32 + j] * LOG2E;
+              m2 = fmaxf(m2, x);
+            }
+          }
+        }
+      }
+    } else {
+      const bool mine = hf < nt;
+      const int c = mine ? col_idx[rp + t0 + hf] : 0;
+      uint32_t v0[32], v1[32];
+      tmem_ld32(t_lane + 64, v0);
+      tmem_ld32(t_lane + 96, v1);
+      tmem_ld_wait();
+      float cm = -INFINITY;
+      if (mine) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          float x0 = __uint_as_float(v0[j]) * sc2, x1 = __uint_as_float(v1[j]) * sc2;
+          if (kp) { x0 -= kp[c * BS + j] * LOG2E; x1 -= kp[c * BS + 32 + j] * LOG2E; }
+          v0[j] = __float_as_uint(x0); v1[j] = __float_as_uint(x1);
+          cm = fmaxf(cm, fmaxf(x0, x1));
+        }
+      }
+      cm = fmaxf(cm, __shfl_xor_sync(0xffffffffu, cm, 16));
+      const float m_new = fmaxf(m2, cm);
+      float sum = 0.f;
+      if (mine) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) sum += exp2f(__uint_as_float(v0[j]) - m_new) + exp2f(__uint_as_float(v1[j]) - m_new);
+      }
+      l_part = l_part * exp2f(m2 - m_new) + sum;
+      m2 = m_new;
+    }
+    if (!single) { tc_fence_before(); __syncthreads(); }        // the next chunk overwrites these columns
+  }
+  m2 = fmaxf(m2, __shfl_xor_sync(0xffffffffu, m2, 16));          // both owners of a row agree
+  float lse_fixed = 0.f;
+  if (online) {
+    const float l = l_part + __shfl_xor_sync(0xffffffffu, l_part, 16) + (float)(L - nblk * BS) * exp2f(-m2);
+    lse_fixed = m2 + log2f(l);
+    m2 = lse_fixed;                                               // pass B then produces normalised P directly
+    l_part = 0.f;
+  }
+  stamp(4);
+
+  // ------------------------------------------------------------------ pass B: exp, P -> smem, O += P V
+  for (int ch = 0; ch < nchunks && ok; ++ch) {
+    if (!single) {
+      if (tid == 0) issue_loads(ch, true);
+      ok = produce_s(ch);
+      if (!ok) break;
+    }
+    const int t0 = ch * CH, nt = min(CH, nblk - t0);
+    for (int p = 0; p < npairs; ++p) {
+      const int t = 2 * p + hf;
+      const bool mine = t < nt;
+      const int c = mine ? col_idx[rp + t0 + t] : 0;
+      uint32_t w[32];
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t v[32];
+        tmem_ld32(t_lane + s_col(2 * p) + half * 32, v);
+        tmem_ld_wait();
+        if (mine) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) {
+            float x0 = __uint_as_float(v[j]) * sc2, x1 = __uint_as_float(v[j + 1]) * sc2;
+            if (kp) { x0 -= kp[c * BS + half * 32 + j] * LOG2E; x1 -= kp[c * BS + half * 32 + j + 1] * LOG2E; }
+            const float e0 = exp2f(x0 - m2), e1 = exp2f(x1 - m2);
+            l_part += e0 + e1;
+            w[half * 16 + (j >> 1)] = pack_bf16(e0, e1);
+          }
+        }
+      }
+      if (mine) store_row_swizzled(sP + t * VT_BYTES, row, w);
+    }
+    fence_proxy_async();                                        // P rows -> visible to the MMA proxy
+    tc_fence_before();
+    __syncthreads();
+    stamp(5);
+    if (tid == 0) {
+      if (mbar_wait(bar_v, ph_v)) {
+        tc_fence_after();
+        for (int t = 0; t < nt; ++t) {
+          const uint32_t d_addr = tmem + ((uint32_t)((t & 1) * 16) << 16);           // O: columns [0, D)
+          const uint32_t first = (ch == 0 && t < 2) ? 0u : 1u;                       // first tile of each lane half
+#pragma unroll
+          for (int kk = 0; kk < BS / 16; ++kk)
+            mma_bf16(d_addr, ValTile::kmajor(sP + t * VT_BYTES, kk), T::mnmajor(sV + t * T::BYTES, kk), IDESC_O,
+                     (kk > 0) ? 1u : first);
+        }
+        mma_commit(bar_o);
+        if (online) {                                             // these tiles are final: store them now
+          for (int t = 0; t < nt; ++t)
+            tma_store_2d(&tmP, sP + t * VT_BYTES, 0, (int)(((size_t)bh * nnzb + rp + t0 + t) * BS));
+          bulk_commit();
+        }
+      } else {
+        report(status, ERR_LOAD_WAIT);
+      }
+    }
+    ph_v ^= 1;
+    // the O MMAs read sP / sV, and the next chunk overwrites them and the S columns: wait here
+    if (!__syncthreads_and(mbar_wait(bar_o, ph_o))) { if (tid == 0) report(status, ERR_MMA2_WAIT); ok = false; break; }
+    ph_o ^= 1;
+    tc_fence_after();
+    if (online && tid == 0) bulk_wait_read_all();                 // before the next chunk's loads reuse the tiles
+    stamp(6);
+  }
+
+  // ------------------------------------------------------------------ epilogue
+  if (ok) {
+    float inv = 1.0f, lse2 = lse_fixed;
+    if (!online) {
+      const float l = l_part + __shfl_xor_sync(0xffffffffu, l_part, 16) + (float)(L - nblk * BS) * exp2f(-m2);
+      inv = 1.0f / l;
+      lse2 = m2 + log2f(l);
+    }
+    if (hf == 0) lse_out[(size_t)bh * L + r * BS + row] = lse2;
+    if (STORE_P && single && nblk > 0) {
+      // rescale this thread's rows of the unnormalised tiles in place, then store the tiles
+      for (int p = 0; p < 2; ++p) {
+        const int t = 2 * p + hf;
+        if (t < nblk) {
+          const uint32_t tile = sP + t * VT_BYTES;
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            const uint32_t addr = tile + row * 128 + ((c ^ (row & 7)) << 4);
+            uint32_t w0, w1, w2, w3;
+            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(w0), "=r"(w1), "=r"(w2), "=r"(w3) : "r"(addr) : "memory");
+            w0 = pack_bf16(bf16_lo(w0) * inv, bf16_hi(w0) * inv); w1 = pack_bf16(bf16_lo(w1) * inv, bf16_hi(w1) * inv);
+            w2 = pack_bf16(bf16_lo(w2) * inv, bf16_hi(w2) * inv); w3 = pack_bf16(bf16_lo(w3) * inv, bf16_hi(w3) * inv);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
+          }
+        }
+      }
+      fence_proxy_async();
+      __syncthreads();
+      if (tid == 0) {
+        for (int t = 0; t < nblk; ++t) tma_store_2d(&tmP, sP + t * VT_BYTES, 0, (int)(((size_t)bh * nnzb + rp + t) * BS));
+        bulk_commit();
+      }
+    }
+    const bool odd_valid = nblk >= 2;
+    __nv_bfloat16* dst = O + ((size_t)bh * L + r * BS + row) * D + hf * (D / 2);
+#pragma unroll
+    for (int h = 0; h < D / 32; ++h) {
+      uint32_t v[32];
+      if (nblk > 0) {
+        tmem_ld32(t_lane + h * 32, v);
+        tmem_ld_wait();
+      }
+      float acc[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const float mine_v = (nblk > 0 && (hf == 0 || odd_valid)) ? __uint_as_float(v[j]) : 0.f;
+        acc[j] = (mine_v + __shfl_xor_sync(0xffffffffu, mine_v, 16)) * inv;
+      }
+      // D = 64: lanes 0-15 store columns [0,32) (h = 0), lanes 16-31 columns [32,64) (h = 1)
+      // D = 32: lanes 0-15 store columns [0,16), lanes 16-31 columns [16,32)
+      if (D == 64) {
+        if (hf == h) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            uint4 pk;
+            pk.x = pack_bf16(acc[j], acc[j + 1]); pk.y = pack_bf16(acc[j + 2], acc[j + 3]);
+            pk.z = pack_bf16(acc[j + 4], acc[j + 5]); pk.w = pack_bf16(acc[j + 6], acc[j + 7]);
+            *reinterpret_cast<uint4*>(dst + j) = pk;
+          }
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 16; j += 8) {
+          float val[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) val[u] = hf ? acc[16 + j + u] : acc[j + u];
+          uint4 pk;
+          pk.x = pack_bf16(val[0], val[1]); pk.y = pack_bf16(val[2], val[3]);
+          pk.z = pack_bf16(val[4], val[5]); pk.w = pack_bf16(val[6], val[7]);
+          *reinterpret_cast<uint4*>(dst + j) = pk;
+        }
+      }
+    }
+  }
+  if (STORE_P && tid == 0) bulk_wait_read_all();                  // shared memory must outlive the tile stores
+  stamp(7);
+  tc_fence_before();
+  __syncthreads();
+  if (q == 0) tmem_dealloc(tmem, FWD_TMEM_COLS);
+}
+
+}  // namespace
+
+namespace tc {
+
+int fused_set_attrs(int d) {
+  if (d == 64) {
+    SPION_CUDA_TRY(cudaFuncSetAttribute(k_fwd_fused<64, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fwd_smem_bytes<64>()));
+    SPION_CUDA_TRY(cudaFuncSetAttribute(k_fwd_fused<64, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fwd_smem_bytes<64>()));
+  } else {
+    SPION_CUDA_TRY(cudaFuncSetAttribute(k_fwd_fused<32, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fwd_smem_bytes<32>()));
+    SPION_CUDA_TRY(cudaFuncSetAttribute(k_fwd_fused<32, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fwd_smem_bytes<32>()));
+  }
+  return SPION_OK;
+}
+
+template <int D>
+static int fwd_launch(spion_ctx* c, TcState* s, const void* Q, const void* K, const void* V, const float* keypad,
+                      void* O, float* lse, void* P) {
+  const uint64_t rows = (uint64_t)c->BH * c->L, vrows = (uint64_t)c->BH * c->nnzb * BS;
+  CUtensorMap mq, mk, mv, mp;
+  int rc;
+  if ((rc = make_map(s, &mq, Q, rows, D, BS)) || (rc = make_map(s, &mk, K, rows, D, BS)) ||
+      (rc = make_map(s, &mv, V, rows, D, BS)))
+    return rc;
+  if (P) { if ((rc = make_map(s, &mp, P, vrows, BS, BS))) return rc; } else mp = mq;
+  prof_mark(c, -1);
+  const dim3 grid(c->nb, c->BH);
+  const float floor_v = keypad ? 0.0f : -100.0f;
+  if (P)
+    k_fwd_fused<D, true><<<grid, FWD_THREADS, fwd_smem_bytes<D>(), c->stream>>>(
+        mq, mk, mv, mp, (__nv_bfloat16*)O, lse, keypad, c->row_ptr, c->col_idx, c->L, c->nnzb, c->scale, floor_v,
+        c->status_dev, (unsigned long long*)c->trace);
+  else
+    k_fwd_fused<D, false><<<grid, FWD_THREADS, fwd_smem_bytes<D>(), c->stream>>>(
+        mq, mk, mv, mp, (__nv_bfloat16*)O, lse, keypad, c->row_ptr, c->col_idx, c->L, c->nnzb, c->scale, floor_v,
+        c->status_dev, (unsigned long long*)c->trace);
+  SPION_LAUNCH_CHECK();
+  c->launches += 1;
+  prof_mark(c, SPION_STAGE_FUSED_FWD);
+  return SPION_OK;
+}
+
+int fused_forward(spion_ctx* c, TcState* s, const void* Q, const void* K, const void* V, const float* keypad, void* O,
+                  float* lse, void* P_optional) {
+  return c->d == 64 ? fwd_launch<64>(c, s, Q, K, V, keypad, O, lse, P_optional)
+                    : fwd_launch<32>(c, s, Q, K, V, keypad, O, lse, P_optional);
+}
+
+int fused_backward(spion_ctx*, TcState*, const void*, const void*, const void*, const float*, const void*,
+                   const float*, const void*, float*, void*, void*, void*) {
+  return SPION_ERR_UNSUPPORTED;
+}
+
+}  // namespace tc

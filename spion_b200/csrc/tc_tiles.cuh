@@ -1,0 +1,84 @@
+// Tile and descriptor helpers shared by the tensor-core kernels (tc_engine.cu, tc_fused.cu).
+#pragma once
+#include <cuda.h>
+
+#include "common.cuh"
+#include "tc_ptx.cuh"
+
+namespace tc {
+
+constexpr int BS = 64;                  // block size of the engine
+constexpr int VT_BYTES = BS * BS * 2;   // one bf16 value tile (P or dS)
+constexpr float LOG2E = 1.4426950408889634f;
+
+enum : int { ERR_LOAD_WAIT = 1, ERR_MMA_WAIT = 2, ERR_MMA2_WAIT = 4 };
+
+__device__ __forceinline__ void report(int* status, int code) { atomicOr(status, code); }
+
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+
+template <int D> struct OpTile {
+  static constexpr int ROW_BYTES = D * 2;                        // 128 (D=64) or 64 (D=32)
+  static constexpr int BYTES = BS * ROW_BYTES;
+  static constexpr uint32_t LAYOUT = (D == 64) ? LAYOUT_SW128 : LAYOUT_SW64;
+  static constexpr uint32_t SBO = 8 * ROW_BYTES;                 // 8-row swizzle atom
+  // K-major use (contraction over the head dimension): 16 elements = 32 bytes per K step
+  __device__ static uint64_t kmajor(uint32_t saddr, int kk) { return make_smem_desc(saddr + kk * 32, 16, SBO, LAYOUT); }
+  // MN-major use (contraction over the 64 rows of the tile): 16 rows per K step
+  __device__ static uint64_t mnmajor(uint32_t saddr, int kk) {
+    return make_smem_desc(saddr + kk * 16 * ROW_BYTES, BYTES, SBO, LAYOUT);
+  }
+};
+// bf16 value tile [64 x 64], 128-byte rows, SWIZZLE_128B
+struct ValTile {
+  __device__ static uint64_t kmajor(uint32_t saddr, int kk) { return make_smem_desc(saddr + kk * 32, 16, 1024, LAYOUT_SW128); }
+  __device__ static uint64_t mnmajor(uint32_t saddr, int kk) {
+    return make_smem_desc(saddr + kk * 2048, VT_BYTES, 1024, LAYOUT_SW128);
+  }
+};
+
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+struct TcState {
+  EncodeTiledFn encode = nullptr;
+  int stages = 0x1f;            // bit0 S->P, bit1 O, bit2 dP->dS, bit3 dQ, bit4 dK+dV
+  bool attr_done = false;
+};
+
+inline int make_map(TcState* s, CUtensorMap* m, const void* base, uint64_t rows, uint32_t cols, uint32_t box_rows) {
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+  const cuuint32_t box[2] = {cols, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUtensorMapSwizzle sw = (cols * 2 == 128) ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+  CUresult r = s->encode(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    fprintf(stderr, "spion_b200: cuTensorMapEncodeTiled failed (%d) rows=%llu cols=%u\n", (int)r,
+            (unsigned long long)rows, cols);
+    return SPION_ERR_CUDA;
+  }
+  return SPION_OK;
+}
+
+
+// tc_engine.cu: P tiles only (S + softmax)
+int tc_engine_probabilities(spion_ctx* c, const void* Q, const void* K, const float* keypad, void* P);
+// tc_fused.cu
+int fused_set_attrs(int d);
+int fused_forward(spion_ctx* c, TcState* s, const void* Q, const void* K, const void* V, const float* keypad, void* O,
+                  float* lse, void* P_optional);
+int fused_backward(spion_ctx* c, TcState* s, const void* Q, const void* K, const void* V, const float* keypad,
+                   const void* O, const float* lse, const void* dO, float* delta, void* dQ, void* dK, void* dV);
+
+}  // namespace tc
