@@ -45,6 +45,16 @@ WORKLOADS = {
     "tiny": (2, 2, 512, 64, 64, 0.25, "bf16"),
 }
 
+# End-to-end training-step workloads (benchmark configs 2, 3, 5): name -> (task, batch, dtype,
+# quantile threshold chosen to land near the config's block density, scaling).  The batch of the
+# "strong" workload is the GLOBAL batch, split evenly across ranks.
+TRAIN_WORKLOADS = {
+    "train_image_L1024": ("image", 256, "fp32", 0.80, "weak"),
+    "train_text_L4096": ("text", 32, "bf16", 0.90, "weak"),
+    "train_retrieval_L4096": ("retrieval", 64, "bf16", 0.90, "strong"),
+    "train_tiny": ("text", 2, "bf16", 0.85, "weak"),
+}
+
 
 def load_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -175,13 +185,103 @@ def run_reference(args, rank):
     }))
 
 
+def run_training(args, rank, world, local_rank):
+    """One optimizer step of the 2-layer SPION-CF encoder classifier per step: dense warm-up step,
+    pattern discovery per layer, then timed sparse steps (fwd + bwd + gradient all-reduce + AdamW)."""
+    from spion_b200 import dp, harness, synthetic
+    import torch.distributed as dist
+    task, batch, dt, thr, scaling = TRAIN_WORKLOADS[args.workload]
+    dev = torch.device("cuda", local_rank)
+    per_rank = batch // world if scaling == "strong" else batch
+    cfg = harness.task_config(task, per_rank, native=True, dtype=dt)
+    if args.workload == "train_tiny":
+        cfg["max_seq_len"] = 512
+    cfg["threshold"] = thr
+    L, dual = cfg["max_seq_len"], cfg["dual"]
+    tr = harness.Trainer(cfg, lr=1e-4, device=dev, seed=0)
+
+    def host_batch(seed):
+        a = synthetic.token_ids(seed + 100 * rank, per_rank, L).pin_memory()
+        b = synthetic.token_ids(seed + 100 * rank + 50, per_rank, L).pin_memory() if dual else None
+        return a, b, synthetic.labels(seed + rank, per_rank, cfg["num_classes"]).pin_memory()
+
+    def to_dev(hb):
+        a, b, y = hb
+        ids = (a.to(dev, non_blocking=True), b.to(dev, non_blocking=True)) if dual else a.to(dev, non_blocking=True)
+        return ids, y.to(dev, non_blocking=True)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    hb = host_batch(1)
+    ids, y = to_dev(hb)
+    _, maps = tr.step(ids, y, is_attn=True)                      # dense warm-up step (untimed)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    mat_lst = tr.discover(maps)
+    torch.cuda.synchronize()
+    pattern_ms = (time.perf_counter() - t0) * 1e3
+    dens = [float(m.mean()) for m in mat_lst[0]]
+    del maps
+    torch.cuda.empty_cache()
+    for _ in range(args.warmup):
+        tr.step(ids, y)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        tr.step(ids, y)
+    e1.record()
+    barrier()
+    t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step = float(t.item()) / args.steps
+    tokens = per_rank * world * L * (2 if dual else 1)
+    # e2e: ids and labels from pinned host memory every step, the loss read back every step
+    for _ in range(2):
+        ids2, y2 = to_dev(hb); float(tr.step(ids2, y2)[0])
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        ids2, y2 = to_dev(hb)
+        loss, _ = tr.step(ids2, y2)
+        lv = float(loss)                                          # device -> host read of the step's result
+    e1.record()
+    barrier()
+    t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_ms = float(t.item()) / args.steps
+    launches = sum(int(layer.mha.block_attn.launch_count()) for layer in tr.model.model.layers)
+    if rank == 0:
+        print(json.dumps({
+            "metric": "training-step Mtokens/s (2-layer SPION-CF encoder, L=%d)" % L, "value": tokens / (ms_step * 1e-3) / 1e6,
+            "unit": "Mtokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
+            "higher_is_better": True, "scaling": scaling, "vs_baseline": None, "dtype": "bf16" if dt == "bf16" else "f32",
+            "data": "synthetic",
+            "config": {"workload": args.workload, "task": cfg["task"], "batch_per_gpu": per_rank, "L": L,
+                       "block": cfg["block_size"], "threshold": thr, "density_per_layer": dens,
+                       "grad_bucket_bytes": tr.bucket.nbytes, "pattern_discovery_ms": pattern_ms,
+                       "l2_policy": "activations of one step exceed L2"},
+            "e2e": {"value": tokens / (e2e_ms * 1e-3) / 1e6, "unit": "Mtokens/s", "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": int((2 if dual else 1) * per_rank * L * 8 + per_rank * 8), "d2h_bytes_per_step": 4},
+            "gpu_launches": launches, "loss": lv}))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=500)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="sweep_L4096_bs64_d05", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="sweep_L4096_bs64_d05", choices=sorted(WORKLOADS) + sorted(TRAIN_WORKLOADS))
     ap.add_argument("--engine", default="auto", choices=["auto", "simt", "tcgen05"])
     ap.add_argument("--mode", default="auto", choices=["auto", "fused", "staged"],
                     help="fused: S/P/dP/dS stay on chip (tcgen05 engine); staged: one kernel per stage")
@@ -208,6 +308,9 @@ def main():
     if world > 1:
         dp.init_from_env("nccl")
     dev = torch.device("cuda", local_rank)
+    if args.workload in TRAIN_WORKLOADS:
+        run_training(args, rank, world, local_rank)
+        return
 
     B, H, L, d, bs, dens, dt = WORKLOADS[args.workload]
     tdt = torch.bfloat16 if dt == "bf16" else torch.float32

@@ -31,10 +31,13 @@ def init_from_env(backend: str | None = None, timeout_s: float = 600.0):
     os.environ.setdefault("MASTER_PORT", "29500")
     if backend is None:
         backend = "nccl" if torch.cuda.is_available() else "gloo"
+    kw = {}
     if backend == "nccl":
-        torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
+        local = int(os.environ.get("LOCAL_RANK", rank))
+        torch.cuda.set_device(local)
+        kw["device_id"] = torch.device("cuda", local)
     if not dist.is_initialized():
-        dist.init_process_group(backend, rank=rank, world_size=world, timeout=timedelta(seconds=timeout_s))
+        dist.init_process_group(backend, rank=rank, world_size=world, timeout=timedelta(seconds=timeout_s), **kw)
     return rank, world
 
 
