@@ -101,7 +101,8 @@ enum {
   SPION_STAGE_FUSED_FWD = 13,  /* tcgen05: S, softmax, P V in one kernel            */
   SPION_STAGE_FUSED_BWD_ROW = 14, /* tcgen05: recompute P, dP, dS, dQ per block row */
   SPION_STAGE_FUSED_BWD_COL = 15, /* tcgen05: transposed tiles, dK and dV per block column */
-  SPION_STAGE_COUNT = 16
+  SPION_STAGE_BWD_ROW = 16,    /* tcgen05: dP, dS and dQ per block row (P read, dS written) */
+  SPION_STAGE_COUNT = 17
 };
 int spion_profile(spion_ctx* ctx, int enable);
 int spion_profile_get(spion_ctx* ctx, int stage, double* total_ms, long long* launches);

@@ -196,7 +196,7 @@ extern "C" int spion_profile_reset(spion_ctx* c) {
 extern "C" const char* spion_stage_name(int stage) {
   static const char* names[SPION_STAGE_COUNT] = {
       "structure", "sddmm_s", "softmax_fwd", "spmm_o", "sddmm_dp", "softmax_bwd", "spmm_dq", "spmm_dk", "spmm_dv",
-      "fused_s_p", "fused_dp_ds", "delta", "spmm_dkdv", "fused_fwd", "fused_bwd_row", "fused_bwd_col"};
+      "fused_s_p", "fused_dp_ds", "delta", "spmm_dkdv", "fused_fwd", "fused_bwd_row", "fused_bwd_col", "bwd_row"};
   return (stage >= 0 && stage < SPION_STAGE_COUNT) ? names[stage] : "?";
 }
 

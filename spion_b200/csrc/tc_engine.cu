@@ -323,6 +323,7 @@ __global__ void __launch_bounds__(128) k_dp_ds(const __grid_constant__ CUtensorM
     }
     delta = acc + __shfl_xor_sync(0xffffffffu, acc, 16);
   }
+  const float nds = -delta * scale;
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -375,7 +376,7 @@ __global__ void __launch_bounds__(128) k_dp_ds(const __grid_constant__ CUtensorM
             for (int u = 0; u < 4; ++u) {
               const float p0 = bf16_lo(w[u]), p1 = bf16_hi(w[u]);
               const float g0 = __uint_as_float(v[cc * 8 + 2 * u]), g1 = __uint_as_float(v[cc * 8 + 2 * u + 1]);
-              w[u] = pack_bf16(p0 * (g0 - delta) * scale, p1 * (g1 - delta) * scale);
+              w[u] = pack_bf16(p0 * fmaf(g0, scale, nds), p1 * fmaf(g1, scale, nds));
             }
             asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
           }
@@ -395,6 +396,227 @@ __global__ void __launch_bounds__(128) k_dp_ds(const __grid_constant__ CUtensorM
   tc_fence_before();
   __syncthreads();
   if (q == 0) tmem_dealloc(tmem, 128);
+}
+
+// =====================================================================================
+// Backward, row side: k_dp_ds plus dQ = dS K in the same CTA.  The K tiles are fetched into the
+// V buffers as soon as the dP MMAs have consumed them (that load overlaps the dS arithmetic),
+// the dS tiles in shared memory feed both the second product and the TMA stores, and for rows of
+// at most 4 blocks the dQ accumulator reuses the TMEM columns of the first dP pair.
+template <int D>
+__global__ void __launch_bounds__(128) k_bwd_row(const __grid_constant__ CUtensorMap tmdO,
+                                                 const __grid_constant__ CUtensorMap tmV,
+                                                 const __grid_constant__ CUtensorMap tmK,
+                                                 const __grid_constant__ CUtensorMap tmP,
+                                                 const __grid_constant__ CUtensorMap tmdS,
+                                                 const __nv_bfloat16* __restrict__ dOg,
+                                                 const __nv_bfloat16* __restrict__ Og, __nv_bfloat16* __restrict__ dQ,
+                                                 const int* __restrict__ row_ptr, const int* __restrict__ col_idx,
+                                                 int L, int nnzb, float scale, int* status) {
+  using T = OpTile<D>;
+  constexpr int NCH = 4;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t sbase = (raw + 1023u) & ~1023u;
+  const uint32_t sA = sbase;                                   // dO tile
+  const uint32_t sB = sA + T::BYTES;                           // V tiles, then K tiles
+  const uint32_t sP = sB + NCH * T::BYTES;                     // P tiles in, dS tiles out
+  const uint32_t bars = sP + NCH * VT_BYTES;
+  const uint32_t bar_v = bars, bar_p = bars + 8, bar_s = bars + 16, bar_k = bars + 24, bar_o = bars + 32, slot = bars + 40;
+  uint32_t* slot_ptr = reinterpret_cast<uint32_t*>(smem_raw + (slot - raw));
+  __shared__ int s_abort;
+
+  const int r = blockIdx.x, bh = blockIdx.y;
+  const int tid = threadIdx.x, q = tid >> 5, lane = tid & 31;
+  const int hf = lane >> 4;
+  const int row = q * 16 + (lane & 15);
+  const int rp = row_ptr[r];
+  const int nblk = row_ptr[r + 1] - rp;
+  const int nchunks = (nblk + NCH - 1) / NCH;
+  const bool single = nblk <= NCH;
+  const uint32_t ncols = single ? 128u : 256u;
+  const uint32_t dq_col = single ? 0u : 128u;
+  bool a_loaded = false;
+
+  auto issue_loads = [&](int ch) {                             // thread 0 only
+    const int t0 = ch * NCH, nt = min(NCH, nblk - t0);
+    mbar_expect_tx(bar_v, (a_loaded ? 0 : T::BYTES) + nt * T::BYTES);
+    if (!a_loaded) tma_load_2d(sA, &tmdO, bar_v, 0, bh * L + r * BS);
+    for (int t = 0; t < nt; ++t) tma_load_2d(sB + t * T::BYTES, &tmV, bar_v, 0, bh * L + col_idx[rp + t0 + t] * BS);
+    mbar_expect_tx(bar_p, nt * VT_BYTES);
+    for (int t = 0; t < nt; ++t)
+      tma_load_2d(sP + t * VT_BYTES, &tmP, bar_p, 0, (int)(((size_t)bh * nnzb + rp + t0 + t) * BS));
+  };
+
+  if (tid == 0) {
+    s_abort = *reinterpret_cast<volatile int*>(status);
+    mbar_init(bar_v, 1);
+    mbar_init(bar_p, 1);
+    mbar_init(bar_s, 1);
+    mbar_init(bar_k, 1);
+    mbar_init(bar_o, 1);
+    fence_barrier_init();
+    if (s_abort == 0 && nblk > 0) issue_loads(0);
+  }
+  a_loaded = true;
+  __syncthreads();
+  if (s_abort != 0) return;
+  if (q == 0) {
+    tmem_alloc(slot, ncols);
+    tmem_relinquish();
+  }
+  float delta;
+  {
+    const size_t off = ((size_t)bh * L + r * BS + row) * D + hf * (D / 2);
+    const uint4* a4 = reinterpret_cast<const uint4*>(dOg + off);
+    const uint4* b4 = reinterpret_cast<const uint4*>(Og + off);
+    float acc = 0.f;
+#pragma unroll
+    for (int u = 0; u < D / 16; ++u) {
+      const uint4 a = a4[u], b = b4[u];
+      acc += bf16_lo(a.x) * bf16_lo(b.x) + bf16_hi(a.x) * bf16_hi(b.x) + bf16_lo(a.y) * bf16_lo(b.y) +
+             bf16_hi(a.y) * bf16_hi(b.y) + bf16_lo(a.z) * bf16_lo(b.z) + bf16_hi(a.z) * bf16_hi(b.z) +
+             bf16_lo(a.w) * bf16_lo(b.w) + bf16_hi(a.w) * bf16_hi(b.w);
+    }
+    delta = acc + __shfl_xor_sync(0xffffffffu, acc, 16);
+  }
+  const float nds = -delta * scale;
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *slot_ptr;
+  const uint32_t t_lane = tmem + ((uint32_t)(q * 32) << 16);
+  constexpr uint32_t IDESC_P = make_idesc_bf16(64, 64, 0, 0);
+  constexpr uint32_t IDESC_Q = make_idesc_bf16(64, D, 0, 1);
+  uint32_t ph_v = 0, ph_p = 0, ph_s = 0, ph_k = 0, ph_o = 0;
+  bool ok = true;
+
+  for (int ch = 0; ch < nchunks && ok; ++ch) {
+    const int t0 = ch * NCH, nt = min(NCH, nblk - t0);
+    if (ch > 0 && tid == 0) {
+      bulk_wait_read_all();                                    // previous dS tiles have left shared memory
+      issue_loads(ch);
+    }
+    if (!__syncthreads_and(mbar_wait(bar_v, ph_v))) { if (tid == 0) report(status, ERR_LOAD_WAIT); ok = false; break; }
+    ph_v ^= 1;
+    if (tid == 0) {
+      tc_fence_after();
+      for (int t = 0; t < nt; ++t) {
+        const uint32_t d_addr = tmem + ((uint32_t)((t & 1) * 16) << 16) + (t >> 1) * 64;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          mma_bf16(d_addr, T::kmajor(sA, kk), T::kmajor(sB + t * T::BYTES, kk), IDESC_P, kk > 0);
+      }
+      mma_commit(bar_s);
+    }
+    const bool w1 = mbar_wait(bar_s, ph_s);
+    if (tid == 0 && w1) {                                      // V consumed: bring K into the same buffers
+      mbar_expect_tx(bar_k, nt * T::BYTES);
+      for (int t = 0; t < nt; ++t) tma_load_2d(sB + t * T::BYTES, &tmK, bar_k, 0, bh * L + col_idx[rp + t0 + t] * BS);
+    }
+    const bool w2 = mbar_wait(bar_p, ph_p);
+    if (!__syncthreads_and(w1 && w2)) { if (tid == 0) report(status, ERR_MMA_WAIT); ok = false; break; }
+    ph_s ^= 1; ph_p ^= 1;
+    tc_fence_after();
+    for (int p = 0; p < 2; ++p) {
+      const int t = 2 * p + hf;
+      const bool mine = t < nt;
+      const uint32_t tile = sP + t * VT_BYTES;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t v[32];
+        tmem_ld32(t_lane + p * 64 + half * 32, v);
+        tmem_ld_wait();
+        if (mine) {
+#pragma unroll
+          for (int cc = 0; cc < 4; ++cc) {
+            const int c = half * 4 + cc;
+            const uint32_t addr = tile + row * 128 + ((c ^ (row & 7)) << 4);
+            uint32_t w[4];
+            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]) : "r"(addr) : "memory");
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const float p0 = bf16_lo(w[u]), p1 = bf16_hi(w[u]);
+              const float g0 = __uint_as_float(v[cc * 8 + 2 * u]), g1 = __uint_as_float(v[cc * 8 + 2 * u + 1]);
+              w[u] = pack_bf16(p0 * fmaf(g0, scale, nds), p1 * fmaf(g1, scale, nds));
+            }
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
+          }
+        }
+      }
+    }
+    fence_proxy_async();
+    tc_fence_before();
+    __syncthreads();
+    if (tid == 0) {
+      for (int t = 0; t < nt; ++t)
+        tma_store_2d(&tmdS, sP + t * VT_BYTES, 0, (int)(((size_t)bh * nnzb + rp + t0 + t) * BS));
+      bulk_commit();
+      if (mbar_wait(bar_k, ph_k)) {
+        tc_fence_after();
+        for (int t = 0; t < nt; ++t) {
+          const uint32_t d_addr = tmem + ((uint32_t)((t & 1) * 16) << 16) + dq_col;
+          const uint32_t first = (ch == 0 && t < 2) ? 0u : 1u;
+#pragma unroll
+          for (int kk = 0; kk < BS / 16; ++kk)
+            mma_bf16(d_addr, ValTile::kmajor(sP + t * VT_BYTES, kk), T::mnmajor(sB + t * T::BYTES, kk), IDESC_Q,
+                     (kk > 0) ? 1u : first);
+        }
+        mma_commit(bar_o);
+      } else {
+        report(status, ERR_LOAD_WAIT);
+      }
+    }
+    ph_k ^= 1;
+    if (!__syncthreads_and(mbar_wait(bar_o, ph_o))) { if (tid == 0) report(status, ERR_MMA2_WAIT); ok = false; break; }
+    ph_o ^= 1;
+    tc_fence_after();
+  }
+
+  if (ok) {
+    const bool odd_valid = nblk >= 2;
+    __nv_bfloat16* dst = dQ + ((size_t)bh * L + r * BS + row) * D + hf * (D / 2);
+#pragma unroll
+    for (int h = 0; h < D / 32; ++h) {
+      uint32_t v[32];
+      if (nblk > 0) {
+        tmem_ld32(t_lane + dq_col + h * 32, v);
+        tmem_ld_wait();
+      }
+      float acc[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const float mine_v = (nblk > 0 && (hf == 0 || odd_valid)) ? __uint_as_float(v[j]) : 0.f;
+        acc[j] = mine_v + __shfl_xor_sync(0xffffffffu, mine_v, 16);
+      }
+      if (D == 64) {
+        if (hf == h) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            uint4 pk;
+            pk.x = pack_bf16(acc[j], acc[j + 1]); pk.y = pack_bf16(acc[j + 2], acc[j + 3]);
+            pk.z = pack_bf16(acc[j + 4], acc[j + 5]); pk.w = pack_bf16(acc[j + 6], acc[j + 7]);
+            *reinterpret_cast<uint4*>(dst + j) = pk;
+          }
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 16; j += 8) {
+          float val[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) val[u] = hf ? acc[16 + j + u] : acc[j + u];
+          uint4 pk;
+          pk.x = pack_bf16(val[0], val[1]); pk.y = pack_bf16(val[2], val[3]);
+          pk.z = pack_bf16(val[4], val[5]); pk.w = pack_bf16(val[6], val[7]);
+          *reinterpret_cast<uint4*>(dst + j) = pk;
+        }
+      }
+    }
+  }
+  if (tid == 0) bulk_wait_read_all();
+  tc_fence_before();
+  __syncthreads();
+  if (q == 0) tmem_dealloc(tmem, ncols);
 }
 
 // =====================================================================================
@@ -542,6 +764,7 @@ int set_attrs() {
   SPION_CUDA_TRY(cudaFuncSetAttribute(k_sddmm_fused<D, 1, NCH_BWD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       (int)smem_sddmm<D>(NCH_BWD)));
   SPION_CUDA_TRY(cudaFuncSetAttribute(k_dp_ds<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dp_ds<D>()));
+  SPION_CUDA_TRY(cudaFuncSetAttribute(k_bwd_row<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dp_ds<D>()));
   SPION_CUDA_TRY(cudaFuncSetAttribute(k_spmm<D, false, NST_N>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       (int)smem_spmm<D>(NST_N, 1)));
   SPION_CUDA_TRY(cudaFuncSetAttribute(k_spmm<D, true, NST_T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -603,44 +826,50 @@ int run_backward(spion_ctx* c, TcState* s, const void* Q, const void* K, const v
   const dim3 grid(c->nb, c->BH);
   int rc;
   prof_mark(c, -1);
-  if (s->stages & 4) {
-    CUtensorMap mdo, mv, mpp, mdss;
-    if ((rc = make_map(s, &mdo, dO, rows, D, BS)) || (rc = make_map(s, &mv, V, rows, D, BS)) ||
-        (rc = make_map(s, &mpp, P, vrows, BS, BS)) || (rc = make_map(s, &mdss, dS, vrows, BS, BS)))
-      return rc;
-    if (s->stages & 32)     // first-generation kernel, kept for comparison
-      k_sddmm_fused<D, 1, NCH_BWD><<<grid, 128, smem_sddmm<D>(NCH_BWD), c->stream>>>(
-          mdo, mv, (__nv_bfloat16*)dS, (const __nv_bfloat16*)P, (const __nv_bfloat16*)dO, (const __nv_bfloat16*)O,
-          nullptr, c->row_ptr, c->col_idx, c->L, c->nnzb, c->scale, 0.f, c->status_dev);
-    else
-      k_dp_ds<D><<<grid, 128, smem_dp_ds<D>(), c->stream>>>(mdo, mv, mpp, mdss, (const __nv_bfloat16*)dO,
-                                                            (const __nv_bfloat16*)O, c->row_ptr, c->col_idx, c->L,
-                                                            c->nnzb, c->scale, c->status_dev);
-    SPION_LAUNCH_CHECK();
-    c->launches += 1;
-    prof_mark(c, SPION_STAGE_FUSED_DP_DS);
-  } else {
-    if (!dP_scratch) return SPION_ERR_ARG;
-    if ((rc = simt_sddmm(SPION_BF16, SPION_F32, dO, rm, V, rm, dP_scratch, vl, p, c->nnzb, c->BH, c->d, c->stream))) return rc;
-    prof_mark(c, SPION_STAGE_SDDMM_DP);
-    if ((rc = softmax_bwd_rows(SPION_BF16, dP_scratch, vl, P, vl, dS, vl, p, c->BH, c->L, c->scale, c->stream))) return rc;
-    prof_mark(c, SPION_STAGE_SOFTMAX_BWD);
-    c->launches += 2;
-  }
-  CUtensorMap mds, mp, mq, mk, mdo;
+  CUtensorMap mds, mp, mq, mk, mdo, mv;
   if ((rc = make_map(s, &mds, dS, vrows, BS, BS)) || (rc = make_map(s, &mp, P, vrows, BS, BS)) ||
       (rc = make_map(s, &mq, Q, rows, D, BS)) || (rc = make_map(s, &mk, K, rows, D, BS)) ||
-      (rc = make_map(s, &mdo, dO, rows, D, BS)))
+      (rc = make_map(s, &mdo, dO, rows, D, BS)) || (rc = make_map(s, &mv, V, rows, D, BS)))
     return rc;
-  if (s->stages & 8) {
-    k_spmm<D, false, NST_N><<<grid, 128, smem_spmm<D>(NST_N, 1), c->stream>>>(
-        mds, mds, mk, mk, (__nv_bfloat16*)dQ, nullptr, c->row_ptr, c->col_idx, nullptr, c->L, c->nnzb, c->status_dev);
+  const bool row_fused = (s->stages & 4) && (s->stages & 8) && !(s->stages & 64);
+  if (row_fused) {
+    k_bwd_row<D><<<grid, 128, smem_dp_ds<D>(), c->stream>>>(mdo, mv, mk, mp, mds, (const __nv_bfloat16*)dO,
+                                                            (const __nv_bfloat16*)O, (__nv_bfloat16*)dQ, c->row_ptr,
+                                                            c->col_idx, c->L, c->nnzb, c->scale, c->status_dev);
     SPION_LAUNCH_CHECK();
+    c->launches += 1;
+    prof_mark(c, SPION_STAGE_BWD_ROW);
   } else {
-    if ((rc = simt_spmm(SPION_BF16, SPION_BF16, false, dS, vl, K, rm, dQ, rm, p, c->BH, c->d, c->stream))) return rc;
+    if (s->stages & 4) {
+      if (s->stages & 32)     // first-generation kernel, kept for comparison
+        k_sddmm_fused<D, 1, NCH_BWD><<<grid, 128, smem_sddmm<D>(NCH_BWD), c->stream>>>(
+            mdo, mv, (__nv_bfloat16*)dS, (const __nv_bfloat16*)P, (const __nv_bfloat16*)dO, (const __nv_bfloat16*)O,
+            nullptr, c->row_ptr, c->col_idx, c->L, c->nnzb, c->scale, 0.f, c->status_dev);
+      else
+        k_dp_ds<D><<<grid, 128, smem_dp_ds<D>(), c->stream>>>(mdo, mv, mp, mds, (const __nv_bfloat16*)dO,
+                                                              (const __nv_bfloat16*)O, c->row_ptr, c->col_idx, c->L,
+                                                              c->nnzb, c->scale, c->status_dev);
+      SPION_LAUNCH_CHECK();
+      c->launches += 1;
+      prof_mark(c, SPION_STAGE_FUSED_DP_DS);
+    } else {
+      if (!dP_scratch) return SPION_ERR_ARG;
+      if ((rc = simt_sddmm(SPION_BF16, SPION_F32, dO, rm, V, rm, dP_scratch, vl, p, c->nnzb, c->BH, c->d, c->stream))) return rc;
+      prof_mark(c, SPION_STAGE_SDDMM_DP);
+      if ((rc = softmax_bwd_rows(SPION_BF16, dP_scratch, vl, P, vl, dS, vl, p, c->BH, c->L, c->scale, c->stream))) return rc;
+      prof_mark(c, SPION_STAGE_SOFTMAX_BWD);
+      c->launches += 2;
+    }
+    if (s->stages & 8) {
+      k_spmm<D, false, NST_N><<<grid, 128, smem_spmm<D>(NST_N, 1), c->stream>>>(
+          mds, mds, mk, mk, (__nv_bfloat16*)dQ, nullptr, c->row_ptr, c->col_idx, nullptr, c->L, c->nnzb, c->status_dev);
+      SPION_LAUNCH_CHECK();
+    } else {
+      if ((rc = simt_spmm(SPION_BF16, SPION_BF16, false, dS, vl, K, rm, dQ, rm, p, c->BH, c->d, c->stream))) return rc;
+    }
+    c->launches += 1;
+    prof_mark(c, SPION_STAGE_SPMM_DQ);
   }
-  c->launches += 1;
-  prof_mark(c, SPION_STAGE_SPMM_DQ);
   if (s->stages & 16) {
     k_spmm<D, true, NST_T><<<grid, 128, smem_spmm<D>(NST_T, 2), c->stream>>>(
         mds, mp, mq, mdo, (__nv_bfloat16*)dK, (__nv_bfloat16*)dV, c->col_ptr, c->row_idx, c->csc_pos, c->L, c->nnzb,
@@ -679,7 +908,7 @@ int tc_engine_prepare(spion_ctx* c) {
   }
   s->encode = (EncodeTiledFn)fn;
   const char* env = getenv("SPION_TC_STAGES");
-  if (env) s->stages = atoi(env) & 0x3f;
+  if (env) s->stages = atoi(env) & 0x7f;
   int rc = (c->d == 64) ? set_attrs<64>() : set_attrs<32>();
   if (!rc) rc = fused_set_attrs(c->d);
   if (rc) { delete s; return rc; }

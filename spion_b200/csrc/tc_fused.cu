@@ -25,7 +25,7 @@ namespace {
 
 constexpr int FWD_THREADS = 128;
 constexpr int FWD_NCH = 4;                 // tiles of a row that fits in one chunk
-constexpr uint32_t FWD_TMEM_COLS = 128;    // S pairs at columns [0,64) and [64,128); O reuses [0,64)
+// TMEM (128 columns): S pairs at [0,64) and [64,128); O overwrites [0,64) once P has been extracted.
 
 template <int D> constexpr size_t fwd_smem_bytes() {
   // Q | K x4 | V x4 | (P x4 only when a K tile is smaller than a P tile) | barriers
@@ -34,6 +34,12 @@ template <int D> constexpr size_t fwd_smem_bytes() {
 
 // Store one 64-value bf16 row into a [64 x 64] K-major SWIZZLE_128B tile (16-byte chunk c of row i
 // sits at chunk c ^ (i & 7)): the image TMA would have produced, readable by tcgen05.mma.
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 __device__ __forceinline__ void store_row_swizzled(uint32_t tile, int i, const uint32_t (&w)[32]) {
 #pragma unroll
   for (int c = 0; c < 8; ++c) {
@@ -96,9 +102,11 @@ __global__ void __launch_bounds__(FWD_THREADS) k_fwd_fused(const __grid_constant
   const bool single = nblk <= FWD_NCH;
   const int CH = single ? FWD_NCH : 2;                         // tiles per chunk
   const int nchunks = (nblk + CH - 1) / CH;
+  constexpr uint32_t ncols = 128u;
+  constexpr uint32_t o_col = 0u;
   bool q_loaded = false;
 
-  // tile t of a chunk: accumulator columns and buffers
+  // tile t of a chunk: accumulator columns (long rows stream one pair through [64,128))
   auto s_col = [&](int t) -> uint32_t { return single ? (uint32_t)(t >> 1) * 64u : 64u; };
   auto issue_loads = [&](int ch, bool with_v) {                // thread 0 only
     const int t0 = ch * CH, nt = min(CH, nblk - t0);
@@ -124,7 +132,7 @@ __global__ void __launch_bounds__(FWD_THREADS) k_fwd_fused(const __grid_constant
   __syncthreads();
   if (s_abort != 0) return;
   if (q == 0) {
-    tmem_alloc(slot, FWD_TMEM_COLS);
+    tmem_alloc(slot, ncols);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -166,6 +174,7 @@ __global__ void __launch_bounds__(FWD_THREADS) k_fwd_fused(const __grid_constant
 
   // ------------------------------------------------------------------ pass A: row maximum
   float m2 = floor_v * LOG2E;
+  float mraw = -INFINITY;
   float l_part = 0.f;
   const int npairs = single ? 2 : 1;
   const bool online = STORE_P && !single;                        // denominator needed before P is written
@@ -185,44 +194,50 @@ __global__ void __launch_bounds__(FWD_THREADS) k_fwd_fused(const __grid_constant
           tmem_ld32(t_lane + s_col(2 * p) + half * 32, v);
           tmem_ld_wait();
           if (mine) {
+            if (!kp) {                                            // the scale is positive: compare raw scores
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              float x = __uint_as_float(v[j]) * sc2;
-              if (kp) x -= kp[c * BS + half * 32 + j] * LOG2E;
-              m2 = fmaxf(m2, x);
+              for (int j = 0; j < 32; j += 2) mraw = fmaxf(mraw, fmaxf(__uint_as_float(v[j]), __uint_as_float(v[j + 1])));
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                m2 = fmaxf(m2, fmaf(__uint_as_float(v[j]), sc2, -kp[c * BS + half * 32 + j] * LOG2E));
             }
           }
         }
       }
     } else {
-      const bool mine = hf < nt;
-      const int c = mine ? col_idx[rp + t0 + hf] : 0;
-      uint32_t v0[32], v1[32];
-      tmem_ld32(t_lane + 64, v0);
-      tmem_ld32(t_lane + 96, v1);
-      tmem_ld_wait();
-      float cm = -INFINITY;
-      if (mine) {
+      for (int p = 0; p < npairs; ++p) {
+        const int t = 2 * p + hf;
+        const bool mine = t < nt;
+        const int c = mine ? col_idx[rp + t0 + t] : 0;
+        uint32_t v0[32], v1[32];
+        tmem_ld32(t_lane + s_col(2 * p), v0);
+        tmem_ld32(t_lane + s_col(2 * p) + 32, v1);
+        tmem_ld_wait();
+        float cm = -INFINITY;
+        if (mine) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          float x0 = __uint_as_float(v0[j]) * sc2, x1 = __uint_as_float(v1[j]) * sc2;
-          if (kp) { x0 -= kp[c * BS + j] * LOG2E; x1 -= kp[c * BS + 32 + j] * LOG2E; }
-          v0[j] = __float_as_uint(x0); v1[j] = __float_as_uint(x1);
-          cm = fmaxf(cm, fmaxf(x0, x1));
+          for (int j = 0; j < 32; ++j) {
+            float x0 = __uint_as_float(v0[j]) * sc2, x1 = __uint_as_float(v1[j]) * sc2;
+            if (kp) { x0 -= kp[c * BS + j] * LOG2E; x1 -= kp[c * BS + 32 + j] * LOG2E; }
+            v0[j] = __float_as_uint(x0); v1[j] = __float_as_uint(x1);
+            cm = fmaxf(cm, fmaxf(x0, x1));
+          }
         }
-      }
-      cm = fmaxf(cm, __shfl_xor_sync(0xffffffffu, cm, 16));
-      const float m_new = fmaxf(m2, cm);
-      float sum = 0.f;
-      if (mine) {
+        cm = fmaxf(cm, __shfl_xor_sync(0xffffffffu, cm, 16));
+        const float m_new = fmaxf(m2, cm);
+        float sum = 0.f;
+        if (mine) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) sum += exp2f(__uint_as_float(v0[j]) - m_new) + exp2f(__uint_as_float(v1[j]) - m_new);
+          for (int j = 0; j < 32; ++j) sum += ex2(__uint_as_float(v0[j]) - m_new) + ex2(__uint_as_float(v1[j]) - m_new);
+        }
+        l_part = l_part * exp2f(m2 - m_new) + sum;
+        m2 = m_new;
       }
-      l_part = l_part * exp2f(m2 - m_new) + sum;
-      m2 = m_new;
     }
     if (!single) { tc_fence_before(); __syncthreads(); }        // the next chunk overwrites these columns
   }
+  m2 = fmaxf(m2, mraw * sc2);
   m2 = fmaxf(m2, __shfl_xor_sync(0xffffffffu, m2, 16));          // both owners of a row agree
   float lse_fixed = 0.f;
   if (online) {
@@ -241,6 +256,44 @@ __global__ void __launch_bounds__(FWD_THREADS) k_fwd_fused(const __grid_constant
       if (!ok) break;
     }
     const int t0 = ch * CH, nt = min(CH, nblk - t0);
+    if (STORE_P && single) {
+      // keep both tiles' exponentials packed in registers, normalise once the denominator is known
+      uint32_t wp[2][32];
+#pragma unroll
+      for (int p = 0; p < npairs; ++p) {
+        const int t = 2 * p + hf;
+        const bool mine = t < nt;
+        const int c = mine ? col_idx[rp + t0 + t] : 0;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t v[32];
+          tmem_ld32(t_lane + s_col(2 * p) + half * 32, v);
+          tmem_ld_wait();
+          if (mine) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 2) {
+              float h0 = m2, h1 = m2;
+              if (kp) { h0 = fmaf(kp[c * BS + half * 32 + j], LOG2E, m2); h1 = fmaf(kp[c * BS + half * 32 + j + 1], LOG2E, m2); }
+              const float e0 = ex2(fmaf(__uint_as_float(v[j]), sc2, -h0)), e1 = ex2(fmaf(__uint_as_float(v[j + 1]), sc2, -h1));
+              l_part += e0 + e1;
+              wp[p][half * 16 + (j >> 1)] = pack_bf16(e0, e1);
+            }
+          }
+        }
+      }
+      const float l = l_part + __shfl_xor_sync(0xffffffffu, l_part, 16) + (float)(L - nblk * BS) * exp2f(-m2);
+      const float inv = 1.0f / l;
+      lse_fixed = m2 + log2f(l);
+#pragma unroll
+      for (int p = 0; p < npairs; ++p) {
+        const int t = 2 * p + hf;
+        if (t < nt) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) wp[p][j] = pack_bf16(bf16_lo(wp[p][j]) * inv, bf16_hi(wp[p][j]) * inv);
+          store_row_swizzled(sP + t * VT_BYTES, row, wp[p]);
+        }
+      }
+    } else {
     for (int p = 0; p < npairs; ++p) {
       const int t = 2 * p + hf;
       const bool mine = t < nt;
@@ -254,15 +307,16 @@ __global__ void __launch_bounds__(FWD_THREADS) k_fwd_fused(const __grid_constant
         if (mine) {
 #pragma unroll
           for (int j = 0; j < 32; j += 2) {
-            float x0 = __uint_as_float(v[j]) * sc2, x1 = __uint_as_float(v[j + 1]) * sc2;
-            if (kp) { x0 -= kp[c * BS + half * 32 + j] * LOG2E; x1 -= kp[c * BS + half * 32 + j + 1] * LOG2E; }
-            const float e0 = exp2f(x0 - m2), e1 = exp2f(x1 - m2);
+            float h0 = m2, h1 = m2;
+            if (kp) { h0 = fmaf(kp[c * BS + half * 32 + j], LOG2E, m2); h1 = fmaf(kp[c * BS + half * 32 + j + 1], LOG2E, m2); }
+            const float e0 = ex2(fmaf(__uint_as_float(v[j]), sc2, -h0)), e1 = ex2(fmaf(__uint_as_float(v[j + 1]), sc2, -h1));
             l_part += e0 + e1;
             w[half * 16 + (j >> 1)] = pack_bf16(e0, e1);
           }
         }
       }
       if (mine) store_row_swizzled(sP + t * VT_BYTES, row, w);
+    }
     }
     fence_proxy_async();                                        // P rows -> visible to the MMA proxy
     tc_fence_before();
@@ -272,7 +326,7 @@ __global__ void __launch_bounds__(FWD_THREADS) k_fwd_fused(const __grid_constant
       if (mbar_wait(bar_v, ph_v)) {
         tc_fence_after();
         for (int t = 0; t < nt; ++t) {
-          const uint32_t d_addr = tmem + ((uint32_t)((t & 1) * 16) << 16);           // O: columns [0, D)
+          const uint32_t d_addr = tmem + ((uint32_t)((t & 1) * 16) << 16) + o_col;
           const uint32_t first = (ch == 0 && t < 2) ? 0u : 1u;                       // first tile of each lane half
 #pragma unroll
           for (int kk = 0; kk < BS / 16; ++kk)
@@ -280,7 +334,7 @@ __global__ void __launch_bounds__(FWD_THREADS) k_fwd_fused(const __grid_constant
                      (kk > 0) ? 1u : first);
         }
         mma_commit(bar_o);
-        if (online) {                                             // these tiles are final: store them now
+        if (STORE_P) {                                            // these tiles are final: store them now
           for (int t = 0; t < nt; ++t)
             tma_store_2d(&tmP, sP + t * VT_BYTES, 0, (int)(((size_t)bh * nnzb + rp + t0 + t) * BS));
           bulk_commit();
@@ -301,43 +355,21 @@ __global__ void __launch_bounds__(FWD_THREADS) k_fwd_fused(const __grid_constant
   // ------------------------------------------------------------------ epilogue
   if (ok) {
     float inv = 1.0f, lse2 = lse_fixed;
-    if (!online) {
+    if (!STORE_P) {
       const float l = l_part + __shfl_xor_sync(0xffffffffu, l_part, 16) + (float)(L - nblk * BS) * exp2f(-m2);
       inv = 1.0f / l;
       lse2 = m2 + log2f(l);
+    } else if (nblk == 0) {
+      lse2 = m2 + log2f((float)L * exp2f(-m2));
     }
     if (hf == 0) lse_out[(size_t)bh * L + r * BS + row] = lse2;
-    if (STORE_P && single && nblk > 0) {
-      // rescale this thread's rows of the unnormalised tiles in place, then store the tiles
-      for (int p = 0; p < 2; ++p) {
-        const int t = 2 * p + hf;
-        if (t < nblk) {
-          const uint32_t tile = sP + t * VT_BYTES;
-#pragma unroll
-          for (int c = 0; c < 8; ++c) {
-            const uint32_t addr = tile + row * 128 + ((c ^ (row & 7)) << 4);
-            uint32_t w0, w1, w2, w3;
-            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(w0), "=r"(w1), "=r"(w2), "=r"(w3) : "r"(addr) : "memory");
-            w0 = pack_bf16(bf16_lo(w0) * inv, bf16_hi(w0) * inv); w1 = pack_bf16(bf16_lo(w1) * inv, bf16_hi(w1) * inv);
-            w2 = pack_bf16(bf16_lo(w2) * inv, bf16_hi(w2) * inv); w3 = pack_bf16(bf16_lo(w3) * inv, bf16_hi(w3) * inv);
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
-          }
-        }
-      }
-      fence_proxy_async();
-      __syncthreads();
-      if (tid == 0) {
-        for (int t = 0; t < nblk; ++t) tma_store_2d(&tmP, sP + t * VT_BYTES, 0, (int)(((size_t)bh * nnzb + rp + t) * BS));
-        bulk_commit();
-      }
-    }
     const bool odd_valid = nblk >= 2;
     __nv_bfloat16* dst = O + ((size_t)bh * L + r * BS + row) * D + hf * (D / 2);
 #pragma unroll
     for (int h = 0; h < D / 32; ++h) {
       uint32_t v[32];
       if (nblk > 0) {
-        tmem_ld32(t_lane + h * 32, v);
+        tmem_ld32(t_lane + o_col + h * 32, v);
         tmem_ld_wait();
       }
       float acc[32];
@@ -376,7 +408,7 @@ __global__ void __launch_bounds__(FWD_THREADS) k_fwd_fused(const __grid_constant
   stamp(7);
   tc_fence_before();
   __syncthreads();
-  if (q == 0) tmem_dealloc(tmem, FWD_TMEM_COLS);
+  if (q == 0) tmem_dealloc(tmem, ncols);
 }
 
 }  // namespace
