@@ -3,10 +3,12 @@
 //
 // Replaces, for the native (block-tile) API, the reference's cuSPARSE calls and SIMT softmax
 // kernels (models/block_attn.cu:453-545):
-//   k_sddmm_fused<MODE 0>   S = Q K^T on the mask  + sparse row softmax  -> P      (:459, :468)
-//   k_spmm<false>           O = P V ; dQ = dS K                                      (:478, :516)
-//   k_sddmm_fused<MODE 1>   dP = dO V^T on the mask + softmax backward   -> dS      (:498, :507)
-//   k_spmm<true>            dK = dS^T Q and dV = P^T dO in one pass over a block column (:526, :536)
+//   k_fwd_fused (tc_fused.cu)  S = Q K^T on the mask, sparse row softmax, O = P V        (:459-478)
+//   k_bwd_row                  dP = dO V^T on the mask, softmax backward -> dS, dQ = dS K  (:498-516)
+//   k_dp_ds + k_spmm<false>    the same two steps as separate kernels (debugging switch)
+//   k_spmm<true>               dK = dS^T Q and dV = P^T dO in one pass over a block column (:526, :536)
+// Masks with 32-wide blocks run on derived 64-wide super-blocks whose unselected quarters are
+// masked inside the forward softmax (P = 0 there, so the backward needs no special handling).
 //
 // Every 64x64 block of the mask is one dense contraction: M = 64 rows (MMA M = 64, accumulator
 // row m lives in TMEM lane (m % 16) + 32 * (m / 16)), N = 64 keys or the head dimension, K in
@@ -28,226 +30,7 @@ using namespace tc;
 namespace {
 
 // =====================================================================================
-// S (or dP) tiles of one block row + fused epilogue.  One CTA per (block row, bh), 128 threads.
-//   MODE 0: P  = softmax row-wise over the selected blocks (reference semantics: the L - n_i
-//                non-selected keys add exp(0 - m) each to the denominator)
-//   MODE 1: dS = P * (dP - delta) * scale,  delta_i = sum_n dO_in O_in
-// NCH tiles (64 TMEM columns each) are produced per chunk.
-template <int D, int MODE, int NCH>
-__global__ void __launch_bounds__(128) k_sddmm_fused(const __grid_constant__ CUtensorMap tmA,
-                                                     const __grid_constant__ CUtensorMap tmB,
-                                                     __nv_bfloat16* __restrict__ out,
-                                                     const __nv_bfloat16* __restrict__ Pin,
-                                                     const __nv_bfloat16* __restrict__ dOg,
-                                                     const __nv_bfloat16* __restrict__ Og,
-                                                     const float* __restrict__ keypad,
-                                                     const int* __restrict__ row_ptr, const int* __restrict__ col_idx,
-                                                     int L, int nnzb, float scale, float floor_v, int* status) {
-  using T = OpTile<D>;
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t sA = sbase;
-  const uint32_t sB = sbase + T::BYTES;
-  const uint32_t bar_load = sB + NCH * T::BYTES;
-  const uint32_t bar_mma = bar_load + 8;
-  const uint32_t slot = bar_mma + 8;
-  uint32_t* slot_ptr = reinterpret_cast<uint32_t*>(smem_raw + (slot - smem_u32(smem_raw)));
-
-  const int r = blockIdx.x, bh = blockIdx.y;
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  constexpr uint32_t TMEM_COLS = NCH * 64 < 32 ? 32 : NCH * 64;
-  __shared__ int s_abort;                                         // an earlier CTA gave up: do not pile on
-  if (tid == 0) s_abort = *reinterpret_cast<volatile int*>(status);
-  __syncthreads();
-  if (s_abort != 0) return;
-
-  if (warp == 0) {
-    tmem_alloc(slot, TMEM_COLS);
-    tmem_relinquish();
-  }
-  if (tid == 0) {
-    mbar_init(bar_load, 1);
-    mbar_init(bar_mma, 1);
-    fence_barrier_init();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = *slot_ptr;
-
-  const int rp = row_ptr[r];
-  const int nblk = row_ptr[r + 1] - rp;
-  const int nchunks = (nblk + NCH - 1) / NCH;
-  const bool active = lane < 16;
-  const int row = warp * 16 + (lane & 15);                       // accumulator row held by this thread
-  const uint32_t tlane = tmem + ((uint32_t)(warp * 32) << 16);
-  constexpr uint32_t IDESC = make_idesc_bf16(64, 64, 0, 0);
-  uint32_t ph_load = 0, ph_mma = 0;
-  bool ok = true;
-  bool a_loaded = false;
-
-  // produce the S tiles of chunk ch into TMEM
-  auto produce = [&](int ch) -> bool {
-    const int t0 = ch * NCH;
-    const int nt = min(NCH, nblk - t0);
-    if (tid == 0) {
-      mbar_expect_tx(bar_load, (a_loaded ? 0 : T::BYTES) + nt * T::BYTES);
-      if (!a_loaded) tma_load_2d(sA, &tmA, bar_load, 0, bh * L + r * BS);
-      for (int t = 0; t < nt; ++t) tma_load_2d(sB + t * T::BYTES, &tmB, bar_load, 0, bh * L + col_idx[rp + t0 + t] * BS);
-    }
-    a_loaded = true;
-    if (!__syncthreads_and(mbar_wait(bar_load, ph_load))) { if (tid == 0) report(status, ERR_LOAD_WAIT); return false; }
-    ph_load ^= 1;
-    if (tid == 0) {
-      tc_fence_after();
-      for (int t = 0; t < nt; ++t) {
-#pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk)
-          mma_bf16(tmem + t * 64, T::kmajor(sA, kk), T::kmajor(sB + t * T::BYTES, kk), IDESC, kk > 0);
-      }
-      mma_commit(bar_mma);
-    }
-    if (!__syncthreads_and(mbar_wait(bar_mma, ph_mma))) { if (tid == 0) report(status, ERR_MMA_WAIT); return false; }
-    ph_mma ^= 1;
-    tc_fence_after();
-    return true;
-  };
-  // all threads are done reading TMEM / smem of the current chunk
-  auto release = [&]() {
-    tc_fence_before();
-    __syncthreads();
-  };
-
-  if (MODE == 0) {
-    const float sc2 = scale * LOG2E;
-    const float* kp = keypad ? keypad + (size_t)bh * L : nullptr;
-    float m2 = floor_v * LOG2E, l = 0.f;
-    // ---- pass 1: row maximum and denominator
-    for (int ch = 0; ch < nchunks && ok; ++ch) {
-      ok = produce(ch);
-      if (!ok) break;
-      const int t0 = ch * NCH, nt = min(NCH, nblk - t0);
-      float cm = m2;
-      for (int t = 0; t < nt; ++t) {
-        const int c = col_idx[rp + t0 + t];
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          uint32_t v[32];
-          tmem_ld32(tlane + t * 64 + half * 32, v);
-          tmem_ld_wait();
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            float x = __uint_as_float(v[j]) * sc2;
-            if (kp) x -= kp[c * BS + half * 32 + j] * LOG2E;
-            cm = fmaxf(cm, x);
-          }
-        }
-      }
-      l *= exp2f(m2 - cm);
-      m2 = cm;
-      for (int t = 0; t < nt; ++t) {
-        const int c = col_idx[rp + t0 + t];
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          uint32_t v[32];
-          tmem_ld32(tlane + t * 64 + half * 32, v);
-          tmem_ld_wait();
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            float x = __uint_as_float(v[j]) * sc2;
-            if (kp) x -= kp[c * BS + half * 32 + j] * LOG2E;
-            l += exp2f(x - m2);
-          }
-        }
-      }
-      if (nchunks > 1) release();
-    }
-    l += (float)(L - nblk * BS) * exp2f(-m2);
-    const float inv = 1.0f / l;
-    // ---- pass 2: write P (TMEM still holds the tiles when the row fits in one chunk)
-    for (int ch = 0; ch < nchunks && ok; ++ch) {
-      if (nchunks > 1) { ok = produce(ch); if (!ok) break; }
-      const int t0 = ch * NCH, nt = min(NCH, nblk - t0);
-      for (int t = 0; t < nt; ++t) {
-        const int blk = rp + t0 + t, c = col_idx[blk];
-        __nv_bfloat16* dst = out + (((size_t)bh * nnzb + blk) * BS + row) * BS;
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          uint32_t v[32];
-          tmem_ld32(tlane + t * 64 + half * 32, v);
-          tmem_ld_wait();
-          uint32_t w[16];
-#pragma unroll
-          for (int j = 0; j < 32; j += 2) {
-            float x0 = __uint_as_float(v[j]) * sc2, x1 = __uint_as_float(v[j + 1]) * sc2;
-            if (kp) { x0 -= kp[c * BS + half * 32 + j] * LOG2E; x1 -= kp[c * BS + half * 32 + j + 1] * LOG2E; }
-            w[j >> 1] = pack_bf16(exp2f(x0 - m2) * inv, exp2f(x1 - m2) * inv);
-          }
-          if (active) {
-            uint4* d4 = reinterpret_cast<uint4*>(dst + half * 32);
-#pragma unroll
-            for (int q = 0; q < 4; ++q) d4[q] = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
-          }
-        }
-      }
-      if (nchunks > 1) release();
-    }
-  } else {
-    // delta of this thread's row
-    float delta = 0.f;
-    if (active) {
-      const uint4* a4 = reinterpret_cast<const uint4*>(dOg + ((size_t)bh * L + r * BS + row) * D);
-      const uint4* b4 = reinterpret_cast<const uint4*>(Og + ((size_t)bh * L + r * BS + row) * D);
-#pragma unroll
-      for (int q = 0; q < D / 8; ++q) {
-        const uint4 a = a4[q], b = b4[q];
-        delta += bf16_lo(a.x) * bf16_lo(b.x) + bf16_hi(a.x) * bf16_hi(b.x) + bf16_lo(a.y) * bf16_lo(b.y) +
-                 bf16_hi(a.y) * bf16_hi(b.y) + bf16_lo(a.z) * bf16_lo(b.z) + bf16_hi(a.z) * bf16_hi(b.z) +
-                 bf16_lo(a.w) * bf16_lo(b.w) + bf16_hi(a.w) * bf16_hi(b.w);
-      }
-    }
-    for (int ch = 0; ch < nchunks && ok; ++ch) {
-      ok = produce(ch);
-      if (!ok) break;
-      const int t0 = ch * NCH, nt = min(NCH, nblk - t0);
-      for (int t = 0; t < nt; ++t) {
-        const int blk = rp + t0 + t;
-        const size_t off = (((size_t)bh * nnzb + blk) * BS + row) * BS;
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          uint32_t v[32];
-          tmem_ld32(tlane + t * 64 + half * 32, v);
-          tmem_ld_wait();
-          if (active) {
-            const uint4* p4 = reinterpret_cast<const uint4*>(Pin + off + half * 32);
-            uint4* d4 = reinterpret_cast<uint4*>(out + off + half * 32);
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const uint4 pw = p4[q];
-              const uint32_t pws[4] = {pw.x, pw.y, pw.z, pw.w};
-              uint32_t o[4];
-#pragma unroll
-              for (int u = 0; u < 4; ++u) {
-                const float p0 = bf16_lo(pws[u]), p1 = bf16_hi(pws[u]);
-                const float g0 = __uint_as_float(v[q * 8 + 2 * u]), g1 = __uint_as_float(v[q * 8 + 2 * u + 1]);
-                o[u] = pack_bf16(p0 * (g0 - delta) * scale, p1 * (g1 - delta) * scale);
-              }
-              d4[q] = make_uint4(o[0], o[1], o[2], o[3]);
-            }
-          }
-        }
-      }
-      release();
-    }
-  }
-
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 0) tmem_dealloc(tmem, TMEM_COLS);
-}
-
-// =====================================================================================
-// dP tiles of one block row + softmax backward -> dS, second generation of MODE 1 above:
+// dP tiles of one block row + softmax backward -> dS (used when the row kernel below is split):
 // 4 warps (one per TMEM quadrant), two tiles per 64 columns (lane halves 0-15 / 16-31) so every
 // lane owns a row, operands requested before TMEM is set up, P tiles brought in by TMA and the
 // dS tiles written over them in shared memory and sent out by TMA stores (full-line writes).
@@ -751,18 +534,59 @@ __global__ void __launch_bounds__(128) k_spmm(const __grid_constant__ CUtensorMa
 
 // =====================================================================================
 // host side
-constexpr int NCH_FWD = 4, NCH_BWD = 4, NST_N = 4, NST_T = 2;
+// ---------------------------------------------------------------- 32-wide masks on 64-wide super-blocks
+__global__ void k_mat64_from_mat32(const uint8_t* __restrict__ mat32, int nb32, uint8_t* __restrict__ mat64) {
+  const int nb64 = nb32 / 2;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < nb64 * nb64; i += gridDim.x * blockDim.x) {
+    const int R = i / nb64, C = i % nb64;
+    const uint8_t* m = mat32 + (size_t)(2 * R) * nb32 + 2 * C;
+    mat64[i] = (m[0] | m[1] | m[nb32] | m[nb32 + 1]) ? 1 : 0;
+  }
+}
+__global__ void k_submask(const uint8_t* __restrict__ mat32, int nb32, const int32_t* __restrict__ blk_row64,
+                          const int32_t* __restrict__ col_idx64, const int32_t* __restrict__ nnzb64,
+                          uint8_t* __restrict__ submask) {
+  const int n = *nnzb64;
+  for (int b = blockIdx.x * blockDim.x + threadIdx.x; b < n; b += gridDim.x * blockDim.x) {
+    const uint8_t* m = mat32 + (size_t)(2 * blk_row64[b]) * nb32 + 2 * col_idx64[b];
+    submask[b] = (uint8_t)((m[0] ? 1 : 0) | (m[1] ? 2 : 0) | (m[nb32] ? 4 : 0) | (m[nb32 + 1] ? 8 : 0));
+  }
+}
+// value tiles: [BH, nnzb64, 64, 64] super-tiles <-> [BH, nnzb32, 32, 32] tiles of the mask's own blocks.
+// One CTA per (super-block, bh); id32 maps a cell of the 32-wide mask to its CSR block id.
+template <bool TO64>
+__global__ void __launch_bounds__(256) k_convert_tiles(__nv_bfloat16* __restrict__ v64, __nv_bfloat16* __restrict__ v32,
+                                                       const int32_t* __restrict__ blk_row64,
+                                                       const int32_t* __restrict__ col_idx64,
+                                                       const uint8_t* __restrict__ submask,
+                                                       const int32_t* __restrict__ id32, int nb32, int nnzb64,
+                                                       int nnzb32) {
+  const int b64 = blockIdx.x, bh = blockIdx.y;
+  const int R = blk_row64[b64], C = col_idx64[b64];
+  const uint8_t sm = submask[b64];
+  __nv_bfloat16* t64 = v64 + ((size_t)bh * nnzb64 + b64) * 4096;
+  for (int e = threadIdx.x; e < 4096 / 8; e += blockDim.x) {           // 8 elements (16 bytes) per step
+    const int i = e / 8, j8 = (e % 8) * 8;
+    const int a = i / 32, bq = j8 / 32;
+    const bool on = (sm >> (a * 2 + bq)) & 1;
+    uint4 val = make_uint4(0, 0, 0, 0);
+    if (on) {
+      const int b32 = id32[(size_t)(2 * R + a) * nb32 + 2 * C + bq];
+      __nv_bfloat16* t32 = v32 + ((size_t)bh * nnzb32 + b32) * 1024 + (i % 32) * 32 + (j8 % 32);
+      if (TO64) val = *reinterpret_cast<const uint4*>(t32);
+      else *reinterpret_cast<uint4*>(t32) = *reinterpret_cast<const uint4*>(t64 + i * 64 + j8);
+    }
+    if (TO64) *reinterpret_cast<uint4*>(t64 + i * 64 + j8) = val;
+  }
+}
 
-template <int D> constexpr size_t smem_sddmm(int nch) { return 1024 + (size_t)(1 + nch) * OpTile<D>::BYTES + 64; }
+constexpr int NST_N = 4, NST_T = 2;
+
 template <int D> constexpr size_t smem_dp_ds() { return 1024 + (size_t)5 * OpTile<D>::BYTES + 4 * VT_BYTES + 64; }
 template <int D> constexpr size_t smem_spmm(int nst, int np) { return 1024 + (size_t)nst * np * (VT_BYTES + OpTile<D>::BYTES) + 64; }
 
 template <int D>
 int set_attrs() {
-  SPION_CUDA_TRY(cudaFuncSetAttribute(k_sddmm_fused<D, 0, NCH_FWD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      (int)smem_sddmm<D>(NCH_FWD)));
-  SPION_CUDA_TRY(cudaFuncSetAttribute(k_sddmm_fused<D, 1, NCH_BWD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      (int)smem_sddmm<D>(NCH_BWD)));
   SPION_CUDA_TRY(cudaFuncSetAttribute(k_dp_ds<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dp_ds<D>()));
   SPION_CUDA_TRY(cudaFuncSetAttribute(k_bwd_row<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dp_ds<D>()));
   SPION_CUDA_TRY(cudaFuncSetAttribute(k_spmm<D, false, NST_N>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -772,200 +596,188 @@ int set_attrs() {
   return SPION_OK;
 }
 
-template <int D>
-int run_forward(spion_ctx* c, TcState* s, const void* Q, const void* K, const void* V, const float* keypad, void* P,
-                void* O, float* S_scratch) {
-  const Pattern p = ctx_pattern(c);
-  const uint64_t rows = (uint64_t)c->BH * c->L, vrows = (uint64_t)c->BH * c->nnzb * BS;
-  const long long nnz = (long long)c->nnzb * BS * BS;
-  const ValueLayout vl{VAL_BLOCKTILE, c->L, nnz};
-  const OperandLayout rm = row_major_operand(c->L, c->d);
-  const dim3 grid(c->nb, c->BH);
-  int rc;
-  prof_mark(c, -1);
-  if (s->stages & 1) {
-    CUtensorMap mq, mk;
-    if ((rc = make_map(s, &mq, Q, rows, D, BS)) || (rc = make_map(s, &mk, K, rows, D, BS))) return rc;
-    k_sddmm_fused<D, 0, NCH_FWD><<<grid, 128, smem_sddmm<D>(NCH_FWD), c->stream>>>(
-        mq, mk, (__nv_bfloat16*)P, nullptr, nullptr, nullptr, keypad, c->row_ptr, c->col_idx, c->L, c->nnzb, c->scale,
-        keypad ? 0.0f : -100.0f, c->status_dev);
-    SPION_LAUNCH_CHECK();
-    c->launches += 1;
-    prof_mark(c, SPION_STAGE_FUSED_S_P);
-  } else {
-    if (!S_scratch) return SPION_ERR_ARG;
-    if ((rc = simt_sddmm(SPION_BF16, SPION_F32, Q, rm, K, rm, S_scratch, vl, p, c->nnzb, c->BH, c->d, c->stream))) return rc;
-    prof_mark(c, SPION_STAGE_SDDMM_S);
-    if ((rc = softmax_fwd_rows(SPION_BF16, S_scratch, vl, P, vl, p, c->BH, c->L, c->scale, keypad,
-                               keypad ? 0.0f : -100.0f, c->stream))) return rc;
-    prof_mark(c, SPION_STAGE_SOFTMAX_FWD);
-    c->launches += 2;
-  }
-  if (s->stages & 2) {
-    CUtensorMap mp, mv;
-    if ((rc = make_map(s, &mp, P, vrows, BS, BS)) || (rc = make_map(s, &mv, V, rows, D, BS))) return rc;
-    k_spmm<D, false, NST_N><<<grid, 128, smem_spmm<D>(NST_N, 1), c->stream>>>(
-        mp, mp, mv, mv, (__nv_bfloat16*)O, nullptr, c->row_ptr, c->col_idx, nullptr, c->L, c->nnzb, c->status_dev);
-    SPION_LAUNCH_CHECK();
-  } else {
-    if ((rc = simt_spmm(SPION_BF16, SPION_BF16, false, P, vl, V, rm, O, rm, p, c->BH, c->d, c->stream))) return rc;
-  }
+int convert_tiles(spion_ctx* c, TcState* s, bool to64, void* v64, void* v32) {
+  const dim3 grid(s->nnzb64, c->BH);
+  if (to64)
+    k_convert_tiles<true><<<grid, 256, 0, c->stream>>>((__nv_bfloat16*)v64, (__nv_bfloat16*)v32, s->blk_row64,
+                                                       s->col_idx64, s->submask, c->work, c->nb, s->nnzb64, c->nnzb);
+  else
+    k_convert_tiles<false><<<grid, 256, 0, c->stream>>>((__nv_bfloat16*)v64, (__nv_bfloat16*)v32, s->blk_row64,
+                                                        s->col_idx64, s->submask, c->work, c->nb, s->nnzb64, c->nnzb);
+  SPION_LAUNCH_CHECK();
   c->launches += 1;
-  prof_mark(c, SPION_STAGE_SPMM_O);
   return SPION_OK;
 }
 
 template <int D>
-int run_backward(spion_ctx* c, TcState* s, const void* Q, const void* K, const void* V, const void* P, const void* O,
-                 const void* dO, void* dS, float* dP_scratch, void* dQ, void* dK, void* dV) {
-  const Pattern p = ctx_pattern(c);
-  const uint64_t rows = (uint64_t)c->BH * c->L, vrows = (uint64_t)c->BH * c->nnzb * BS;
-  const long long nnz = (long long)c->nnzb * BS * BS;
-  const ValueLayout vl{VAL_BLOCKTILE, c->L, nnz};
-  const OperandLayout rm = row_major_operand(c->L, c->d);
-  const dim3 grid(c->nb, c->BH);
+int run_backward(spion_ctx* c, TcState* s, const void* Q, const void* K, const void* V, const void* P_user,
+                 const void* O, const void* dO, void* dS_user, void* dQ, void* dK, void* dV) {
+  const TcView vw = tc_view(c, s);
+  const void* P = P_user;
+  void* dS = dS_user;
   int rc;
+  if (s->super) {                    // bring the caller's 32-wide tiles into super-tile form
+    if ((rc = convert_tiles(c, s, true, s->p64_ws, const_cast<void*>(P_user)))) return rc;
+    P = s->p64_ws;
+    dS = s->ds64_ws;
+  }
+  const uint64_t rows = (uint64_t)c->BH * c->L, vrows = (uint64_t)c->BH * vw.nnzb * BS;
+  const dim3 grid(vw.nb, c->BH);
   prof_mark(c, -1);
   CUtensorMap mds, mp, mq, mk, mdo, mv;
   if ((rc = make_map(s, &mds, dS, vrows, BS, BS)) || (rc = make_map(s, &mp, P, vrows, BS, BS)) ||
       (rc = make_map(s, &mq, Q, rows, D, BS)) || (rc = make_map(s, &mk, K, rows, D, BS)) ||
       (rc = make_map(s, &mdo, dO, rows, D, BS)) || (rc = make_map(s, &mv, V, rows, D, BS)))
     return rc;
-  const bool row_fused = (s->stages & 4) && (s->stages & 8) && !(s->stages & 64);
-  if (row_fused) {
+  if (!(s->stages & 64)) {
     k_bwd_row<D><<<grid, 128, smem_dp_ds<D>(), c->stream>>>(mdo, mv, mk, mp, mds, (const __nv_bfloat16*)dO,
-                                                            (const __nv_bfloat16*)O, (__nv_bfloat16*)dQ, c->row_ptr,
-                                                            c->col_idx, c->L, c->nnzb, c->scale, c->status_dev);
+                                                            (const __nv_bfloat16*)O, (__nv_bfloat16*)dQ, vw.row_ptr,
+                                                            vw.col_idx, c->L, vw.nnzb, c->scale, c->status_dev);
     SPION_LAUNCH_CHECK();
     c->launches += 1;
     prof_mark(c, SPION_STAGE_BWD_ROW);
   } else {
-    if (s->stages & 4) {
-      if (s->stages & 32)     // first-generation kernel, kept for comparison
-        k_sddmm_fused<D, 1, NCH_BWD><<<grid, 128, smem_sddmm<D>(NCH_BWD), c->stream>>>(
-            mdo, mv, (__nv_bfloat16*)dS, (const __nv_bfloat16*)P, (const __nv_bfloat16*)dO, (const __nv_bfloat16*)O,
-            nullptr, c->row_ptr, c->col_idx, c->L, c->nnzb, c->scale, 0.f, c->status_dev);
-      else
-        k_dp_ds<D><<<grid, 128, smem_dp_ds<D>(), c->stream>>>(mdo, mv, mp, mds, (const __nv_bfloat16*)dO,
-                                                              (const __nv_bfloat16*)O, c->row_ptr, c->col_idx, c->L,
-                                                              c->nnzb, c->scale, c->status_dev);
-      SPION_LAUNCH_CHECK();
-      c->launches += 1;
-      prof_mark(c, SPION_STAGE_FUSED_DP_DS);
-    } else {
-      if (!dP_scratch) return SPION_ERR_ARG;
-      if ((rc = simt_sddmm(SPION_BF16, SPION_F32, dO, rm, V, rm, dP_scratch, vl, p, c->nnzb, c->BH, c->d, c->stream))) return rc;
-      prof_mark(c, SPION_STAGE_SDDMM_DP);
-      if ((rc = softmax_bwd_rows(SPION_BF16, dP_scratch, vl, P, vl, dS, vl, p, c->BH, c->L, c->scale, c->stream))) return rc;
-      prof_mark(c, SPION_STAGE_SOFTMAX_BWD);
-      c->launches += 2;
-    }
-    if (s->stages & 8) {
-      k_spmm<D, false, NST_N><<<grid, 128, smem_spmm<D>(NST_N, 1), c->stream>>>(
-          mds, mds, mk, mk, (__nv_bfloat16*)dQ, nullptr, c->row_ptr, c->col_idx, nullptr, c->L, c->nnzb, c->status_dev);
-      SPION_LAUNCH_CHECK();
-    } else {
-      if ((rc = simt_spmm(SPION_BF16, SPION_BF16, false, dS, vl, K, rm, dQ, rm, p, c->BH, c->d, c->stream))) return rc;
-    }
-    c->launches += 1;
+    k_dp_ds<D><<<grid, 128, smem_dp_ds<D>(), c->stream>>>(mdo, mv, mp, mds, (const __nv_bfloat16*)dO,
+                                                          (const __nv_bfloat16*)O, vw.row_ptr, vw.col_idx, c->L,
+                                                          vw.nnzb, c->scale, c->status_dev);
+    SPION_LAUNCH_CHECK();
+    prof_mark(c, SPION_STAGE_FUSED_DP_DS);
+    k_spmm<D, false, NST_N><<<grid, 128, smem_spmm<D>(NST_N, 1), c->stream>>>(
+        mds, mds, mk, mk, (__nv_bfloat16*)dQ, nullptr, vw.row_ptr, vw.col_idx, nullptr, c->L, vw.nnzb, c->status_dev);
+    SPION_LAUNCH_CHECK();
+    c->launches += 2;
     prof_mark(c, SPION_STAGE_SPMM_DQ);
   }
-  if (s->stages & 16) {
-    k_spmm<D, true, NST_T><<<grid, 128, smem_spmm<D>(NST_T, 2), c->stream>>>(
-        mds, mp, mq, mdo, (__nv_bfloat16*)dK, (__nv_bfloat16*)dV, c->col_ptr, c->row_idx, c->csc_pos, c->L, c->nnzb,
-        c->status_dev);
-    SPION_LAUNCH_CHECK();
-    c->launches += 1;
-    prof_mark(c, SPION_STAGE_SPMM_DKDV);
-  } else {
-    if ((rc = simt_spmm(SPION_BF16, SPION_BF16, true, dS, vl, Q, rm, dK, rm, p, c->BH, c->d, c->stream))) return rc;
-    prof_mark(c, SPION_STAGE_SPMM_DK);
-    if ((rc = simt_spmm(SPION_BF16, SPION_BF16, true, P, vl, dO, rm, dV, rm, p, c->BH, c->d, c->stream))) return rc;
-    prof_mark(c, SPION_STAGE_SPMM_DV);
-    c->launches += 2;
+  k_spmm<D, true, NST_T><<<grid, 128, smem_spmm<D>(NST_T, 2), c->stream>>>(
+      mds, mp, mq, mdo, (__nv_bfloat16*)dK, (__nv_bfloat16*)dV, vw.col_ptr, vw.row_idx, vw.csc_pos, c->L, vw.nnzb,
+      c->status_dev);
+  SPION_LAUNCH_CHECK();
+  c->launches += 1;
+  prof_mark(c, SPION_STAGE_SPMM_DKDV);
+  return SPION_OK;
+}
+
+void free_super(TcState* s) {
+  cudaFree(s->mat64); cudaFree(s->submask); cudaFree(s->row_ptr64); cudaFree(s->col_idx64); cudaFree(s->blk_row64);
+  cudaFree(s->col_ptr64); cudaFree(s->row_idx64); cudaFree(s->csc_pos64); cudaFree(s->work64); cudaFree(s->nnzb64_dev);
+  cudaFree(s->p64_ws); cudaFree(s->ds64_ws);
+  s->mat64 = s->submask = nullptr;
+  s->row_ptr64 = s->col_idx64 = s->blk_row64 = s->col_ptr64 = s->row_idx64 = s->csc_pos64 = s->work64 = s->nnzb64_dev = nullptr;
+  s->p64_ws = s->ds64_ws = nullptr;
+  s->ws_elems = 0;
+}
+
+// derive the super-block structure of a 32-wide mask (set_pattern time; synchronises once)
+int build_super(spion_ctx* c, TcState* s) {
+  const int nb64 = c->nb / 2;
+  const size_t cap = (size_t)nb64 * nb64;
+  if (!s->mat64) {
+    bool ok = cudaMalloc(&s->mat64, cap) == cudaSuccess && cudaMalloc(&s->submask, cap) == cudaSuccess &&
+              cudaMalloc(&s->row_ptr64, (nb64 + 1) * 4) == cudaSuccess && cudaMalloc(&s->col_idx64, cap * 4) == cudaSuccess &&
+              cudaMalloc(&s->blk_row64, cap * 4) == cudaSuccess && cudaMalloc(&s->col_ptr64, (nb64 + 1) * 4) == cudaSuccess &&
+              cudaMalloc(&s->row_idx64, cap * 4) == cudaSuccess && cudaMalloc(&s->csc_pos64, cap * 4) == cudaSuccess &&
+              cudaMalloc(&s->work64, cap * 4) == cudaSuccess && cudaMalloc(&s->nnzb64_dev, 4) == cudaSuccess;
+    if (!ok) return SPION_ERR_ALLOC;
   }
+  s->nb64 = nb64;
+  k_mat64_from_mat32<<<64, 256, 0, c->stream>>>(c->mat, c->nb, s->mat64);
+  SPION_LAUNCH_CHECK();
+  int rc = spion_launch_build_structure(s->mat64, nb64, s->nnzb64_dev, s->row_ptr64, s->col_idx64, s->blk_row64,
+                                        s->col_ptr64, s->row_idx64, s->csc_pos64, s->work64, c->stream);
+  if (rc) return rc;
+  k_submask<<<64, 256, 0, c->stream>>>(c->mat, c->nb, s->blk_row64, s->col_idx64, s->nnzb64_dev, s->submask);
+  SPION_LAUNCH_CHECK();
+  int32_t n = 0;
+  SPION_CUDA_TRY(cudaMemcpyAsync(&n, s->nnzb64_dev, 4, cudaMemcpyDeviceToHost, c->stream));
+  SPION_CUDA_TRY(cudaStreamSynchronize(c->stream));
+  s->nnzb64 = n;
+  const size_t need = (size_t)c->BH * n * 4096;
+  if (need > s->ws_elems) {
+    cudaFree(s->p64_ws); cudaFree(s->ds64_ws);
+    s->p64_ws = s->ds64_ws = nullptr;
+    if (cudaMalloc(&s->p64_ws, need * 2) != cudaSuccess || cudaMalloc(&s->ds64_ws, need * 2) != cudaSuccess)
+      return SPION_ERR_ALLOC;
+    s->ws_elems = need;
+  }
+  c->launches += 3;
   return SPION_OK;
 }
 
 }  // namespace
 
 bool tc_engine_supports(const spion_ctx* c) {
-  return c->dtype == SPION_BF16 && c->bs == BS && (c->d == 64 || c->d == 32) &&
+  const bool blocks = c->bs == BS || (c->bs == 32 && c->L % 64 == 0);
+  return c->dtype == SPION_BF16 && blocks && (c->d == 64 || c->d == 32) &&
          (c->kind == SPION_KIND_BLOCK || c->kind == SPION_KIND_BLOCK_KPM) && c->BH <= 65535 &&
          (unsigned long long)c->BH * c->L < 0x7fffffffULL;
 }
 
 int tc_engine_prepare(spion_ctx* c) {
-  if (c->tc) return SPION_OK;
-  TcState* s = new TcState();
-  void* fn = nullptr;
-  cudaDriverEntryPointQueryResult q;
-  cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
-  if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || !fn) {
-    fprintf(stderr, "spion_b200: cuTensorMapEncodeTiled is not available from this driver\n");
-    delete s;
-    return SPION_ERR_CUDA;
+  TcState* s = (TcState*)c->tc;
+  if (!s) {
+    s = new TcState();
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+    if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || !fn) {
+      fprintf(stderr, "spion_b200: cuTensorMapEncodeTiled is not available from this driver\n");
+      delete s;
+      return SPION_ERR_CUDA;
+    }
+    s->encode = (EncodeTiledFn)fn;
+    const char* env = getenv("SPION_TC_STAGES");
+    if (env) s->stages = atoi(env);
+    int rc = (c->d == 64) ? set_attrs<64>() : set_attrs<32>();
+    if (!rc) rc = fused_set_attrs(c->d);
+    if (!rc && cudaMalloc(&s->lse_ws, (size_t)c->BH * c->L * sizeof(float)) != cudaSuccess) rc = SPION_ERR_ALLOC;
+    if (rc) { delete s; return rc; }
+    s->super = c->bs == 32;
+    c->tc = s;
   }
-  s->encode = (EncodeTiledFn)fn;
-  const char* env = getenv("SPION_TC_STAGES");
-  if (env) s->stages = atoi(env) & 0x7f;
-  int rc = (c->d == 64) ? set_attrs<64>() : set_attrs<32>();
-  if (!rc) rc = fused_set_attrs(c->d);
-  if (rc) { delete s; return rc; }
-  c->tc = s;
+  if (s->super) return build_super(c, s);
   return SPION_OK;
 }
 
 void tc_engine_release(spion_ctx* c) {
-  if (c->tc) { delete (TcState*)c->tc; c->tc = nullptr; }
+  if (!c->tc) return;
+  TcState* s = (TcState*)c->tc;
+  free_super(s);
+  cudaFree(s->lse_ws);
+  delete s;
+  c->tc = nullptr;
+}
+
+// forward with the probabilities in the caller's tile layout (P_user may be NULL)
+static int forward_any(spion_ctx* c, const void* Q, const void* K, const void* V, const float* keypad, void* O,
+                       float* lse, void* P_user) {
+  TcState* s = (TcState*)c->tc;
+  if (!s) return SPION_ERR_STATE;
+  if (c->nnzb == 0) return SPION_ERR_SHAPE;
+  void* P64 = P_user ? (s->super ? s->p64_ws : P_user) : nullptr;
+  int rc = fused_forward(c, s, Q, K, V, keypad, O, lse ? lse : s->lse_ws, P64);
+  if (rc || !P_user || !s->super) return rc;
+  return convert_tiles(c, s, false, s->p64_ws, P_user);
 }
 
 int tc_engine_forward(spion_ctx* c, const void* Q, const void* K, const void* V, const float* keypad, void* P, void* O,
                       float* S_scratch) {
-  if (!c->tc) return SPION_ERR_STATE;
-  TcState* s = (TcState*)c->tc;
-  if (c->nnzb == 0) return SPION_ERR_SHAPE;
-  return c->d == 64 ? run_forward<64>(c, s, Q, K, V, keypad, P, O, S_scratch)
-                    : run_forward<32>(c, s, Q, K, V, keypad, P, O, S_scratch);
+  (void)S_scratch;
+  return forward_any(c, Q, K, V, keypad, O, nullptr, P);
 }
 
 int tc_engine_backward(spion_ctx* c, const void* Q, const void* K, const void* V, const void* P, const void* O,
                        const void* dO, void* dS, float* dP_scratch, void* dQ, void* dK, void* dV) {
+  (void)dP_scratch;
   if (!c->tc) return SPION_ERR_STATE;
   TcState* s = (TcState*)c->tc;
   if (c->nnzb == 0) return SPION_ERR_SHAPE;
-  return c->d == 64 ? run_backward<64>(c, s, Q, K, V, P, O, dO, dS, dP_scratch, dQ, dK, dV)
-                    : run_backward<32>(c, s, Q, K, V, P, O, dO, dS, dP_scratch, dQ, dK, dV);
+  return c->d == 64 ? run_backward<64>(c, s, Q, K, V, P, O, dO, dS, dQ, dK, dV)
+                    : run_backward<32>(c, s, Q, K, V, P, O, dO, dS, dQ, dK, dV);
 }
-
-namespace tc {
-int tc_engine_probabilities(spion_ctx* c, const void* Q, const void* K, const float* keypad, void* P) {
-  TcState* s = (TcState*)c->tc;
-  const uint64_t rows = (uint64_t)c->BH * c->L;
-  CUtensorMap mq, mk;
-  int rc;
-  if ((rc = make_map(s, &mq, Q, rows, (uint32_t)c->d, BS)) || (rc = make_map(s, &mk, K, rows, (uint32_t)c->d, BS))) return rc;
-  const dim3 grid(c->nb, c->BH);
-  if (c->d == 64)
-    k_sddmm_fused<64, 0, NCH_FWD><<<grid, 128, smem_sddmm<64>(NCH_FWD), c->stream>>>(
-        mq, mk, (__nv_bfloat16*)P, nullptr, nullptr, nullptr, keypad, c->row_ptr, c->col_idx, c->L, c->nnzb, c->scale,
-        keypad ? 0.0f : -100.0f, c->status_dev);
-  else
-    k_sddmm_fused<32, 0, NCH_FWD><<<grid, 128, smem_sddmm<32>(NCH_FWD), c->stream>>>(
-        mq, mk, (__nv_bfloat16*)P, nullptr, nullptr, nullptr, keypad, c->row_ptr, c->col_idx, c->L, c->nnzb, c->scale,
-        keypad ? 0.0f : -100.0f, c->status_dev);
-  SPION_LAUNCH_CHECK();
-  c->launches += 1;
-  prof_mark(c, SPION_STAGE_FUSED_S_P);
-  return SPION_OK;
-}
-}  // namespace tc
 
 int tc_engine_forward_fused(spion_ctx* c, const void* Q, const void* K, const void* V, const float* keypad, void* O,
                             float* lse, void* P_optional) {
-  if (!c->tc) return SPION_ERR_STATE;
-  if (c->nnzb == 0) return SPION_ERR_SHAPE;
-  return fused_forward(c, (TcState*)c->tc, Q, K, V, keypad, O, lse, P_optional);
+  return forward_any(c, Q, K, V, keypad, O, lse, P_optional);
 }
 
 int tc_engine_backward_fused(spion_ctx* c, const void* Q, const void* K, const void* V, const float* keypad,

@@ -59,7 +59,7 @@ __device__ __forceinline__ void store_row_swizzled(uint32_t tile, int i, const u
 // STORE_P: also write the normalised probabilities as [64 x 64] bf16 tiles (TMA store from the shared
 // memory tiles the second product reads): rows of one chunk are rescaled in place once the
 // denominator is known; longer rows accumulate the denominator on line in pass A instead.
-template <int D, bool STORE_P>
+template <int D, bool STORE_P, bool SUB>
 __global__ void __launch_bounds__(FWD_THREADS) k_fwd_fused(const __grid_constant__ CUtensorMap tmQ,
                                                            const __grid_constant__ CUtensorMap tmK,
                                                            const __grid_constant__ CUtensorMap tmV,
@@ -67,7 +67,8 @@ __global__ void __launch_bounds__(FWD_THREADS) k_fwd_fused(const __grid_constant
                                                            __nv_bfloat16* __restrict__ O, float* __restrict__ lse_out,
                                                            const float* __restrict__ keypad,
                                                            const int* __restrict__ row_ptr,
-                                                           const int* __restrict__ col_idx, int L, int nnzb,
+                                                           const int* __restrict__ col_idx,
+                                                           const uint8_t* __restrict__ submask, int L, int nnzb,
                                                            float scale, float floor_v, int* status,
                                                            unsigned long long* trace) {
   using T = OpTile<D>;
@@ -99,6 +100,14 @@ __global__ void __launch_bounds__(FWD_THREADS) k_fwd_fused(const __grid_constant
 
   const int rp = row_ptr[r];
   const int nblk = row_ptr[r + 1] - rp;
+  // 32-wide masks: bit (2*(row/32) + col/32) of submask[block] tells whether that quarter is selected
+  const int rh2 = (q >> 1) * 2;
+  auto quarter_ok = [&](int blk, int half) -> bool { return !SUB || ((submask[blk] >> (rh2 + half)) & 1); };
+  int n_sel = nblk * BS;                                       // selected keys of this thread's row
+  if (SUB) {
+    n_sel = 0;
+    for (int t = 0; t < nblk; ++t) n_sel += 32 * __popc((submask[rp + t] >> rh2) & 3);
+  }
   const bool single = nblk <= FWD_NCH;
   const int CH = single ? FWD_NCH : 2;                         // tiles per chunk
   const int nchunks = (nblk + CH - 1) / CH;
@@ -193,7 +202,7 @@ __global__ void __launch_bounds__(FWD_THREADS) k_fwd_fused(const __grid_constant
           uint32_t v[32];
           tmem_ld32(t_lane + s_col(2 * p) + half * 32, v);
           tmem_ld_wait();
-          if (mine) {
+          if (mine && quarter_ok(rp + t0 + t, half)) {
             if (!kp) {                                            // the scale is positive: compare raw scores
 #pragma unroll
               for (int j = 0; j < 32; j += 2) mraw = fmaxf(mraw, fmaxf(__uint_as_float(v[j]), __uint_as_float(v[j + 1])));
@@ -216,10 +225,13 @@ __global__ void __launch_bounds__(FWD_THREADS) k_fwd_fused(const __grid_constant
         tmem_ld_wait();
         float cm = -INFINITY;
         if (mine) {
+          const bool ok0 = quarter_ok(rp + t0 + t, 0), ok1 = quarter_ok(rp + t0 + t, 1);
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             float x0 = __uint_as_float(v0[j]) * sc2, x1 = __uint_as_float(v1[j]) * sc2;
             if (kp) { x0 -= kp[c * BS + j] * LOG2E; x1 -= kp[c * BS + 32 + j] * LOG2E; }
+            if (!ok0) x0 = -INFINITY;
+            if (!ok1) x1 = -INFINITY;
             v0[j] = __float_as_uint(x0); v1[j] = __float_as_uint(x1);
             cm = fmaxf(cm, fmaxf(x0, x1));
           }
@@ -241,7 +253,7 @@ __global__ void __launch_bounds__(FWD_THREADS) k_fwd_fused(const __grid_constant
   m2 = fmaxf(m2, __shfl_xor_sync(0xffffffffu, m2, 16));          // both owners of a row agree
   float lse_fixed = 0.f;
   if (online) {
-    const float l = l_part + __shfl_xor_sync(0xffffffffu, l_part, 16) + (float)(L - nblk * BS) * exp2f(-m2);
+    const float l = l_part + __shfl_xor_sync(0xffffffffu, l_part, 16) + (float)(L - n_sel) * exp2f(-m2);
     lse_fixed = m2 + log2f(l);
     m2 = lse_fixed;                                               // pass B then produces normalised P directly
     l_part = 0.f;
@@ -269,7 +281,7 @@ __global__ void __launch_bounds__(FWD_THREADS) k_fwd_fused(const __grid_constant
           uint32_t v[32];
           tmem_ld32(t_lane + s_col(2 * p) + half * 32, v);
           tmem_ld_wait();
-          if (mine) {
+          if (mine && quarter_ok(rp + t0 + t, half)) {
 #pragma unroll
             for (int j = 0; j < 32; j += 2) {
               float h0 = m2, h1 = m2;
@@ -278,10 +290,13 @@ __global__ void __launch_bounds__(FWD_THREADS) k_fwd_fused(const __grid_constant
               l_part += e0 + e1;
               wp[p][half * 16 + (j >> 1)] = pack_bf16(e0, e1);
             }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) wp[p][half * 16 + j] = 0u;
           }
         }
       }
-      const float l = l_part + __shfl_xor_sync(0xffffffffu, l_part, 16) + (float)(L - nblk * BS) * exp2f(-m2);
+      const float l = l_part + __shfl_xor_sync(0xffffffffu, l_part, 16) + (float)(L - n_sel) * exp2f(-m2);
       const float inv = 1.0f / l;
       lse_fixed = m2 + log2f(l);
 #pragma unroll
@@ -304,7 +319,7 @@ __global__ void __launch_bounds__(FWD_THREADS) k_fwd_fused(const __grid_constant
         uint32_t v[32];
         tmem_ld32(t_lane + s_col(2 * p) + half * 32, v);
         tmem_ld_wait();
-        if (mine) {
+        if (mine && quarter_ok(rp + t0 + t, half)) {
 #pragma unroll
           for (int j = 0; j < 32; j += 2) {
             float h0 = m2, h1 = m2;
@@ -313,6 +328,9 @@ __global__ void __launch_bounds__(FWD_THREADS) k_fwd_fused(const __grid_constant
             l_part += e0 + e1;
             w[half * 16 + (j >> 1)] = pack_bf16(e0, e1);
           }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) w[half * 16 + j] = 0u;
         }
       }
       if (mine) store_row_swizzled(sP + t * VT_BYTES, row, w);
@@ -356,7 +374,7 @@ __global__ void __launch_bounds__(FWD_THREADS) k_fwd_fused(const __grid_constant
   if (ok) {
     float inv = 1.0f, lse2 = lse_fixed;
     if (!STORE_P) {
-      const float l = l_part + __shfl_xor_sync(0xffffffffu, l_part, 16) + (float)(L - nblk * BS) * exp2f(-m2);
+      const float l = l_part + __shfl_xor_sync(0xffffffffu, l_part, 16) + (float)(L - n_sel) * exp2f(-m2);
       inv = 1.0f / l;
       lse2 = m2 + log2f(l);
     } else if (nblk == 0) {
@@ -415,38 +433,39 @@ __global__ void __launch_bounds__(FWD_THREADS) k_fwd_fused(const __grid_constant
 
 namespace tc {
 
-int fused_set_attrs(int d) {
-  if (d == 64) {
-    SPION_CUDA_TRY(cudaFuncSetAttribute(k_fwd_fused<64, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fwd_smem_bytes<64>()));
-    SPION_CUDA_TRY(cudaFuncSetAttribute(k_fwd_fused<64, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fwd_smem_bytes<64>()));
-  } else {
-    SPION_CUDA_TRY(cudaFuncSetAttribute(k_fwd_fused<32, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fwd_smem_bytes<32>()));
-    SPION_CUDA_TRY(cudaFuncSetAttribute(k_fwd_fused<32, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fwd_smem_bytes<32>()));
-  }
+template <int D>
+static int fwd_attrs() {
+  const int bytes = (int)fwd_smem_bytes<D>();
+  SPION_CUDA_TRY(cudaFuncSetAttribute(k_fwd_fused<D, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  SPION_CUDA_TRY(cudaFuncSetAttribute(k_fwd_fused<D, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  SPION_CUDA_TRY(cudaFuncSetAttribute(k_fwd_fused<D, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  SPION_CUDA_TRY(cudaFuncSetAttribute(k_fwd_fused<D, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
   return SPION_OK;
 }
 
+int fused_set_attrs(int d) { return d == 64 ? fwd_attrs<64>() : fwd_attrs<32>(); }
+
 template <int D>
 static int fwd_launch(spion_ctx* c, TcState* s, const void* Q, const void* K, const void* V, const float* keypad,
-                      void* O, float* lse, void* P) {
-  const uint64_t rows = (uint64_t)c->BH * c->L, vrows = (uint64_t)c->BH * c->nnzb * BS;
+                      void* O, float* lse, void* P64) {
+  const TcView vw = tc_view(c, s);
+  const uint64_t rows = (uint64_t)c->BH * c->L, vrows = (uint64_t)c->BH * vw.nnzb * BS;
   CUtensorMap mq, mk, mv, mp;
   int rc;
   if ((rc = make_map(s, &mq, Q, rows, D, BS)) || (rc = make_map(s, &mk, K, rows, D, BS)) ||
       (rc = make_map(s, &mv, V, rows, D, BS)))
     return rc;
-  if (P) { if ((rc = make_map(s, &mp, P, vrows, BS, BS))) return rc; } else mp = mq;
+  if (P64) { if ((rc = make_map(s, &mp, P64, vrows, BS, BS))) return rc; } else mp = mq;
   prof_mark(c, -1);
-  const dim3 grid(c->nb, c->BH);
+  const dim3 grid(vw.nb, c->BH);
   const float floor_v = keypad ? 0.0f : -100.0f;
-  if (P)
-    k_fwd_fused<D, true><<<grid, FWD_THREADS, fwd_smem_bytes<D>(), c->stream>>>(
-        mq, mk, mv, mp, (__nv_bfloat16*)O, lse, keypad, c->row_ptr, c->col_idx, c->L, c->nnzb, c->scale, floor_v,
-        c->status_dev, (unsigned long long*)c->trace);
-  else
-    k_fwd_fused<D, false><<<grid, FWD_THREADS, fwd_smem_bytes<D>(), c->stream>>>(
-        mq, mk, mv, mp, (__nv_bfloat16*)O, lse, keypad, c->row_ptr, c->col_idx, c->L, c->nnzb, c->scale, floor_v,
-        c->status_dev, (unsigned long long*)c->trace);
+#define SPION_FWD_LAUNCH(SP, SB)                                                                                  \
+  k_fwd_fused<D, SP, SB><<<grid, FWD_THREADS, fwd_smem_bytes<D>(), c->stream>>>(                                   \
+      mq, mk, mv, mp, (__nv_bfloat16*)O, lse, keypad, vw.row_ptr, vw.col_idx, vw.submask, c->L, vw.nnzb, c->scale, \
+      floor_v, c->status_dev, (unsigned long long*)c->trace)
+  if (P64) { if (vw.submask) SPION_FWD_LAUNCH(true, true); else SPION_FWD_LAUNCH(true, false); }
+  else { if (vw.submask) SPION_FWD_LAUNCH(false, true); else SPION_FWD_LAUNCH(false, false); }
+#undef SPION_FWD_LAUNCH
   SPION_LAUNCH_CHECK();
   c->launches += 1;
   prof_mark(c, SPION_STAGE_FUSED_FWD);
@@ -454,9 +473,9 @@ static int fwd_launch(spion_ctx* c, TcState* s, const void* Q, const void* K, co
 }
 
 int fused_forward(spion_ctx* c, TcState* s, const void* Q, const void* K, const void* V, const float* keypad, void* O,
-                  float* lse, void* P_optional) {
-  return c->d == 64 ? fwd_launch<64>(c, s, Q, K, V, keypad, O, lse, P_optional)
-                    : fwd_launch<32>(c, s, Q, K, V, keypad, O, lse, P_optional);
+                  float* lse, void* P64_optional) {
+  return c->d == 64 ? fwd_launch<64>(c, s, Q, K, V, keypad, O, lse, P64_optional)
+                    : fwd_launch<32>(c, s, Q, K, V, keypad, O, lse, P64_optional);
 }
 
 int fused_backward(spion_ctx*, TcState*, const void*, const void*, const void*, const float*, const void*,

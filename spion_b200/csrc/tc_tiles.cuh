@@ -50,9 +50,29 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
 
 struct TcState {
   EncodeTiledFn encode = nullptr;
-  int stages = 0x1f;            // bit0 S->P, bit1 O, bit2 dP->dS, bit3 dQ, bit4 dK+dV
-  bool attr_done = false;
+  int stages = 0;               // debugging switches (SPION_TC_STAGES): bit 6 = split row kernels
+  float* lse_ws = nullptr;      // [BH*L] log-sum-exp workspace for the calls that do not expose it
+  // 32-wide masks run on 64-wide super-blocks: derived structure + which 32x32 quarters are selected
+  bool super = false;
+  int nb64 = 0, nnzb64 = 0;
+  uint8_t* mat64 = nullptr; uint8_t* submask = nullptr;
+  int32_t *row_ptr64 = nullptr, *col_idx64 = nullptr, *blk_row64 = nullptr, *col_ptr64 = nullptr, *row_idx64 = nullptr,
+          *csc_pos64 = nullptr, *work64 = nullptr, *nnzb64_dev = nullptr;
+  void* p64_ws = nullptr; void* ds64_ws = nullptr;     // [BH, nnzb64, 64, 64] bf16 each
+  size_t ws_elems = 0;
 };
+
+// What the kernels see: the 64-block structure (the mask's own, or the derived super-block one).
+struct TcView {
+  const int32_t *row_ptr, *col_idx, *col_ptr, *row_idx, *csc_pos;
+  const uint8_t* submask;       // nullptr: every block is fully selected
+  int nb, nnzb;
+};
+inline TcView tc_view(const spion_ctx* c, const TcState* s) {
+  if (s->super)
+    return TcView{s->row_ptr64, s->col_idx64, s->col_ptr64, s->row_idx64, s->csc_pos64, s->submask, s->nb64, s->nnzb64};
+  return TcView{c->row_ptr, c->col_idx, c->col_ptr, c->row_idx, c->csc_pos, nullptr, c->nb, c->nnzb};
+}
 
 inline int make_map(TcState* s, CUtensorMap* m, const void* base, uint64_t rows, uint32_t cols, uint32_t box_rows) {
   const cuuint64_t dims[2] = {cols, rows};
@@ -72,12 +92,10 @@ inline int make_map(TcState* s, CUtensorMap* m, const void* base, uint64_t rows,
 }
 
 
-// tc_engine.cu: P tiles only (S + softmax)
-int tc_engine_probabilities(spion_ctx* c, const void* Q, const void* K, const float* keypad, void* P);
 // tc_fused.cu
 int fused_set_attrs(int d);
 int fused_forward(spion_ctx* c, TcState* s, const void* Q, const void* K, const void* V, const float* keypad, void* O,
-                  float* lse, void* P_optional);
+                  float* lse, void* P64_optional);
 int fused_backward(spion_ctx* c, TcState* s, const void* Q, const void* K, const void* V, const float* keypad,
                    const void* O, const float* lse, const void* dO, float* delta, void* dQ, void* dK, void* dV);
 
