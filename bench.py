@@ -276,13 +276,57 @@ def run_training(args, rank, world, local_rank):
         dist.destroy_process_group()
 
 
+def run_pattern(args, rank, local_rank):
+    """Pattern discovery of one layer (conv + pool + quantile + walkers + CSR/CSC) at L=4096, block 64."""
+    if rank != 0:
+        return
+    from spion_b200 import pattern, synthetic
+    L, bs, q = (4096, 64, 0.96) if args.workload == "pattern_L4096_bs64" else (1024, 32, 0.96)
+    dev = torch.device("cuda", local_rank)
+    A = synthetic.structured_map(25, L).to(dev)
+    for _ in range(args.warmup):
+        pat = pattern.discover_pattern(A, bs, q)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        pat = pattern.discover_pattern(A, bs, q)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    peaks = load_peaks()
+    by = 4.0 * L * L
+    cpu = None
+    if not args.no_cpu_baseline:
+        from oracle import pattern as opat
+        cores = os.cpu_count() or 1
+        torch.set_num_threads(cores)
+        An = A.cpu().numpy()
+        t0 = time.perf_counter()
+        opat.discover_block_mask(An, bs, q, float_path="torch")       # the reference's calls + restated walkers
+        cs = time.perf_counter() - t0
+        cpu = {"value": 1.0 / cs, "unit": "maps/s", "cores": cores, "kind": "port",
+               "sample": "one [%d,%d] map, torch conv2d/avg_pool2d/quantile + iterative walkers" % (L, L), "s_per_map": cs}
+    print(json.dumps({
+        "metric": "pattern discovery maps/s at L=%d" % L, "value": 1e3 / ms, "unit": "maps/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32 in, f64 accumulate, u8/int32 out", "data": "synthetic",
+        "config": {"workload": args.workload, "L": L, "block": bs, "quantile": q, "nnzb": pat.nnzb,
+                   "includes": "one host sync per call to return the block count"},
+        "roofline": {"bound": "hbm", "achieved": by / (ms * 1e-3) / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": by / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
+                     "algorithmic_bytes_per_launch": by},
+        "cpu_baseline": cpu, "gpu_launches": 3 * args.steps}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=500)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="sweep_L4096_bs64_d05", choices=sorted(WORKLOADS) + sorted(TRAIN_WORKLOADS))
+    ap.add_argument("--workload", default="sweep_L4096_bs64_d05",
+                    choices=sorted(WORKLOADS) + sorted(TRAIN_WORKLOADS) + ["pattern_L4096_bs64", "pattern_L1024_bs32"])
     ap.add_argument("--engine", default="auto", choices=["auto", "simt", "tcgen05"])
     ap.add_argument("--mode", default="auto", choices=["auto", "fused", "staged"],
                     help="fused: S/P/dP/dS stay on chip (tcgen05 engine); staged: one kernel per stage")
@@ -312,6 +356,9 @@ def main():
     if args.workload in TRAIN_WORKLOADS:
         run_training(args, rank, world, local_rank)
         return
+    if args.workload.startswith("pattern_"):
+        run_pattern(args, rank, local_rank)
+        return
 
     B, H, L, d, bs, dens, dt = WORKLOADS[args.workload]
     tdt = torch.bfloat16 if dt == "bf16" else torch.float32
@@ -321,10 +368,9 @@ def main():
            "transformer_dim": H * d, "task": "sweep"}
     engine = {"auto": _lib.ENGINE_AUTO, "simt": _lib.ENGINE_SIMT, "tcgen05": _lib.ENGINE_TCGEN05}[args.engine]
     mod = BlockSparseAttention(cfg, dtype=tdt, engine=engine, device=dev,
-                               fused=None if args.mode == "auto" else (args.mode == "fused"), return_attn=False)
-    from spion_b200 import native as _native
+                               fused=None if args.mode == "auto" else (args.mode == "fused"))
     fused_fwd = mod.fused
-    fused_bwd = mod.fused and _native.FUSED_BACKWARD
+    fused_bwd = False            # the backward kernels read the stored P tiles
     mat = synthetic.band_random_mask(2024, nb, dens)          # same mask on every rank (one layer)
     nnzb = mod.set_mask(torch.as_tensor(mat).to(dev))
     flops, fused_bytes, nnz = algorithmic(B, H, L, d, bs, nnzb, esz)
@@ -343,16 +389,11 @@ def main():
 
     def step_device():
         if fused_fwd:
-            check(lib.spion_attn_forward_fused(mod.handle, ptr(Q), ptr(K), ptr(V), None, ptr(O), ptr(lse),
-                                               None if fused_bwd else ptr(P)))
+            check(lib.spion_attn_forward_fused(mod.handle, ptr(Q), ptr(K), ptr(V), None, ptr(O), ptr(lse), ptr(P)))
         else:
             check(lib.spion_attn_forward_ex(mod.handle, ptr(Q), ptr(K), ptr(V), None, ptr(P), ptr(O), ptr(scr)))
-        if fused_bwd:
-            check(lib.spion_attn_backward_fused(mod.handle, ptr(Q), ptr(K), ptr(V), None, ptr(O), ptr(lse), ptr(dO),
-                                                ptr(delta), ptr(dQ), ptr(dK), ptr(dV)))
-        else:
-            check(lib.spion_attn_backward_ex(mod.handle, ptr(Q), ptr(K), ptr(V), ptr(P), ptr(O), ptr(dO), ptr(dS),
-                                             ptr(scr), ptr(delta), ptr(dQ), ptr(dK), ptr(dV)))
+        check(lib.spion_attn_backward_ex(mod.handle, ptr(Q), ptr(K), ptr(V), ptr(P), ptr(O), ptr(dO), ptr(dS),
+                                         ptr(scr), ptr(delta), ptr(dQ), ptr(dK), ptr(dV)))
 
     def barrier():
         torch.cuda.synchronize()
@@ -516,7 +557,7 @@ def main():
             "dtype": "bf16" if dt == "bf16" else "f32", "data": "synthetic",
             "config": {"workload": args.workload, "B_per_gpu": B, "H": H, "L": L, "d_head": d, "block": bs,
                        "density": nnzb / float(nb * nb), "nnzb": nnzb, "engine": args.engine,
-                       "mode": ("fused" if fused_bwd else "fused-forward+staged-backward") if fused_fwd else "staged",
+                       "mode": "fused forward (P stored) + row / column backward kernels" if fused_fwd else "one kernel per stage",
                        "l2_policy": "inputs larger than L2 (Q,K,V,dO = %.0f MB, P+dS = %.0f MB per step)"
                                     % (4 * hQ.numel() * esz / 1e6, 2 * n * esz / 1e6)},
             "roofline": roofline, "kernels": kern,

@@ -94,13 +94,13 @@ enum {
   SPION_STAGE_SPMM_DQ = 6,     /* dQ = dS K                                        */
   SPION_STAGE_SPMM_DK = 7,     /* dK = dS^T Q                                      */
   SPION_STAGE_SPMM_DV = 8,     /* dV = P^T dO                                      */
-  SPION_STAGE_FUSED_S_P = 9,   /* tcgen05: S tiles + softmax -> P                  */
-  SPION_STAGE_FUSED_DP_DS = 10,/* tcgen05: dP tiles + softmax backward -> dS       */
+  SPION_STAGE_RESERVED_9 = 9,
+  SPION_STAGE_FUSED_DP_DS = 10,/* tcgen05: dP tiles + softmax backward -> dS (split row kernel) */
   SPION_STAGE_DELTA = 11,      /* row sums of dO*O                                 */
   SPION_STAGE_SPMM_DKDV = 12,  /* tcgen05: dK and dV in one kernel                 */
   SPION_STAGE_FUSED_FWD = 13,  /* tcgen05: S, softmax, P V in one kernel            */
-  SPION_STAGE_FUSED_BWD_ROW = 14, /* tcgen05: recompute P, dP, dS, dQ per block row */
-  SPION_STAGE_FUSED_BWD_COL = 15, /* tcgen05: transposed tiles, dK and dV per block column */
+  SPION_STAGE_RESERVED_14 = 14,
+  SPION_STAGE_RESERVED_15 = 15,
   SPION_STAGE_BWD_ROW = 16,    /* tcgen05: dP, dS and dQ per block row (P read, dS written) */
   SPION_STAGE_COUNT = 17
 };
@@ -199,31 +199,30 @@ int spion_pattern_nnzb(const spion_ctx* ctx);
  *   Q, K, V, O  [BH,L,d] row-major (no transposed copies: compare attention_blockcuda.py:48)
  *   P           [BH, nnzb, bs, bs] block tiles in CSR block order (out; needed by backward)
  *   keypad      [BH*L] fp32 penalty (1e6 on padded keys) or NULL
- *   S_scratch   [BH*nnzb*bs*bs] fp32, used by the SIMT engine only (may be NULL otherwise). */
+ *   S_scratch   [BH*nnzb*bs*bs] fp32, used by the SIMT engine only (may be NULL otherwise).
+ * On the tcgen05 engine this is the fused forward kernel with the probabilities stored. */
 int spion_attn_forward_ex(spion_ctx* ctx, const void* Q, const void* K, const void* V,
                           const float* keypad, void* P, void* O, float* S_scratch);
 
 /* Native backward.
  *   dS          [BH, nnzb, bs, bs] elements of the context dtype (scratch, written)
  *   dP_scratch  [BH*nnzb*bs*bs] fp32, used by the SIMT engine only
- *   delta       [BH*L] fp32 scratch (row sums of dO*O), used by the tcgen05 engine only
+ *   delta       unused (kept for ABI stability; may be NULL)
  *   dQ, dK, dV  [BH,L,d] (out). */
 int spion_attn_backward_ex(spion_ctx* ctx, const void* Q, const void* K, const void* V,
                            const void* P, const void* O, const void* dO,
                            void* dS, float* dP_scratch, float* delta,
                            void* dQ, void* dK, void* dV);
 
-/* Fused native forward / backward (tcgen05 engine only; UNSUPPORTED otherwise).  S, P, dP and dS
- * never reach HBM: forward writes O and one fp32 log-sum-exp value per row (lse [BH*L], log2 domain,
- * including the reference's non-selected-key term of models/block_attn.cu:71); backward recomputes
- * P from Q, K and lse.  P_optional: if not NULL the [BH, nnzb, bs, bs] probabilities are also
- * stored (what the reference returns as `attn`).  delta [BH*L] fp32 is scratch for backward. */
-int spion_supports_fused(const spion_ctx* ctx);   /* 1 if the fused calls can run this context */
+/* Fused native forward (tcgen05 engine only; UNSUPPORTED otherwise).  S never reaches HBM: one
+ * kernel computes the scores of a block row in tensor memory, the sparse row softmax in registers and
+ * O = P V from shared memory.  It writes O and one fp32 log-sum-exp value per row (lse [BH*L], log2
+ * domain, including the reference's non-selected-key term of models/block_attn.cu:71).
+ * P_optional: if not NULL the [BH, nnzb, bs, bs] probabilities are stored as well (what the reference
+ * returns as `attn`, and what spion_attn_backward_ex reads). */
+int spion_supports_fused(const spion_ctx* ctx);   /* 1 if the fused call can run this context */
 int spion_attn_forward_fused(spion_ctx* ctx, const void* Q, const void* K, const void* V,
                              const float* keypad, void* O, float* lse, void* P_optional);
-int spion_attn_backward_fused(spion_ctx* ctx, const void* Q, const void* K, const void* V,
-                              const float* keypad, const void* O, const float* lse, const void* dO,
-                              float* delta, void* dQ, void* dK, void* dV);
 
 /* Stand-alone sparse row softmax on block tiles (the kernels of models/block_attn.cu:33-130):
  * forward S (fp32 tiles) -> P (context dtype), backward (dP fp32, P) -> dS (context dtype). */

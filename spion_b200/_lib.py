@@ -48,7 +48,6 @@ SIGNATURES = {
     "spion_attn_backward_ex": (c_int, [c_void_p] * 13),
     "spion_supports_fused": (c_int, [c_void_p]),
     "spion_attn_forward_fused": (c_int, [c_void_p] * 8),
-    "spion_attn_backward_fused": (c_int, [c_void_p] * 12),
     "spion_softmax_forward_ex": (c_int, [c_void_p] * 4),
     "spion_softmax_backward_ex": (c_int, [c_void_p] * 4),
     "spion_static_scratch_capacity": (ctypes.c_size_t, []),

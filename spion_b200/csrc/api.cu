@@ -196,7 +196,7 @@ extern "C" int spion_profile_reset(spion_ctx* c) {
 extern "C" const char* spion_stage_name(int stage) {
   static const char* names[SPION_STAGE_COUNT] = {
       "structure", "sddmm_s", "softmax_fwd", "spmm_o", "sddmm_dp", "softmax_bwd", "spmm_dq", "spmm_dk", "spmm_dv",
-      "fused_s_p", "fused_dp_ds", "delta", "spmm_dkdv", "fused_fwd", "fused_bwd_row", "fused_bwd_col", "bwd_row"};
+      "reserved9", "fused_dp_ds", "delta", "spmm_dkdv", "fused_fwd", "reserved14", "reserved15", "bwd_row"};
   return (stage >= 0 && stage < SPION_STAGE_COUNT) ? names[stage] : "?";
 }
 
@@ -424,16 +424,6 @@ extern "C" int spion_attn_forward_fused(spion_ctx* c, const void* Q, const void*
   if (!use_tc(c)) return SPION_ERR_UNSUPPORTED;
   DeviceGuard guard(c->device);
   return tc_engine_forward_fused(c, Q, K, V, keypad, O, lse, P_optional);
-}
-
-extern "C" int spion_attn_backward_fused(spion_ctx* c, const void* Q, const void* K, const void* V, const float* keypad,
-                                         const void* O, const float* lse, const void* dO, float* delta, void* dQ,
-                                         void* dK, void* dV) {
-  if (!c || !Q || !K || !V || !O || !lse || !dO || !delta || !dQ || !dK || !dV) return SPION_ERR_ARG;
-  if (is_dense(c) || c->nnzb < 0) return SPION_ERR_STATE;
-  if (!use_tc(c)) return SPION_ERR_UNSUPPORTED;
-  DeviceGuard guard(c->device);
-  return tc_engine_backward_fused(c, Q, K, V, keypad, O, lse, dO, delta, dQ, dK, dV);
 }
 
 extern "C" int spion_softmax_forward_ex(spion_ctx* c, const float* S, const float* keypad, void* P) {

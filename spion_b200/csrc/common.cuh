@@ -155,6 +155,3 @@ int tc_engine_backward(spion_ctx* c, const void* Q, const void* K, const void* V
                        const void* dO, void* dS, float* dP_scratch, void* dQ, void* dK, void* dV);
 int tc_engine_forward_fused(spion_ctx* c, const void* Q, const void* K, const void* V, const float* keypad, void* O,
                             float* lse, void* P_optional);
-int tc_engine_backward_fused(spion_ctx* c, const void* Q, const void* K, const void* V, const float* keypad,
-                             const void* O, const float* lse, const void* dO, float* delta, void* dQ, void* dK,
-                             void* dV);

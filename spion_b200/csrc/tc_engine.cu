@@ -780,10 +780,3 @@ int tc_engine_forward_fused(spion_ctx* c, const void* Q, const void* K, const vo
   return forward_any(c, Q, K, V, keypad, O, lse, P_optional);
 }
 
-int tc_engine_backward_fused(spion_ctx* c, const void* Q, const void* K, const void* V, const float* keypad,
-                             const void* O, const float* lse, const void* dO, float* delta, void* dQ, void* dK,
-                             void* dV) {
-  if (!c->tc) return SPION_ERR_STATE;
-  if (c->nnzb == 0) return SPION_ERR_SHAPE;
-  return fused_backward(c, (TcState*)c->tc, Q, K, V, keypad, O, lse, dO, delta, dQ, dK, dV);
-}

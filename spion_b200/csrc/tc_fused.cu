@@ -1,18 +1,14 @@
-// Fused block-sparse attention kernels (sm_100a, bf16, 64x64 blocks): S, the sparse row softmax
-// and the products that follow stay on chip; only Q, K, V, dO, O, the gradients and one fp32
-// log-sum-exp per row cross HBM (P is written only when the caller asks for it).
+// Fused block-sparse attention forward (sm_100a, bf16, 64x64 blocks): S and the sparse row softmax
+// stay on chip; Q, K, V are read once per use, O and one fp32 log-sum-exp per row are written
+// (the P tiles only when the caller asks for them, e.g. for the backward pass).
 //
 //   k_fwd_fused   per block row:   S = Q K^T (tcgen05, TMEM) -> row softmax (fp32, registers)
 //                                  -> P (bf16, swizzled shared memory) -> O = P V (tcgen05)
 //                 replaces the three forward stages of models/block_attn.cu:453-487.
-//   k_bwd_row     per block row:   recompute P from Q, K and the stored log-sum-exp, dP = dO V^T,
-//                                  dS = P (dP - delta) scale -> dQ = dS K          (:498-516)
-//   k_bwd_col     per block column: the same tiles transposed (S^T = K Q^T, dP^T = V dO^T)
-//                                  -> dV = P^T dO, dK = dS^T Q                     (:526-536)
 //
 // Softmax semantics are the reference's (models/block_attn.cu:48-87): every non-selected key of a
 // row adds exp(0 - m) to the denominator.  lse2_i = m_i*log2(e) + log2(Z_i) is stored so that
-// P_ij = exp2(s_ij*scale*log2(e) - lse2_i) can be recomputed by the backward kernels.
+// P_ij = exp2(s_ij*scale*log2(e) - lse2_i) can be recomputed from Q and K.
 //
 // Accumulator placement: an MMA with M = 64 fills TMEM lanes (m%16) + 32*(m/16); a second tile is
 // placed in the same columns at lane offset 16, so that all 32 lanes of every warp hold a row
@@ -476,11 +472,6 @@ int fused_forward(spion_ctx* c, TcState* s, const void* Q, const void* K, const 
                   float* lse, void* P64_optional) {
   return c->d == 64 ? fwd_launch<64>(c, s, Q, K, V, keypad, O, lse, P64_optional)
                     : fwd_launch<32>(c, s, Q, K, V, keypad, O, lse, P64_optional);
-}
-
-int fused_backward(spion_ctx*, TcState*, const void*, const void*, const void*, const float*, const void*,
-                   const float*, const void*, float*, void*, void*, void*) {
-  return SPION_ERR_UNSUPPORTED;
 }
 
 }  // namespace tc

@@ -96,7 +96,5 @@ inline int make_map(TcState* s, CUtensorMap* m, const void* base, uint64_t rows,
 int fused_set_attrs(int d);
 int fused_forward(spion_ctx* c, TcState* s, const void* Q, const void* K, const void* V, const float* keypad, void* O,
                   float* lse, void* P64_optional);
-int fused_backward(spion_ctx* c, TcState* s, const void* Q, const void* K, const void* V, const float* keypad,
-                   const void* O, const float* lse, const void* dO, float* delta, void* dQ, void* dK, void* dV);
 
 }  // namespace tc

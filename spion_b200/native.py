@@ -20,12 +20,11 @@ from . import _lib
 from ._lib import check, lib, ptr
 
 _DTYPES = {torch.float32: _lib.F32, torch.bfloat16: _lib.BF16}
-FUSED_BACKWARD = False     # the fused backward kernels are switched on once they pass parity
 
 
 class BlockSparseAttention(nn.Module):
     def __init__(self, config, dtype=torch.float32, keypad: bool = False, engine: int = _lib.ENGINE_AUTO,
-                 device=None, fused=None, return_attn: bool = True):
+                 device=None, fused=None):
         super().__init__()
         self.d = config["head_dim"]
         self.H = config["num_head"]
@@ -48,7 +47,6 @@ class BlockSparseAttention(nn.Module):
         if fused and not can_fuse:
             raise _lib.SpionError("fused kernels need the tcgen05 engine (bf16, block 64, head_dim 32/64)")
         self.fused = can_fuse if fused is None else bool(fused)
-        self.return_attn = return_attn
         self.nnzb = -1
         self._mask_key = None
         self._fn = _make_function(self)
@@ -116,36 +114,24 @@ def _make_function(mod: BlockSparseAttention):
             dev = q.device
             O = torch.empty_like(q)
             lse = torch.empty(mod.BH * mod.L, dtype=torch.float32, device=dev)
-            need_p = mod.return_attn or not FUSED_BACKWARD
-            P = torch.empty(mod.BH * mod.nnz, dtype=mod.dtype, device=dev) if need_p else None
+            P = torch.empty(mod.BH * mod.nnz, dtype=mod.dtype, device=dev)     # read again by the backward
             check(lib.spion_set_stream(mod.handle, _lib.current_stream_ptr()))
             check(lib.spion_attn_forward_fused(mod.handle, ptr(q), ptr(k), ptr(v), ptr(pen), ptr(O), ptr(lse), ptr(P)),
                   "spion_attn_forward_fused")
-            ctx.save_for_backward(q, k, v, O, lse, pen if pen is not None else torch.empty(0, device=dev),
-                                  P if P is not None else torch.empty(0, device=dev))
-            ctx.has_pen = pen is not None
-            if P is None:
-                P = torch.empty(0, dtype=mod.dtype, device=dev)
+            ctx.save_for_backward(q, k, v, O, P)
             ctx.mark_non_differentiable(P)
             return O, P
 
         @staticmethod
         def backward(ctx, grad_output, grad_p):
-            q, k, v, O, lse, pen, P = ctx.saved_tensors
-            pen = pen if ctx.has_pen else None
+            q, k, v, O, P = ctx.saved_tensors
             dev = q.device
             go = grad_output.to(mod.dtype).contiguous()
             dq, dk, dv = torch.empty_like(q), torch.empty_like(q), torch.empty_like(q)
-            delta = torch.empty(mod.BH * mod.L, dtype=torch.float32, device=dev)
             check(lib.spion_set_stream(mod.handle, _lib.current_stream_ptr()))
-            if FUSED_BACKWARD:
-                check(lib.spion_attn_backward_fused(mod.handle, ptr(q), ptr(k), ptr(v), ptr(pen), ptr(O), ptr(lse),
-                                                    ptr(go), ptr(delta), ptr(dq), ptr(dk), ptr(dv)),
-                      "spion_attn_backward_fused")
-            else:
-                dS = torch.empty(mod.BH * mod.nnz, dtype=mod.dtype, device=dev)
-                check(lib.spion_attn_backward_ex(mod.handle, ptr(q), ptr(k), ptr(v), ptr(P), ptr(O), ptr(go), ptr(dS),
-                                                 None, ptr(delta), ptr(dq), ptr(dk), ptr(dv)), "spion_attn_backward_ex")
+            dS = torch.empty(mod.BH * mod.nnz, dtype=mod.dtype, device=dev)
+            check(lib.spion_attn_backward_ex(mod.handle, ptr(q), ptr(k), ptr(v), ptr(P), ptr(O), ptr(go), ptr(dS),
+                                             None, None, ptr(dq), ptr(dk), ptr(dv)), "spion_attn_backward_ex")
             return dq, dk, dv, None
 
     if mod.fused:
