@@ -76,6 +76,13 @@ int spion_check_device_status(spion_ctx* ctx);
  * phase boundaries, into this device buffer (8 * grid size uint64; NULL switches it off). */
 int spion_set_trace_buffer(spion_ctx* ctx, void* device_buffer);
 
+/* Failure-path self-test that faults nothing: launches one CTA that waits, with the given limit
+ * in clock cycles (at most 2e9), on a barrier nobody arrives on.  The kernel gives up, records the
+ * time-out in the status word and exits normally; the call then returns what
+ * spion_check_device_status returns, i.e. SPION_ERR_TIMEOUT when the machinery works, and the
+ * context stays usable. */
+int spion_selftest_bounded_wait(spion_ctx* ctx, long long limit_cycles);
+
 /* Number of kernels this context has launched since creation (bench bookkeeping). */
 long long spion_launch_count(const spion_ctx* ctx);
 

@@ -29,6 +29,7 @@ SIGNATURES = {
     "spion_set_engine": (c_int, [c_void_p, c_int]),
     "spion_check_device_status": (c_int, [c_void_p]),
     "spion_set_trace_buffer": (c_int, [c_void_p, c_void_p]),
+    "spion_selftest_bounded_wait": (c_int, [c_void_p, c_longlong]),
     "spion_launch_count": (c_longlong, [c_void_p]),
     "spion_profile": (c_int, [c_void_p, c_int]),
     "spion_profile_get": (c_int, [c_void_p, c_int, c_void_p, c_void_p]),

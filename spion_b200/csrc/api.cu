@@ -135,6 +135,14 @@ extern "C" int spion_set_trace_buffer(spion_ctx* c, void* device_buffer) {
   return SPION_OK;
 }
 
+extern "C" int spion_selftest_bounded_wait(spion_ctx* c, long long limit_cycles) {
+  if (!c || limit_cycles < 1 || limit_cycles > 2000000000LL) return SPION_ERR_ARG;
+  DeviceGuard guard(c->device);
+  int rc = tc_engine_wait_selftest(c, limit_cycles);
+  if (rc) return rc;
+  return spion_check_device_status(c);      // expected: SPION_ERR_TIMEOUT, and the word is cleared again
+}
+
 extern "C" long long spion_launch_count(const spion_ctx* c) { return c ? c->launches : 0; }
 
 // ------------------------------------------------------------ per-stage timing

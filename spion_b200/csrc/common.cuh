@@ -155,3 +155,4 @@ int tc_engine_backward(spion_ctx* c, const void* Q, const void* K, const void* V
                        const void* dO, void* dS, float* dP_scratch, void* dQ, void* dK, void* dV);
 int tc_engine_forward_fused(spion_ctx* c, const void* Q, const void* K, const void* V, const float* keypad, void* O,
                             float* lse, void* P_optional);
+int tc_engine_wait_selftest(spion_ctx* c, long long limit_cycles);

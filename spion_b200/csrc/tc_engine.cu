@@ -580,6 +580,20 @@ __global__ void __launch_bounds__(256) k_convert_tiles(__nv_bfloat16* __restrict
   }
 }
 
+// Self-test of the bounded wait: one CTA waits on an mbarrier that nothing ever arrives on, with a
+// short limit; it must give up, record ERR_LOAD_WAIT in the status word and return normally.
+__global__ void k_wait_selftest(int* status, long long limit_cycles) {
+  __shared__ __align__(8) unsigned long long bar_storage;
+  const uint32_t bar = smem_u32(&bar_storage);
+  if (threadIdx.x == 0) {
+    mbar_init(bar, 1);
+    fence_barrier_init();
+  }
+  __syncthreads();
+  const bool ok = __syncthreads_and(mbar_wait_limit(bar, 0, limit_cycles));
+  if (!ok && threadIdx.x == 0) report(status, ERR_LOAD_WAIT);
+}
+
 constexpr int NST_N = 4, NST_T = 2;
 
 template <int D> constexpr size_t smem_dp_ds() { return 1024 + (size_t)5 * OpTile<D>::BYTES + 4 * VT_BYTES + 64; }
@@ -780,3 +794,10 @@ int tc_engine_forward_fused(spion_ctx* c, const void* Q, const void* K, const vo
   return forward_any(c, Q, K, V, keypad, O, lse, P_optional);
 }
 
+
+int tc_engine_wait_selftest(spion_ctx* c, long long limit_cycles) {
+  k_wait_selftest<<<1, 128, 0, c->stream>>>(c->status_dev, limit_cycles);
+  SPION_LAUNCH_CHECK();
+  c->launches += 1;
+  return SPION_OK;
+}

@@ -35,13 +35,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait.  Returns false when the limit is hit (the caller records it and leaves).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, long long limit_cycles) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   for (;;) {
     if (mbar_try_wait(bar, parity)) return true;
-    if (clock64() - t0 > SPION_WAIT_CYCLES) return false;
+    if (clock64() - t0 > limit_cycles) return false;
   }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  return mbar_wait_limit(bar, parity, SPION_WAIT_CYCLES);
 }
 
 // ------------------------------------------------------------------ TMA (tiled, 2-D, no cluster features)

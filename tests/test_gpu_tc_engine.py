@@ -1,0 +1,86 @@
+"""Edge cases of the tcgen05 engine (bf16, native tiles) against the oracle: rows that need several
+chunks, rows with one block, full masks, key padding with fully padded tails, 32-wide masks on
+super-blocks, and the bounded-wait failure path (which faults nothing)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import attention as oatt
+from spion_b200 import synthetic
+
+pytestmark = pytest.mark.gpu
+REL = 2e-2
+
+
+def cfg(B, H, L, d, bs):
+    return {"head_dim": d, "num_head": H, "max_seq_len": L, "batch_size": B, "block_size": bs,
+            "transformer_dim": H * d, "task": "t"}
+
+
+def rel(a, b):
+    b = b.float().cpu()
+    return float((a.detach().float().cpu() - b).abs().max() / b.abs().max().clamp_min(1e-30))
+
+
+def check(B, H, L, d, bs, mat, keypad=None, seed=5):
+    from spion_b200 import _lib
+    from spion_b200.native import BlockSparseAttention
+    Q, K, V, dO = [t.to(torch.bfloat16) for t in synthetic.qkv(seed, B, H, L, d)]
+    mod = BlockSparseAttention(cfg(B, H, L, d, bs), dtype=torch.bfloat16, keypad=keypad is not None,
+                               engine=_lib.ENGINE_TCGEN05)
+    assert mod.fused
+    q = Q.cuda().requires_grad_(True); k = K.cuda().requires_grad_(True); v = V.cuda().requires_grad_(True)
+    out, P = mod(q, k, v, None if keypad is None else keypad.cuda(), torch.as_tensor(mat).cuda())
+    out.backward(dO.cuda())
+    torch.cuda.synchronize()
+    mod.check_device_status()
+    O, Pd, gQ, gK, gV = oatt.sparse_attention(Q.float(), K.float(), V.float(), mat, bs, keypad, dO.float())
+    want_tiles = torch.as_tensor(oatt.block_values_from_dense(Pd.numpy(), mat, bs))
+    assert rel(out, O) <= REL
+    assert rel(P.view(B * H, -1, bs, bs), want_tiles) <= REL
+    assert rel(q.grad, gQ) <= REL and rel(k.grad, gK) <= REL and rel(v.grad, gV) <= REL
+
+
+@pytest.mark.parametrize("d", [32, 64])
+def test_rows_of_every_length(d):
+    """Block rows with 1, 2, 3, 4 (one chunk) and 5..9 blocks (streamed chunks) in one mask."""
+    nb = 10
+    mat = np.eye(nb, dtype=np.uint8)
+    for r in range(nb):
+        mat[r, :min(nb, r)] = 1            # row r has r+1 blocks (last: 10)
+    check(1, 2, nb * 64, d, 64, mat)
+
+
+def test_full_mask_is_dense_attention():
+    check(1, 2, 512, 64, 64, np.ones((8, 8), np.uint8))
+
+
+def test_single_column_and_diagonal_only():
+    m = np.eye(8, dtype=np.uint8); m[:, 3] = 1
+    check(2, 1, 512, 64, 64, m)
+    check(2, 1, 512, 32, 64, np.eye(8, dtype=np.uint8))
+
+
+def test_key_padding_with_fully_padded_tail():
+    B, L = 2, 512
+    kp = torch.ones(B, L); kp[0, 200:] = 0; kp[1, 64:] = 0        # whole key blocks are padding
+    mat = synthetic.band_random_mask(4, 8, 0.5)
+    check(B, 2, L, 64, 64, mat, keypad=kp)
+
+
+@pytest.mark.parametrize("dens", [0.1, 0.6])
+def test_blocks_of_32_on_super_blocks(dens):
+    mat = synthetic.band_random_mask(11, 16, dens)
+    check(1, 2, 512, 64, 32, mat)
+    kp = synthetic.key_padding(2, 1, 512)
+    check(1, 2, 512, 32, 32, mat, keypad=kp)
+
+
+def test_bounded_wait_reports_and_context_survives():
+    from spion_b200 import _lib
+    from spion_b200.native import BlockSparseAttention
+    mod = BlockSparseAttention(cfg(1, 1, 128, 64, 64), dtype=torch.bfloat16)
+    rc = _lib.lib.spion_selftest_bounded_wait(mod.handle, 2_000_000)      # about a millisecond
+    assert rc == -4, "the wait must give up and be reported as SPION_ERR_TIMEOUT"
+    mod.check_device_status()                                              # word was cleared
+    check(1, 1, 128, 64, 64, np.ones((2, 2), np.uint8))                    # the GPU context still works
