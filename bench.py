@@ -228,13 +228,17 @@ def run_training(args, rank, world, local_rank):
     dens = [float(m.mean()) for m in mat_lst[0]]
     del maps
     torch.cuda.empty_cache()
+    use_graph = not args.no_graph
+    if use_graph:
+        tr.capture_sparse_step(ids, y)
+    run_step = (lambda a, b: tr.step_graph(a, b)) if use_graph else (lambda a, b: tr.step(a, b)[0])
     for _ in range(args.warmup):
-        tr.step(ids, y)
+        run_step(ids, y)
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(args.steps):
-        tr.step(ids, y)
+        run_step(ids, y)
     e1.record()
     barrier()
     t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
@@ -244,12 +248,12 @@ def run_training(args, rank, world, local_rank):
     tokens = per_rank * world * L * (2 if dual else 1)
     # e2e: ids and labels from pinned host memory every step, the loss read back every step
     for _ in range(2):
-        ids2, y2 = to_dev(hb); float(tr.step(ids2, y2)[0])
+        ids2, y2 = to_dev(hb); float(run_step(ids2, y2))
     barrier()
     e0.record()
     for _ in range(args.steps):
         ids2, y2 = to_dev(hb)
-        loss, _ = tr.step(ids2, y2)
+        loss = run_step(ids2, y2)
         lv = float(loss)                                          # device -> host read of the step's result
     e1.record()
     barrier()
@@ -266,7 +270,7 @@ def run_training(args, rank, world, local_rank):
             "data": "synthetic",
             "config": {"workload": args.workload, "task": cfg["task"], "batch_per_gpu": per_rank, "L": L,
                        "block": cfg["block_size"], "threshold": thr, "density_per_layer": dens,
-                       "grad_bucket_bytes": tr.bucket.nbytes, "pattern_discovery_ms": pattern_ms,
+                       "grad_bucket_bytes": tr.bucket.nbytes, "cuda_graph": use_graph, "pattern_discovery_ms": pattern_ms,
                        "l2_policy": "activations of one step exceed L2"},
             "e2e": {"value": tokens / (e2e_ms * 1e-3) / 1e6, "unit": "Mtokens/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": int((2 if dual else 1) * per_rank * L * 8 + per_rank * 8), "d2h_bytes_per_step": 4},
@@ -330,6 +334,7 @@ def main():
     ap.add_argument("--engine", default="auto", choices=["auto", "simt", "tcgen05"])
     ap.add_argument("--mode", default="auto", choices=["auto", "fused", "staged"],
                     help="fused: S/P/dP/dS stay on chip (tcgen05 engine); staged: one kernel per stage")
+    ap.add_argument("--no-graph", action="store_true", help="training workloads: launch the step eagerly")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-clocks", action="store_true", help="do not sample nvidia-smi (profiler runs)")
     args = ap.parse_args()

@@ -129,9 +129,10 @@ class Trainer:
         torch.manual_seed(seed)                      # identical initial weights on every rank
         self.model = Classifier(config).to(self.device)
         self.bucket = dp.FlatGradBucket(self.model.parameters())
-        self.opt = torch.optim.AdamW(self.model.parameters(), lr=lr, weight_decay=0.0)
+        self.opt = torch.optim.AdamW(self.model.parameters(), lr=lr, weight_decay=0.0, capturable=True, fused=True)
         self.mat_lst = None
         self.patterns = None
+        self._graph = None
 
     def step(self, ids, label, is_attn=False):
         self.bucket.zero()
@@ -141,6 +142,39 @@ class Trainer:
         torch.nn.utils.clip_grad_value_(self.model.parameters(), 1.0)   # main_conv_ff.py:186
         self.opt.step()
         return loss.detach(), maps
+
+    def capture_sparse_step(self, ids, label, warmup: int = 3):
+        """Record one sparse step (forward, backward, all-reduce, optimizer) as a CUDA graph: the step is
+        a few hundred small launches, so replaying it removes most of the host time.  The library's
+        calls are plain stream-ordered launches with caller-owned buffers, which is what capture needs."""
+        if self.mat_lst is None:
+            raise RuntimeError("capture the step after discover()")
+        dual = isinstance(ids, (tuple, list))
+        self._g_ids = tuple(t.clone() for t in ids) if dual else ids.clone()
+        self._g_lab = label.clone()
+        cur = torch.cuda.current_stream()
+        side = torch.cuda.Stream()
+        side.wait_stream(cur)
+        with torch.cuda.stream(side):
+            for _ in range(warmup):
+                self.step(self._g_ids, self._g_lab)
+        cur.wait_stream(side)
+        torch.cuda.synchronize()
+        self._graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self._graph):
+            self._g_loss, _ = self.step(self._g_ids, self._g_lab)
+        return self._graph
+
+    def step_graph(self, ids, label):
+        """Replay the captured step on new inputs (copied into the graph's static buffers)."""
+        if isinstance(ids, (tuple, list)):
+            for dst, src in zip(self._g_ids, ids):
+                dst.copy_(src, non_blocking=True)
+        else:
+            self._g_ids.copy_(ids, non_blocking=True)
+        self._g_lab.copy_(label, non_blocking=True)
+        self._graph.replay()
+        return self._g_loss
 
     def discover(self, maps, threshold=None):
         cfg = dict(self.config)
