@@ -56,6 +56,13 @@ TRAIN_WORKLOADS = {
 }
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum per launch, from the ncu capture summarised in
+# profiles/tcgen05_fused_pipeline_sweep_L4096_bs64_d05.md (same workload, same kernels)
+NCU_TRAFFIC = {
+    "sweep_L4096_bs64_d05": {"fused_fwd": 193.9e6, "bwd_row": 352.5e6, "spmm_dkdv": 332.6e6},
+}
+
+
 def load_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -463,7 +470,9 @@ def main():
     dom_bytes = stage_bytes(dom, BH, L, d, nnz, esz, psz, p_stored=not fused_bwd)
     achieved = dom_bytes / (stages[dom] * 1e-3) / 1e9
     roofline = {"kernel": dom, "bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
+                "frac": achieved / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC.get(args.workload, {}).get(dom),
+                "traffic_source": "ncu dram bytes per launch, profiles/tcgen05_fused_pipeline_sweep_L4096_bs64_d05.md",
+                "peak_source": peaks["source"],
                 "algorithmic_bytes_per_launch": dom_bytes, "ms_per_launch": stages[dom]}
     step_bound_ms = max(flops / (peaks["bf16_tflops"] * 1e12), fused_bytes / (peaks["hbm_gbs"] * 1e9)) * 1e3
 

@@ -41,7 +41,7 @@ __global__ void __launch_bounds__(128) k_dp_ds(const __grid_constant__ CUtensorM
                                                const __grid_constant__ CUtensorMap tmdS,
                                                const __nv_bfloat16* __restrict__ dOg,
                                                const __nv_bfloat16* __restrict__ Og,
-                                               const int* __restrict__ row_ptr, const int* __restrict__ col_idx,
+                                               const int4* __restrict__ row_info, const int* __restrict__ col_idx,
                                                int L, int nnzb, float scale, int* status) {
   using T = OpTile<D>;
   constexpr int NCH = 4;
@@ -60,8 +60,11 @@ __global__ void __launch_bounds__(128) k_dp_ds(const __grid_constant__ CUtensorM
   const int tid = threadIdx.x, q = tid >> 5, lane = tid & 31;
   const int hf = lane >> 4;
   const int row = q * 16 + (lane & 15);
-  const int rp = row_ptr[r];
-  const int nblk = row_ptr[r + 1] - rp;
+  const int4 ri = row_info[r];
+  const int rp = ri.x, nblk = ri.y;
+  auto col_of = [&](int t) -> int {                            // block column of the row's t-th block
+    return t < 4 ? ((t & 2 ? ri.w : ri.z) >> ((t & 1) * 16)) & 0xffff : col_idx[rp + t];
+  };
   const int nchunks = (nblk + NCH - 1) / NCH;
   bool a_loaded = false;
 
@@ -69,7 +72,7 @@ __global__ void __launch_bounds__(128) k_dp_ds(const __grid_constant__ CUtensorM
     const int t0 = ch * NCH, nt = min(NCH, nblk - t0);
     mbar_expect_tx(bar_k, (a_loaded ? 0 : T::BYTES) + nt * T::BYTES);
     if (!a_loaded) tma_load_2d(sA, &tmdO, bar_k, 0, bh * L + r * BS);
-    for (int t = 0; t < nt; ++t) tma_load_2d(sB + t * T::BYTES, &tmV, bar_k, 0, bh * L + col_idx[rp + t0 + t] * BS);
+    for (int t = 0; t < nt; ++t) tma_load_2d(sB + t * T::BYTES, &tmV, bar_k, 0, bh * L + col_of(t0 + t) * BS);
     mbar_expect_tx(bar_p, nt * VT_BYTES);
     for (int t = 0; t < nt; ++t)
       tma_load_2d(sP + t * VT_BYTES, &tmP, bar_p, 0, (int)(((size_t)bh * nnzb + rp + t0 + t) * BS));
@@ -194,7 +197,7 @@ __global__ void __launch_bounds__(128) k_bwd_row(const __grid_constant__ CUtenso
                                                  const __grid_constant__ CUtensorMap tmdS,
                                                  const __nv_bfloat16* __restrict__ dOg,
                                                  const __nv_bfloat16* __restrict__ Og, __nv_bfloat16* __restrict__ dQ,
-                                                 const int* __restrict__ row_ptr, const int* __restrict__ col_idx,
+                                                 const int4* __restrict__ row_info, const int* __restrict__ col_idx,
                                                  int L, int nnzb, float scale, int* status) {
   using T = OpTile<D>;
   constexpr int NCH = 4;
@@ -209,12 +212,18 @@ __global__ void __launch_bounds__(128) k_bwd_row(const __grid_constant__ CUtenso
   uint32_t* slot_ptr = reinterpret_cast<uint32_t*>(smem_raw + (slot - raw));
   __shared__ int s_abort;
 
-  const int r = blockIdx.x, bh = blockIdx.y;
+  // (b,h) matrices are walked in descending order: the forward pass wrote P in ascending order, so the
+  // most recently written tiles (still in L2) are read first, and the dS tiles this kernel writes
+  // last are the ones the column kernel, which ascends, reads first.
+  const int r = blockIdx.x, bh = gridDim.y - 1 - blockIdx.y;
   const int tid = threadIdx.x, q = tid >> 5, lane = tid & 31;
   const int hf = lane >> 4;
   const int row = q * 16 + (lane & 15);
-  const int rp = row_ptr[r];
-  const int nblk = row_ptr[r + 1] - rp;
+  const int4 ri = row_info[r];
+  const int rp = ri.x, nblk = ri.y;
+  auto col_of = [&](int t) -> int {                            // block column of the row's t-th block
+    return t < 4 ? ((t & 2 ? ri.w : ri.z) >> ((t & 1) * 16)) & 0xffff : col_idx[rp + t];
+  };
   const int nchunks = (nblk + NCH - 1) / NCH;
   const bool single = nblk <= NCH;
   const uint32_t ncols = single ? 128u : 256u;
@@ -225,7 +234,7 @@ __global__ void __launch_bounds__(128) k_bwd_row(const __grid_constant__ CUtenso
     const int t0 = ch * NCH, nt = min(NCH, nblk - t0);
     mbar_expect_tx(bar_v, (a_loaded ? 0 : T::BYTES) + nt * T::BYTES);
     if (!a_loaded) tma_load_2d(sA, &tmdO, bar_v, 0, bh * L + r * BS);
-    for (int t = 0; t < nt; ++t) tma_load_2d(sB + t * T::BYTES, &tmV, bar_v, 0, bh * L + col_idx[rp + t0 + t] * BS);
+    for (int t = 0; t < nt; ++t) tma_load_2d(sB + t * T::BYTES, &tmV, bar_v, 0, bh * L + col_of(t0 + t) * BS);
     mbar_expect_tx(bar_p, nt * VT_BYTES);
     for (int t = 0; t < nt; ++t)
       tma_load_2d(sP + t * VT_BYTES, &tmP, bar_p, 0, (int)(((size_t)bh * nnzb + rp + t0 + t) * BS));
@@ -295,7 +304,7 @@ __global__ void __launch_bounds__(128) k_bwd_row(const __grid_constant__ CUtenso
     const bool w1 = mbar_wait(bar_s, ph_s);
     if (tid == 0 && w1) {                                      // V consumed: bring K into the same buffers
       mbar_expect_tx(bar_k, nt * T::BYTES);
-      for (int t = 0; t < nt; ++t) tma_load_2d(sB + t * T::BYTES, &tmK, bar_k, 0, bh * L + col_idx[rp + t0 + t] * BS);
+      for (int t = 0; t < nt; ++t) tma_load_2d(sB + t * T::BYTES, &tmK, bar_k, 0, bh * L + col_of(t0 + t) * BS);
     }
     const bool w2 = mbar_wait(bar_p, ph_p);
     if (!__syncthreads_and(w1 && w2)) { if (tid == 0) report(status, ERR_MMA_WAIT); ok = false; break; }
@@ -580,6 +589,16 @@ __global__ void __launch_bounds__(256) k_convert_tiles(__nv_bfloat16* __restrict
   }
 }
 
+__global__ void k_row_info(const int32_t* __restrict__ row_ptr, const int32_t* __restrict__ col_idx, int nb,
+                           int4* __restrict__ info) {
+  for (int r = blockIdx.x * blockDim.x + threadIdx.x; r < nb; r += gridDim.x * blockDim.x) {
+    const int rp = row_ptr[r], n = row_ptr[r + 1] - rp;
+    int c[4] = {0, 0, 0, 0};
+    for (int t = 0; t < 4 && t < n; ++t) c[t] = col_idx[rp + t];
+    info[r] = make_int4(rp, n, c[0] | (c[1] << 16), c[2] | (c[3] << 16));
+  }
+}
+
 // Self-test of the bounded wait: one CTA waits on an mbarrier that nothing ever arrives on, with a
 // short limit; it must give up, record ERR_LOAD_WAIT in the status word and return normally.
 __global__ void k_wait_selftest(int* status, long long limit_cycles) {
@@ -645,14 +664,14 @@ int run_backward(spion_ctx* c, TcState* s, const void* Q, const void* K, const v
     return rc;
   if (!(s->stages & 64)) {
     k_bwd_row<D><<<grid, 128, smem_dp_ds<D>(), c->stream>>>(mdo, mv, mk, mp, mds, (const __nv_bfloat16*)dO,
-                                                            (const __nv_bfloat16*)O, (__nv_bfloat16*)dQ, vw.row_ptr,
+                                                            (const __nv_bfloat16*)O, (__nv_bfloat16*)dQ, vw.row_info,
                                                             vw.col_idx, c->L, vw.nnzb, c->scale, c->status_dev);
     SPION_LAUNCH_CHECK();
     c->launches += 1;
     prof_mark(c, SPION_STAGE_BWD_ROW);
   } else {
     k_dp_ds<D><<<grid, 128, smem_dp_ds<D>(), c->stream>>>(mdo, mv, mp, mds, (const __nv_bfloat16*)dO,
-                                                          (const __nv_bfloat16*)O, vw.row_ptr, vw.col_idx, c->L,
+                                                          (const __nv_bfloat16*)O, vw.row_info, vw.col_idx, c->L,
                                                           vw.nnzb, c->scale, c->status_dev);
     SPION_LAUNCH_CHECK();
     prof_mark(c, SPION_STAGE_FUSED_DP_DS);
@@ -748,7 +767,15 @@ int tc_engine_prepare(spion_ctx* c) {
     s->super = c->bs == 32;
     c->tc = s;
   }
-  if (s->super) return build_super(c, s);
+  if (s->super) {
+    int rc = build_super(c, s);
+    if (rc) return rc;
+  }
+  const TcView vw = tc_view(c, s);
+  if (!s->row_info && cudaMalloc(&s->row_info, (size_t)SPION_MAX_NB * sizeof(int4)) != cudaSuccess) return SPION_ERR_ALLOC;
+  k_row_info<<<4, 128, 0, c->stream>>>(vw.row_ptr, vw.col_idx, vw.nb, s->row_info);
+  SPION_LAUNCH_CHECK();
+  c->launches += 1;
   return SPION_OK;
 }
 
@@ -757,6 +784,7 @@ void tc_engine_release(spion_ctx* c) {
   TcState* s = (TcState*)c->tc;
   free_super(s);
   cudaFree(s->lse_ws);
+  cudaFree(s->row_info);
   delete s;
   c->tc = nullptr;
 }

@@ -62,7 +62,7 @@ __global__ void __launch_bounds__(FWD_THREADS) k_fwd_fused(const __grid_constant
                                                            const __grid_constant__ CUtensorMap tmP,
                                                            __nv_bfloat16* __restrict__ O, float* __restrict__ lse_out,
                                                            const float* __restrict__ keypad,
-                                                           const int* __restrict__ row_ptr,
+                                                           const int4* __restrict__ row_info,
                                                            const int* __restrict__ col_idx,
                                                            const uint8_t* __restrict__ submask, int L, int nnzb,
                                                            float scale, float floor_v, int* status,
@@ -94,8 +94,11 @@ __global__ void __launch_bounds__(FWD_THREADS) k_fwd_fused(const __grid_constant
   const int hf = lane >> 4;                                    // 0: even tiles, 1: odd tiles
   const int row = q * 16 + (lane & 15);                        // row of the block this thread owns
 
-  const int rp = row_ptr[r];
-  const int nblk = row_ptr[r + 1] - rp;
+  const int4 ri = row_info[r];
+  const int rp = ri.x, nblk = ri.y;
+  auto col_of = [&](int t) -> int {                            // block column of the row's t-th block
+    return t < 4 ? ((t & 2 ? ri.w : ri.z) >> ((t & 1) * 16)) & 0xffff : col_idx[rp + t];
+  };
   // 32-wide masks: bit (2*(row/32) + col/32) of submask[block] tells whether that quarter is selected
   const int rh2 = (q >> 1) * 2;
   auto quarter_ok = [&](int blk, int half) -> bool { return !SUB || ((submask[blk] >> (rh2 + half)) & 1); };
@@ -117,10 +120,10 @@ __global__ void __launch_bounds__(FWD_THREADS) k_fwd_fused(const __grid_constant
     const int t0 = ch * CH, nt = min(CH, nblk - t0);
     mbar_expect_tx(bar_k, (q_loaded ? 0 : T::BYTES) + nt * T::BYTES);
     if (!q_loaded) tma_load_2d(sQ, &tmQ, bar_k, 0, bh * L + r * BS);
-    for (int t = 0; t < nt; ++t) tma_load_2d(sK + t * T::BYTES, &tmK, bar_k, 0, bh * L + col_idx[rp + t0 + t] * BS);
+    for (int t = 0; t < nt; ++t) tma_load_2d(sK + t * T::BYTES, &tmK, bar_k, 0, bh * L + col_of(t0 + t) * BS);
     if (with_v) {
       mbar_expect_tx(bar_v, nt * T::BYTES);
-      for (int t = 0; t < nt; ++t) tma_load_2d(sV + t * T::BYTES, &tmV, bar_v, 0, bh * L + col_idx[rp + t0 + t] * BS);
+      for (int t = 0; t < nt; ++t) tma_load_2d(sV + t * T::BYTES, &tmV, bar_v, 0, bh * L + col_of(t0 + t) * BS);
     }
   };
 
@@ -192,7 +195,7 @@ __global__ void __launch_bounds__(FWD_THREADS) k_fwd_fused(const __grid_constant
       for (int p = 0; p < npairs; ++p) {
         const int t = 2 * p + hf;
         const bool mine = t < nt;
-        const int c = mine ? col_idx[rp + t0 + t] : 0;
+        const int c = mine ? col_of(t0 + t) : 0;
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
           uint32_t v[32];
@@ -214,7 +217,7 @@ __global__ void __launch_bounds__(FWD_THREADS) k_fwd_fused(const __grid_constant
       for (int p = 0; p < npairs; ++p) {
         const int t = 2 * p + hf;
         const bool mine = t < nt;
-        const int c = mine ? col_idx[rp + t0 + t] : 0;
+        const int c = mine ? col_of(t0 + t) : 0;
         uint32_t v0[32], v1[32];
         tmem_ld32(t_lane + s_col(2 * p), v0);
         tmem_ld32(t_lane + s_col(2 * p) + 32, v1);
@@ -271,7 +274,7 @@ __global__ void __launch_bounds__(FWD_THREADS) k_fwd_fused(const __grid_constant
       for (int p = 0; p < npairs; ++p) {
         const int t = 2 * p + hf;
         const bool mine = t < nt;
-        const int c = mine ? col_idx[rp + t0 + t] : 0;
+        const int c = mine ? col_of(t0 + t) : 0;
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
           uint32_t v[32];
@@ -308,7 +311,7 @@ __global__ void __launch_bounds__(FWD_THREADS) k_fwd_fused(const __grid_constant
     for (int p = 0; p < npairs; ++p) {
       const int t = 2 * p + hf;
       const bool mine = t < nt;
-      const int c = mine ? col_idx[rp + t0 + t] : 0;
+      const int c = mine ? col_of(t0 + t) : 0;
       uint32_t w[32];
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
@@ -457,7 +460,7 @@ static int fwd_launch(spion_ctx* c, TcState* s, const void* Q, const void* K, co
   const float floor_v = keypad ? 0.0f : -100.0f;
 #define SPION_FWD_LAUNCH(SP, SB)                                                                                  \
   k_fwd_fused<D, SP, SB><<<grid, FWD_THREADS, fwd_smem_bytes<D>(), c->stream>>>(                                   \
-      mq, mk, mv, mp, (__nv_bfloat16*)O, lse, keypad, vw.row_ptr, vw.col_idx, vw.submask, c->L, vw.nnzb, c->scale, \
+      mq, mk, mv, mp, (__nv_bfloat16*)O, lse, keypad, vw.row_info, vw.col_idx, vw.submask, c->L, vw.nnzb, c->scale, \
       floor_v, c->status_dev, (unsigned long long*)c->trace)
   if (P64) { if (vw.submask) SPION_FWD_LAUNCH(true, true); else SPION_FWD_LAUNCH(true, false); }
   else { if (vw.submask) SPION_FWD_LAUNCH(false, true); else SPION_FWD_LAUNCH(false, false); }

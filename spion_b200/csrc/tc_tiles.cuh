@@ -52,6 +52,7 @@ struct TcState {
   EncodeTiledFn encode = nullptr;
   int stages = 0;               // debugging switches (SPION_TC_STAGES): bit 6 = split row kernels
   float* lse_ws = nullptr;      // [BH*L] log-sum-exp workspace for the calls that do not expose it
+  int4* row_info = nullptr;     // per block row: {row_ptr, blocks, col0 | col1 << 16, col2 | col3 << 16}: one load instead of two dependent ones
   // 32-wide masks run on 64-wide super-blocks: derived structure + which 32x32 quarters are selected
   bool super = false;
   int nb64 = 0, nnzb64 = 0;
@@ -66,12 +67,13 @@ struct TcState {
 struct TcView {
   const int32_t *row_ptr, *col_idx, *col_ptr, *row_idx, *csc_pos;
   const uint8_t* submask;       // nullptr: every block is fully selected
+  const int4* row_info;
   int nb, nnzb;
 };
 inline TcView tc_view(const spion_ctx* c, const TcState* s) {
   if (s->super)
-    return TcView{s->row_ptr64, s->col_idx64, s->col_ptr64, s->row_idx64, s->csc_pos64, s->submask, s->nb64, s->nnzb64};
-  return TcView{c->row_ptr, c->col_idx, c->col_ptr, c->row_idx, c->csc_pos, nullptr, c->nb, c->nnzb};
+    return TcView{s->row_ptr64, s->col_idx64, s->col_ptr64, s->row_idx64, s->csc_pos64, s->submask, s->row_info, s->nb64, s->nnzb64};
+  return TcView{c->row_ptr, c->col_idx, c->col_ptr, c->row_idx, c->csc_pos, nullptr, s->row_info, c->nb, c->nnzb};
 }
 
 inline int make_map(TcState* s, CUtensorMap* m, const void* base, uint64_t rows, uint32_t cols, uint32_t box_rows) {

@@ -1,0 +1,38 @@
+"""bench.py contract checks that need no GPU: the reference arm prints one JSON line with the keys the
+driver reads, and the algorithmic byte / flop formulas agree with their definitions."""
+import json
+import os
+import subprocess
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_reference_arm_prints_contract_line():
+    out = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--workload", "tiny",
+                          "--steps", "1", "--warmup", "1"], stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True,
+                         timeout=300)
+    assert out.returncode == 0, out.stderr[-2000:]
+    line = json.loads(out.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference" and line["unit"] == "Mtokens/s" and line["higher_is_better"] is True
+    for key in ("metric", "value", "n_gpus", "steps", "warmup", "ms_per_step", "scaling", "config", "cpu_baseline", "e2e"):
+        assert key in line
+    assert line["cpu_baseline"]["kind"] == "port" and line["cpu_baseline"]["cores"] >= 1
+    assert line["e2e"]["h2d_bytes_per_step"] == 0 and line["e2e"]["d2h_bytes_per_step"] == 0
+    assert line["value"] > 0
+
+
+def test_algorithmic_formulas():
+    sys.path.insert(0, ROOT)
+    import bench
+    B, H, L, d, bs, nnzb, e = 8, 8, 4096, 64, 64, 205, 2
+    flops, fused_bytes, nnz = bench.algorithmic(B, H, L, d, bs, nnzb, e)
+    assert nnz == nnzb * bs * bs
+    assert flops == 12.0 * nnz * d * B * H                      # 2 SDDMM + 4 SpMM of 2*nnz*d each
+    assert fused_bytes == 12.0 * L * d * e * B * H
+    BH = B * H
+    ld, v = BH * L * d * e, BH * nnz
+    assert bench.stage_bytes("fused_fwd", BH, L, d, nnz, e, e, p_stored=True) == 4 * ld + 4 * BH * L + e * v
+    assert bench.stage_bytes("bwd_row", BH, L, d, nnz, e, e) == 5 * ld + 2 * e * v
+    assert bench.stage_bytes("spmm_dkdv", BH, L, d, nnz, e, e) == 2 * e * v + 4 * ld
+    assert bench.stage_flops("bwd_row", BH, d, nnz) == 4.0 * nnz * d * BH
