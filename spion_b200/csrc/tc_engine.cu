@@ -68,22 +68,28 @@ __global__ void __launch_bounds__(128) k_dp_ds(const __grid_constant__ CUtensorM
   const int nchunks = (nblk + NCH - 1) / NCH;
   bool a_loaded = false;
 
-  auto issue_loads = [&](int ch) {                             // thread 0 only
+  auto issue_loads = [&](int ch) {                             // all lanes of warp 0: one copy per lane
     const int t0 = ch * NCH, nt = min(NCH, nblk - t0);
-    mbar_expect_tx(bar_k, (a_loaded ? 0 : T::BYTES) + nt * T::BYTES);
-    if (!a_loaded) tma_load_2d(sA, &tmdO, bar_k, 0, bh * L + r * BS);
-    for (int t = 0; t < nt; ++t) tma_load_2d(sB + t * T::BYTES, &tmV, bar_k, 0, bh * L + col_of(t0 + t) * BS);
-    mbar_expect_tx(bar_p, nt * VT_BYTES);
-    for (int t = 0; t < nt; ++t)
-      tma_load_2d(sP + t * VT_BYTES, &tmP, bar_p, 0, (int)(((size_t)bh * nnzb + rp + t0 + t) * BS));
+    if (lane == 0) {
+      mbar_expect_tx(bar_k, (a_loaded ? 0 : T::BYTES) + nt * T::BYTES);
+      mbar_expect_tx(bar_p, nt * VT_BYTES);
+    }
+    __syncwarp();
+    if (lane == 0 && !a_loaded) tma_load_2d(sA, &tmdO, bar_k, 0, bh * L + r * BS);
+    if (lane >= 1 && lane <= nt) tma_load_2d(sB + (lane - 1) * T::BYTES, &tmV, bar_k, 0, bh * L + col_of(t0 + lane - 1) * BS);
+    if (lane >= 9 && lane < 9 + nt)
+      tma_load_2d(sP + (lane - 9) * VT_BYTES, &tmP, bar_p, 0, (int)(((size_t)bh * nnzb + rp + t0 + lane - 9) * BS));
   };
 
-  if (tid == 0) {
-    s_abort = *reinterpret_cast<volatile int*>(status);
-    mbar_init(bar_k, 1);
-    mbar_init(bar_p, 1);
-    mbar_init(bar_s, 1);
-    fence_barrier_init();
+  if (q == 0) {
+    if (lane == 0) {
+      s_abort = *reinterpret_cast<volatile int*>(status);
+      mbar_init(bar_k, 1);
+      mbar_init(bar_p, 1);
+      mbar_init(bar_s, 1);
+      fence_barrier_init();
+    }
+    __syncwarp();
     if (s_abort == 0 && nblk > 0) issue_loads(0);
   }
   a_loaded = true;
@@ -121,8 +127,9 @@ __global__ void __launch_bounds__(128) k_dp_ds(const __grid_constant__ CUtensorM
 
   for (int ch = 0; ch < nchunks && ok; ++ch) {
     const int t0 = ch * NCH, nt = min(NCH, nblk - t0);
-    if (ch > 0 && tid == 0) {
-      bulk_wait_read_all();                                    // the previous dS tiles have left shared memory
+    if (ch > 0 && q == 0) {
+      if (lane == 0) bulk_wait_read_all();                     // the previous dS tiles have left shared memory
+      __syncwarp();
       issue_loads(ch);
     }
     if (!__syncthreads_and(mbar_wait(bar_k, ph_k))) { if (tid == 0) report(status, ERR_LOAD_WAIT); ok = false; break; }
@@ -230,24 +237,30 @@ __global__ void __launch_bounds__(128) k_bwd_row(const __grid_constant__ CUtenso
   const uint32_t dq_col = single ? 0u : 128u;
   bool a_loaded = false;
 
-  auto issue_loads = [&](int ch) {                             // thread 0 only
+  auto issue_loads = [&](int ch) {                             // all lanes of warp 0: one copy per lane
     const int t0 = ch * NCH, nt = min(NCH, nblk - t0);
-    mbar_expect_tx(bar_v, (a_loaded ? 0 : T::BYTES) + nt * T::BYTES);
-    if (!a_loaded) tma_load_2d(sA, &tmdO, bar_v, 0, bh * L + r * BS);
-    for (int t = 0; t < nt; ++t) tma_load_2d(sB + t * T::BYTES, &tmV, bar_v, 0, bh * L + col_of(t0 + t) * BS);
-    mbar_expect_tx(bar_p, nt * VT_BYTES);
-    for (int t = 0; t < nt; ++t)
-      tma_load_2d(sP + t * VT_BYTES, &tmP, bar_p, 0, (int)(((size_t)bh * nnzb + rp + t0 + t) * BS));
+    if (lane == 0) {
+      mbar_expect_tx(bar_v, (a_loaded ? 0 : T::BYTES) + nt * T::BYTES);
+      mbar_expect_tx(bar_p, nt * VT_BYTES);
+    }
+    __syncwarp();
+    if (lane == 0 && !a_loaded) tma_load_2d(sA, &tmdO, bar_v, 0, bh * L + r * BS);
+    if (lane >= 1 && lane <= nt) tma_load_2d(sB + (lane - 1) * T::BYTES, &tmV, bar_v, 0, bh * L + col_of(t0 + lane - 1) * BS);
+    if (lane >= 9 && lane < 9 + nt)
+      tma_load_2d(sP + (lane - 9) * VT_BYTES, &tmP, bar_p, 0, (int)(((size_t)bh * nnzb + rp + t0 + lane - 9) * BS));
   };
 
-  if (tid == 0) {
-    s_abort = *reinterpret_cast<volatile int*>(status);
-    mbar_init(bar_v, 1);
-    mbar_init(bar_p, 1);
-    mbar_init(bar_s, 1);
-    mbar_init(bar_k, 1);
-    mbar_init(bar_o, 1);
-    fence_barrier_init();
+  if (q == 0) {
+    if (lane == 0) {
+      s_abort = *reinterpret_cast<volatile int*>(status);
+      mbar_init(bar_v, 1);
+      mbar_init(bar_p, 1);
+      mbar_init(bar_s, 1);
+      mbar_init(bar_k, 1);
+      mbar_init(bar_o, 1);
+      fence_barrier_init();
+    }
+    __syncwarp();
     if (s_abort == 0 && nblk > 0) issue_loads(0);
   }
   a_loaded = true;
@@ -285,8 +298,9 @@ __global__ void __launch_bounds__(128) k_bwd_row(const __grid_constant__ CUtenso
 
   for (int ch = 0; ch < nchunks && ok; ++ch) {
     const int t0 = ch * NCH, nt = min(NCH, nblk - t0);
-    if (ch > 0 && tid == 0) {
-      bulk_wait_read_all();                                    // previous dS tiles have left shared memory
+    if (ch > 0 && q == 0) {
+      if (lane == 0) bulk_wait_read_all();                     // previous dS tiles have left shared memory
+      __syncwarp();
       issue_loads(ch);
     }
     if (!__syncthreads_and(mbar_wait(bar_v, ph_v))) { if (tid == 0) report(status, ERR_LOAD_WAIT); ok = false; break; }
@@ -302,9 +316,13 @@ __global__ void __launch_bounds__(128) k_bwd_row(const __grid_constant__ CUtenso
       mma_commit(bar_s);
     }
     const bool w1 = mbar_wait(bar_s, ph_s);
-    if (tid == 0 && w1) {                                      // V consumed: bring K into the same buffers
-      mbar_expect_tx(bar_k, nt * T::BYTES);
-      for (int t = 0; t < nt; ++t) tma_load_2d(sB + t * T::BYTES, &tmK, bar_k, 0, bh * L + col_of(t0 + t) * BS);
+    if (q == 0) {                                              // V consumed: bring K into the same buffers
+      const bool all_ok = __all_sync(0xffffffffu, w1);
+      if (all_ok) {
+        if (lane == 0) mbar_expect_tx(bar_k, nt * T::BYTES);
+        __syncwarp();
+        if (lane < nt) tma_load_2d(sB + lane * T::BYTES, &tmK, bar_k, 0, bh * L + col_of(t0 + lane) * BS);
+      }
     }
     const bool w2 = mbar_wait(bar_p, ph_p);
     if (!__syncthreads_and(w1 && w2)) { if (tid == 0) report(status, ERR_MMA_WAIT); ok = false; break; }

@@ -116,24 +116,31 @@ __global__ void __launch_bounds__(FWD_THREADS) k_fwd_fused(const __grid_constant
 
   // tile t of a chunk: accumulator columns (long rows stream one pair through [64,128))
   auto s_col = [&](int t) -> uint32_t { return single ? (uint32_t)(t >> 1) * 64u : 64u; };
-  auto issue_loads = [&](int ch, bool with_v) {                // thread 0 only
+  // Called by all lanes of warp 0: lane 0 announces the bytes, then one lane per tile issues its copy
+  // (a single thread needs about 0.1 us per copy; a row has up to nine).
+  auto issue_loads = [&](int ch, bool with_v) {
     const int t0 = ch * CH, nt = min(CH, nblk - t0);
-    mbar_expect_tx(bar_k, (q_loaded ? 0 : T::BYTES) + nt * T::BYTES);
-    if (!q_loaded) tma_load_2d(sQ, &tmQ, bar_k, 0, bh * L + r * BS);
-    for (int t = 0; t < nt; ++t) tma_load_2d(sK + t * T::BYTES, &tmK, bar_k, 0, bh * L + col_of(t0 + t) * BS);
-    if (with_v) {
-      mbar_expect_tx(bar_v, nt * T::BYTES);
-      for (int t = 0; t < nt; ++t) tma_load_2d(sV + t * T::BYTES, &tmV, bar_v, 0, bh * L + col_of(t0 + t) * BS);
+    if (lane == 0) {
+      mbar_expect_tx(bar_k, (q_loaded ? 0 : T::BYTES) + nt * T::BYTES);
+      if (with_v) mbar_expect_tx(bar_v, nt * T::BYTES);
     }
+    __syncwarp();
+    if (lane == 0 && !q_loaded) tma_load_2d(sQ, &tmQ, bar_k, 0, bh * L + r * BS);
+    if (lane >= 1 && lane <= nt) tma_load_2d(sK + (lane - 1) * T::BYTES, &tmK, bar_k, 0, bh * L + col_of(t0 + lane - 1) * BS);
+    if (with_v && lane >= 9 && lane < 9 + nt)
+      tma_load_2d(sV + (lane - 9) * T::BYTES, &tmV, bar_v, 0, bh * L + col_of(t0 + lane - 9) * BS);
   };
 
-  if (tid == 0) {
-    s_abort = *reinterpret_cast<volatile int*>(status);
-    mbar_init(bar_k, 1);
-    mbar_init(bar_v, 1);
-    mbar_init(bar_s, 1);
-    mbar_init(bar_o, 1);
-    fence_barrier_init();
+  if (q == 0) {
+    if (lane == 0) {
+      s_abort = *reinterpret_cast<volatile int*>(status);
+      mbar_init(bar_k, 1);
+      mbar_init(bar_v, 1);
+      mbar_init(bar_s, 1);
+      mbar_init(bar_o, 1);
+      fence_barrier_init();
+    }
+    __syncwarp();
     if (s_abort == 0 && nblk > 0) issue_loads(0, single);      // operands are on their way before TMEM is set up
   }
   q_loaded = true;
@@ -187,7 +194,7 @@ __global__ void __launch_bounds__(FWD_THREADS) k_fwd_fused(const __grid_constant
   const int npairs = single ? 2 : 1;
   const bool online = STORE_P && !single;                        // denominator needed before P is written
   for (int ch = 0; ch < nchunks; ++ch) {
-    if (ch > 0 && tid == 0) issue_loads(ch, false);
+    if (ch > 0 && q == 0) issue_loads(ch, false);
     ok = produce_s(ch);
     if (!ok) break;
     const int t0 = ch * CH, nt = min(CH, nblk - t0);
@@ -262,7 +269,7 @@ __global__ void __launch_bounds__(FWD_THREADS) k_fwd_fused(const __grid_constant
   // ------------------------------------------------------------------ pass B: exp, P -> smem, O += P V
   for (int ch = 0; ch < nchunks && ok; ++ch) {
     if (!single) {
-      if (tid == 0) issue_loads(ch, true);
+      if (q == 0) issue_loads(ch, true);
       ok = produce_s(ch);
       if (!ok) break;
     }
