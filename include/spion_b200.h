@@ -161,6 +161,12 @@ int spion_dense_attn_backward(spion_ctx* ctx, const float* Qt, const float* Kt, 
 int spion_mean_attention_map(const float* attn, int batch, int heads, int L, int transposed,
                              float* A, void* cuda_stream);
 
+/* The same mean taken from block-tile probabilities ([BH, nnzb, bs, bs], what the native forward
+ * returns): with the full mask this is the warm-up phase without a [B,H,L,L] tensor in the
+ * reference's layout.  Cells of unselected blocks are 0.  blk_row / col_idx: block CSR (device). */
+int spion_mean_map_tiles(const void* P, int dtype, const int32_t* blk_row, const int32_t* col_idx,
+                         int block_size, int nnzb, int num_batches, int L, float* A, void* cuda_stream);
+
 /* ------------------------------------------------------------ pattern discovery ---- */
 
 /* Replaces the inline driver block main_conv_ff.py:255-279 (and its flood_fill, :35-62):

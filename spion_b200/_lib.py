@@ -40,6 +40,7 @@ SIGNATURES = {
     "spion_dense_attn_forward": (c_int, [c_void_p] * 7),
     "spion_dense_attn_backward": (c_int, [c_void_p] * 12),
     "spion_mean_attention_map": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "spion_mean_map_tiles": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
     "spion_discover_pattern": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_double] + [c_void_p] * 13),
     "spion_build_structure": (c_int, [c_void_p, c_int] + [c_void_p] * 10),
     "spion_expand_csr": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),

@@ -60,7 +60,10 @@ class Attention(nn.Module):
         self.W_k = nn.Linear(self.dim, self.num_head * self.head_dim)
         self.W_v = nn.Linear(self.dim, self.num_head * self.head_dim)
 
-        if not inference:
+        if not inference and self.native:
+            from .native import DenseViaBlocks
+            self.attn = DenseViaBlocks(config, dtype=self.native_dtype, keypad=self.with_keypad)
+        elif not inference:
             num_batches = config["num_head"] * config["batch_size"]
             if self.with_keypad:
                 attn_cpp = Attention._cuda_mask_compile_module()
@@ -80,7 +83,10 @@ class Attention(nn.Module):
         K = self.split_heads(self.W_k(X))
         V = self.split_heads(self.W_v(X))
         with torch.autocast(device_type="cuda", enabled=False):
-            if mat is None:
+            if mat is None and self.native:
+                attn_out, attn = self.attn(Q, K, V, mask.float())
+                attn_out = attn_out.to(X.dtype)
+            elif mat is None:
                 attn_out, attn = self.attn(Q.float(), K.float(), V.float(), mask.float())
             elif self.native:
                 attn_out, attn = self.block_attn(Q, K, V, mask.float(), mat)

@@ -224,7 +224,43 @@ __global__ void mean_map_kernel(const float* __restrict__ attn, int B, int H, in
   }
 }
 
+// Mean over the (b,h) matrices of block-tile probabilities: one CTA per selected block.
+// A[i, j] = (1 / BH) * sum_bh P[bh][blk][i % bs][j % bs]; cells of unselected blocks stay 0.
+template <typename T>
+__global__ void __launch_bounds__(256) mean_map_tiles_kernel(const T* __restrict__ P, const int32_t* __restrict__ blk_row,
+                                                             const int32_t* __restrict__ col_idx, int bs, int nnzb,
+                                                             int BH, int L, float* __restrict__ A) {
+  const int blk = blockIdx.x;
+  const int r = blk_row[blk], c = col_idx[blk];
+  const int n = bs * bs;
+  const float inv = 1.0f / (float)BH;
+  for (int e = threadIdx.x; e < n; e += blockDim.x) {
+    float acc = 0.f;
+    const T* src = P + (size_t)blk * n + e;
+    for (int bh = 0; bh < BH; ++bh) acc += to_f32(src[(size_t)bh * nnzb * n]);
+    A[(size_t)(r * bs + e / bs) * L + c * bs + e % bs] = acc * inv;
+  }
+}
+
 }  // namespace
+
+extern "C" int spion_mean_map_tiles(const void* P, int dtype, const int32_t* blk_row, const int32_t* col_idx,
+                                    int block_size, int nnzb, int num_batches, int L, float* A, void* cuda_stream) {
+  if (!P || !blk_row || !col_idx || !A) return SPION_ERR_ARG;
+  if (block_size < 1 || nnzb < 0 || num_batches < 1 || L < 1 || L % block_size != 0) return SPION_ERR_SHAPE;
+  if (dtype != SPION_F32 && dtype != SPION_BF16) return SPION_ERR_ARG;
+  cudaStream_t st = (cudaStream_t)cuda_stream;
+  SPION_CUDA_TRY(cudaMemsetAsync(A, 0, (size_t)L * L * sizeof(float), st));
+  if (nnzb == 0) return SPION_OK;
+  if (dtype == SPION_F32)
+    mean_map_tiles_kernel<float><<<nnzb, 256, 0, st>>>((const float*)P, blk_row, col_idx, block_size, nnzb,
+                                                       num_batches, L, A);
+  else
+    mean_map_tiles_kernel<__nv_bfloat16><<<nnzb, 256, 0, st>>>((const __nv_bfloat16*)P, blk_row, col_idx, block_size,
+                                                               nnzb, num_batches, L, A);
+  SPION_LAUNCH_CHECK();
+  return SPION_OK;
+}
 
 extern "C" int spion_discover_pattern(const float* A, int L, int block_size, int conv_kind, int F, int select,
                                       double param, uint8_t* mat, float* pooled, float* thresh, int32_t* nnzb,

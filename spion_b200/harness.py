@@ -83,7 +83,9 @@ class Encoder(nn.Module):
         for i, layer in enumerate(self.layers):
             if mat_lst is None:
                 X, attn = layer(X, mask)
-                if is_attn:
+                if is_attn and layer.mha.native:
+                    maps.append(layer.mha.attn.mean_attention_map(attn))      # from block tiles
+                elif is_attn:
                     # attn is the permuted view of the S^T-stored tensor: its base is contiguous
                     maps.append(mean_attention_map(attn.permute(0, 1, 3, 2), transposed_storage=True))
             else:

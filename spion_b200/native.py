@@ -65,12 +65,25 @@ class BlockSparseAttention(nn.Module):
         check(lib.spion_set_stream(self.handle, _lib.current_stream_ptr()))
         check(lib.spion_set_pattern(self.handle, ptr(m8)), "spion_set_pattern")
         self.nnzb = int(lib.spion_pattern_nnzb(self.handle))
+        from .pattern import pattern_from_mask
+        self._pattern = pattern_from_mask(m8, self.bs)          # block CSR for the helpers above
         self._mask_key = (mat.data_ptr(), mat._version)
         return self.nnzb
 
     @property
     def nnz(self) -> int:
         return self.nnzb * self.bs * self.bs
+
+    def mean_attention_map(self, P_tiles: torch.Tensor) -> torch.Tensor:
+        """A = mean over (b,h) of the probabilities this module returned ([BH, nnzb, bs, bs] tiles) as an
+        [L, L] fp32 map (zero outside the mask): what the encoder hands to pattern discovery
+        (models/model_transformer.py:137), without a dense [B, H, L, L] tensor."""
+        pat = self._pattern
+        A = torch.empty(self.L, self.L, dtype=torch.float32, device=P_tiles.device)
+        check(lib.spion_mean_map_tiles(ptr(P_tiles), _DTYPES[self.dtype], ptr(pat.blk_row), ptr(pat.col_idx), self.bs,
+                                       self.nnzb, self.BH, self.L, ptr(A), _lib.current_stream_ptr()),
+              "spion_mean_map_tiles")
+        return A
 
     def launch_count(self) -> int:
         return int(lib.spion_launch_count(self.handle))
@@ -102,6 +115,25 @@ class BlockSparseAttention(nn.Module):
         if self.keypad:
             pen = (1e6 * (1 - mask.to(torch.float32)))[:, None, :].expand(self.B, self.H, self.L).contiguous()
         return self._fn.apply(query, key, value, pen)
+
+
+class DenseViaBlocks(nn.Module):
+    """Warm-up (dense) attention through the same block kernels with the full mask: the dense phase of
+    the reference (models/attention_cuda.py) without fp32 up-casts, transposed copies or a
+    [B, H, L, L] tensor in the reference's S^T layout.  ``forward(query, key, value, mask)`` ->
+    ``(out, P_tiles)``; ``mean_attention_map(P_tiles)`` gives the [L, L] map for pattern discovery."""
+
+    def __init__(self, config, dtype=torch.float32, keypad: bool = False, device=None):
+        super().__init__()
+        self.block = BlockSparseAttention(config, dtype=dtype, keypad=keypad, device=device)
+        nb = config["max_seq_len"] // config["block_size"]
+        self.block.set_mask(torch.ones(nb, nb, dtype=torch.uint8, device=self.block.device))
+
+    def forward(self, query, key, value, mask=None):
+        return self.block(query, key, value, mask)
+
+    def mean_attention_map(self, P_tiles):
+        return self.block.mean_attention_map(P_tiles)
 
 
 def _make_function(mod: BlockSparseAttention):

@@ -84,3 +84,28 @@ def test_bounded_wait_reports_and_context_survives():
     assert rc == -4, "the wait must give up and be reported as SPION_ERR_TIMEOUT"
     mod.check_device_status()                                              # word was cleared
     check(1, 1, 128, 64, 64, np.ones((2, 2), np.uint8))                    # the GPU context still works
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_mean_map_from_tiles_and_dense_via_blocks(dtype):
+    from spion_b200.native import DenseViaBlocks
+    B, H, L, d, bs = 2, 2, 256, 64, 64
+    Q, K, V = [t.to(dtype) for t in synthetic.qkv(9, B, H, L, d, n=3)]
+    mod = DenseViaBlocks(cfg(B, H, L, d, bs), dtype=dtype)
+    out, P = mod(Q.cuda(), K.cuda(), V.cuda())
+    A = mod.mean_attention_map(P)
+    O, Pd = oatt.dense_attention(Q.float(), K.float(), V.float())
+    want = Pd.mean(0).mean(0)
+    tol = 1e-6 if dtype == torch.float32 else 2e-2 * float(want.max())
+    assert float((A.cpu() - want).abs().max()) <= tol
+    assert rel(out, O) <= (1e-4 if dtype == torch.float32 else REL)
+    # sparse mask: cells outside the mask are exactly zero
+    from spion_b200.native import BlockSparseAttention
+    mat = synthetic.band_random_mask(3, L // bs, 0.4)
+    sp = BlockSparseAttention(cfg(B, H, L, d, bs), dtype=dtype)
+    _, Ps = sp(Q.cuda(), K.cuda(), V.cuda(), None, torch.as_tensor(mat).cuda())
+    As = sp.mean_attention_map(Ps).cpu()
+    M = oatt.expand_mask(mat, bs)
+    assert float((As * (1 - M)).abs().max()) == 0.0
+    _, Pm = oatt.sparse_attention(Q.float(), K.float(), V.float(), mat, bs)
+    assert float((As - Pm.mean(0).mean(0)).abs().max()) <= tol
