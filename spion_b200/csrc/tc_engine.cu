@@ -56,12 +56,12 @@ __global__ void __launch_bounds__(128) k_dp_ds(const __grid_constant__ CUtensorM
   uint32_t* slot_ptr = reinterpret_cast<uint32_t*>(smem_raw + (slot - raw));
   __shared__ int s_abort;
 
-  const int r = blockIdx.x, bh = blockIdx.y;
+  const int bh = blockIdx.y;
   const int tid = threadIdx.x, q = tid >> 5, lane = tid & 31;
   const int hf = lane >> 4;
   const int row = q * 16 + (lane & 15);
-  const int4 ri = row_info[r];
-  const int rp = ri.x, nblk = ri.y;
+  const int4 ri = row_info[blockIdx.x];                        // records are sorted, longest row first
+  const int rp = ri.x, nblk = ri.y & 0xffff, r = ri.y >> 16;
   auto col_of = [&](int t) -> int {                            // block column of the row's t-th block
     return t < 4 ? ((t & 2 ? ri.w : ri.z) >> ((t & 1) * 16)) & 0xffff : col_idx[rp + t];
   };
@@ -222,12 +222,12 @@ __global__ void __launch_bounds__(128) k_bwd_row(const __grid_constant__ CUtenso
   // (b,h) matrices are walked in descending order: the forward pass wrote P in ascending order, so the
   // most recently written tiles (still in L2) are read first, and the dS tiles this kernel writes
   // last are the ones the column kernel, which ascends, reads first.
-  const int r = blockIdx.x, bh = gridDim.y - 1 - blockIdx.y;
+  const int bh = gridDim.y - 1 - blockIdx.y;
   const int tid = threadIdx.x, q = tid >> 5, lane = tid & 31;
   const int hf = lane >> 4;
   const int row = q * 16 + (lane & 15);
-  const int4 ri = row_info[r];
-  const int rp = ri.x, nblk = ri.y;
+  const int4 ri = row_info[blockIdx.x];                        // records are sorted, longest row first
+  const int rp = ri.x, nblk = ri.y & 0xffff, r = ri.y >> 16;
   auto col_of = [&](int t) -> int {                            // block column of the row's t-th block
     return t < 4 ? ((t & 2 ? ri.w : ri.z) >> ((t & 1) * 16)) & 0xffff : col_idx[rp + t];
   };
@@ -607,13 +607,21 @@ __global__ void __launch_bounds__(256) k_convert_tiles(__nv_bfloat16* __restrict
   }
 }
 
+// One record per block row, sorted by descending number of blocks (ties: ascending row), so that a
+// grid walking the records starts its longest rows first.  One CTA; nb <= SPION_MAX_NB.
+//   {row_ptr, blocks | row << 16, col0 | col1 << 16, col2 | col3 << 16}
 __global__ void k_row_info(const int32_t* __restrict__ row_ptr, const int32_t* __restrict__ col_idx, int nb,
                            int4* __restrict__ info) {
-  for (int r = blockIdx.x * blockDim.x + threadIdx.x; r < nb; r += gridDim.x * blockDim.x) {
-    const int rp = row_ptr[r], n = row_ptr[r + 1] - rp;
+  __shared__ int s_n[SPION_MAX_NB];
+  for (int r = threadIdx.x; r < nb; r += blockDim.x) s_n[r] = row_ptr[r + 1] - row_ptr[r];
+  __syncthreads();
+  for (int r = threadIdx.x; r < nb; r += blockDim.x) {
+    const int rp = row_ptr[r], n = s_n[r];
+    int rank = 0;
+    for (int o = 0; o < nb; ++o) rank += (s_n[o] > n) || (s_n[o] == n && o < r);
     int c[4] = {0, 0, 0, 0};
     for (int t = 0; t < 4 && t < n; ++t) c[t] = col_idx[rp + t];
-    info[r] = make_int4(rp, n, c[0] | (c[1] << 16), c[2] | (c[3] << 16));
+    info[rank] = make_int4(rp, n | (r << 16), c[0] | (c[1] << 16), c[2] | (c[3] << 16));
   }
 }
 
@@ -791,7 +799,7 @@ int tc_engine_prepare(spion_ctx* c) {
   }
   const TcView vw = tc_view(c, s);
   if (!s->row_info && cudaMalloc(&s->row_info, (size_t)SPION_MAX_NB * sizeof(int4)) != cudaSuccess) return SPION_ERR_ALLOC;
-  k_row_info<<<4, 128, 0, c->stream>>>(vw.row_ptr, vw.col_idx, vw.nb, s->row_info);
+  k_row_info<<<1, 512, 0, c->stream>>>(vw.row_ptr, vw.col_idx, vw.nb, s->row_info);
   SPION_LAUNCH_CHECK();
   c->launches += 1;
   return SPION_OK;

@@ -89,13 +89,15 @@ __global__ void __launch_bounds__(FWD_THREADS) k_fwd_fused(const __grid_constant
   };
   stamp(0);
 
-  const int r = blockIdx.x, bh = blockIdx.y;
+  // blockIdx.y walks the block rows from the longest to the shortest (the records are sorted), and
+  // all (b,h) matrices of one row length start together: the last wave holds only short rows.
+  const int bh = blockIdx.x;
   const int tid = threadIdx.x, q = tid >> 5, lane = tid & 31;
   const int hf = lane >> 4;                                    // 0: even tiles, 1: odd tiles
   const int row = q * 16 + (lane & 15);                        // row of the block this thread owns
 
-  const int4 ri = row_info[r];
-  const int rp = ri.x, nblk = ri.y;
+  const int4 ri = row_info[blockIdx.y];
+  const int rp = ri.x, nblk = ri.y & 0xffff, r = ri.y >> 16;
   auto col_of = [&](int t) -> int {                            // block column of the row's t-th block
     return t < 4 ? ((t & 2 ? ri.w : ri.z) >> ((t & 1) * 16)) & 0xffff : col_idx[rp + t];
   };
@@ -303,14 +305,17 @@ __global__ void __launch_bounds__(FWD_THREADS) k_fwd_fused(const __grid_constant
         }
       }
       const float l = l_part + __shfl_xor_sync(0xffffffffu, l_part, 16) + (float)(L - n_sel) * exp2f(-m2);
+      // 1/l as a sum of two bf16 values: the packed product then carries one rounding of the result only
       const float inv = 1.0f / l;
+      const float inv_h = bf16_hi(pack_bf16(0.f, inv));
+      const uint32_t inv_hi = pack_bf16(inv_h, inv_h), inv_lo = pack_bf16(inv - inv_h, inv - inv_h);
       lse_fixed = m2 + log2f(l);
 #pragma unroll
       for (int p = 0; p < npairs; ++p) {
         const int t = 2 * p + hf;
         if (t < nt) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) wp[p][j] = pack_bf16(bf16_lo(wp[p][j]) * inv, bf16_hi(wp[p][j]) * inv);
+          for (int j = 0; j < 32; ++j) wp[p][j] = fma_bf16x2(wp[p][j], inv_hi, mul_bf16x2(wp[p][j], inv_lo));
           store_row_swizzled(sP + t * VT_BYTES, row, wp[p]);
         }
       }
@@ -463,7 +468,7 @@ static int fwd_launch(spion_ctx* c, TcState* s, const void* Q, const void* K, co
     return rc;
   if (P64) { if ((rc = make_map(s, &mp, P64, vrows, BS, BS))) return rc; } else mp = mq;
   prof_mark(c, -1);
-  const dim3 grid(vw.nb, c->BH);
+  const dim3 grid(c->BH, vw.nb);
   const float floor_v = keypad ? 0.0f : -100.0f;
 #define SPION_FWD_LAUNCH(SP, SB)                                                                                  \
   k_fwd_fused<D, SP, SB><<<grid, FWD_THREADS, fwd_smem_bytes<D>(), c->stream>>>(                                   \
