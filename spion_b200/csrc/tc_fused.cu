@@ -76,7 +76,8 @@ __global__ void __launch_bounds__(FWD_THREADS) k_fwd_fused(const __grid_constant
   const uint32_t sV = sK + FWD_NCH * T::BYTES;
   const uint32_t sP = (D == 64) ? sK : sV + FWD_NCH * T::BYTES;            // P tiles reuse the K buffers
   const uint32_t bars = sV + FWD_NCH * T::BYTES + (D == 64 ? 0 : FWD_NCH * VT_BYTES);
-  const uint32_t bar_k = bars, bar_v = bars + 8, bar_s = bars + 16, bar_o = bars + 24, slot = bars + 32;
+  const uint32_t bar_k0 = bars, bar_v0 = bars + 8, bar_s = bars + 16, bar_o = bars + 24, slot = bars + 32;
+  const uint32_t bar_k1 = bars + 40, bar_v1 = bars + 48;          // second half of the buffers (long rows)
   uint32_t* slot_ptr = reinterpret_cast<uint32_t*>(smem_raw + (slot - raw));
   __shared__ int s_abort;
   // optional phase timestamps (ns) of this CTA: 8 slots per CTA, written by thread 0
@@ -114,38 +115,50 @@ __global__ void __launch_bounds__(FWD_THREADS) k_fwd_fused(const __grid_constant
   const int nchunks = (nblk + CH - 1) / CH;
   constexpr uint32_t ncols = 128u;
   constexpr uint32_t o_col = 0u;
-  bool q_loaded = false;
+  // Load jobs.  A short row has one (Q, K and V tiles of the row).  A long row has 2*nchunks: the K
+  // pairs of pass A, then the K and V pairs of pass B; job g uses buffers [2*(g&1), 2*(g&1)+1] and the
+  // barriers of that half, so job g+2 is requested as soon as job g has released its half and two
+  // jobs are in flight throughout.
+  const int njobs = nblk == 0 ? 0 : (single ? 1 : 2 * nchunks);
+  auto job_half = [&](int g) -> int { return single ? 0 : (g & 1); };
 
-  // tile t of a chunk: accumulator columns (long rows stream one pair through [64,128))
-  auto s_col = [&](int t) -> uint32_t { return single ? (uint32_t)(t >> 1) * 64u : 64u; };
   // Called by all lanes of warp 0: lane 0 announces the bytes, then one lane per tile issues its copy
   // (a single thread needs about 0.1 us per copy; a row has up to nine).
-  auto issue_loads = [&](int ch, bool with_v) {
+  auto issue_job = [&](int g) {
+    const bool with_v = single || g >= nchunks;
+    const int ch = (single || g < nchunks) ? g : g - nchunks;
     const int t0 = ch * CH, nt = min(CH, nblk - t0);
+    const int hb = job_half(g), b0 = 2 * hb;
+    const uint32_t bk = hb ? bar_k1 : bar_k0, bv = hb ? bar_v1 : bar_v0;
     if (lane == 0) {
-      mbar_expect_tx(bar_k, (q_loaded ? 0 : T::BYTES) + nt * T::BYTES);
-      if (with_v) mbar_expect_tx(bar_v, nt * T::BYTES);
+      mbar_expect_tx(bk, (g == 0 ? T::BYTES : 0) + nt * T::BYTES);
+      if (with_v) mbar_expect_tx(bv, nt * T::BYTES);
     }
     __syncwarp();
-    if (lane == 0 && !q_loaded) tma_load_2d(sQ, &tmQ, bar_k, 0, bh * L + r * BS);
-    if (lane >= 1 && lane <= nt) tma_load_2d(sK + (lane - 1) * T::BYTES, &tmK, bar_k, 0, bh * L + col_of(t0 + lane - 1) * BS);
+    if (lane == 0 && g == 0) tma_load_2d(sQ, &tmQ, bk, 0, bh * L + r * BS);
+    if (lane >= 1 && lane <= nt)
+      tma_load_2d(sK + (b0 + lane - 1) * T::BYTES, &tmK, bk, 0, bh * L + col_of(t0 + lane - 1) * BS);
     if (with_v && lane >= 9 && lane < 9 + nt)
-      tma_load_2d(sV + (lane - 9) * T::BYTES, &tmV, bar_v, 0, bh * L + col_of(t0 + lane - 9) * BS);
+      tma_load_2d(sV + (b0 + lane - 9) * T::BYTES, &tmV, bv, 0, bh * L + col_of(t0 + lane - 9) * BS);
   };
 
   if (q == 0) {
     if (lane == 0) {
       s_abort = *reinterpret_cast<volatile int*>(status);
-      mbar_init(bar_k, 1);
-      mbar_init(bar_v, 1);
+      mbar_init(bar_k0, 1);
+      mbar_init(bar_v0, 1);
+      mbar_init(bar_k1, 1);
+      mbar_init(bar_v1, 1);
       mbar_init(bar_s, 1);
       mbar_init(bar_o, 1);
       fence_barrier_init();
     }
     __syncwarp();
-    if (s_abort == 0 && nblk > 0) issue_loads(0, single);      // operands are on their way before TMEM is set up
+    if (s_abort == 0 && njobs > 0) {                           // operands are on their way before TMEM is set up
+      issue_job(0);
+      if (njobs > 1) issue_job(1);
+    }
   }
-  q_loaded = true;
   __syncthreads();
   if (s_abort != 0) return;
   if (q == 0) {
@@ -163,43 +176,35 @@ __global__ void __launch_bounds__(FWD_THREADS) k_fwd_fused(const __grid_constant
   constexpr uint32_t IDESC_O = make_idesc_bf16(64, D, 0, 1);
   const float sc2 = scale * LOG2E;
   const float* kp = keypad ? keypad + (size_t)bh * L : nullptr;
-  uint32_t ph_k = 0, ph_v = 0, ph_s = 0, ph_o = 0;
+  uint32_t ph_v = 0;                                             // one bit per half of the buffers
   bool ok = true;
 
-  // wait for the K tiles of chunk ch (already requested), run the S MMAs, wait for them
-  auto produce_s = [&](int ch) -> bool {
+  // tid 0: wait for the K tiles of job g (already requested) and issue the S MMAs of its chunk into
+  // accumulator columns col(t); the commit arrives on bar
+  auto issue_s = [&](int g, uint32_t pair_stride, uint32_t col0, uint32_t bar) -> bool {
+    const int ch = (single || g < nchunks) ? g : g - nchunks;
     const int t0 = ch * CH, nt = min(CH, nblk - t0);
-    if (!__syncthreads_and(mbar_wait(bar_k, ph_k))) { if (tid == 0) report(status, ERR_LOAD_WAIT); return false; }
-    ph_k ^= 1;
-    stamp(2);
-    if (tid == 0) {
-      tc_fence_after();
-      for (int t = 0; t < nt; ++t) {
-        const uint32_t d_addr = tmem + ((uint32_t)((t & 1) * 16) << 16) + s_col(t);
-#pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk)
-          mma_bf16(d_addr, T::kmajor(sQ, kk), T::kmajor(sK + t * T::BYTES, kk), IDESC_S, kk > 0);
-      }
-      mma_commit(bar_s);
-    }
-    if (!__syncthreads_and(mbar_wait(bar_s, ph_s))) { if (tid == 0) report(status, ERR_MMA_WAIT); return false; }
-    ph_s ^= 1;
+    const int hb = job_half(g), b0 = 2 * hb;
+    if (!mbar_wait(hb ? bar_k1 : bar_k0, (g >> 1) & 1)) { report(status, ERR_LOAD_WAIT); return false; }
     tc_fence_after();
-    stamp(3);
+    for (int t = 0; t < nt; ++t) {
+      const uint32_t d_addr = tmem + ((uint32_t)((t & 1) * 16) << 16) + col0 + (uint32_t)(t >> 1) * pair_stride;
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk)
+        mma_bf16(d_addr, T::kmajor(sQ, kk), T::kmajor(sK + (b0 + t) * T::BYTES, kk), IDESC_S, kk > 0);
+    }
+    mma_commit(bar);
     return true;
   };
 
-  // ------------------------------------------------------------------ pass A: row maximum
   float m2 = floor_v * LOG2E;
   float mraw = -INFINITY;
   float l_part = 0.f;
-  const int npairs = single ? 2 : 1;
   const bool online = STORE_P && !single;                        // denominator needed before P is written
-  for (int ch = 0; ch < nchunks; ++ch) {
-    if (ch > 0 && q == 0) issue_loads(ch, false);
-    ok = produce_s(ch);
-    if (!ok) break;
-    const int t0 = ch * CH, nt = min(CH, nblk - t0);
+
+  // Row statistics of one chunk whose pair p sits in columns colbase + 64 p: the maximum, and for
+  // `online` also the running sum of exponentials.
+  auto stats_math = [&](uint32_t colbase, int t0, int nt, int npairs) {
     if (!online) {
       for (int p = 0; p < npairs; ++p) {
         const int t = 2 * p + hf;
@@ -208,7 +213,7 @@ __global__ void __launch_bounds__(FWD_THREADS) k_fwd_fused(const __grid_constant
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
           uint32_t v[32];
-          tmem_ld32(t_lane + s_col(2 * p) + half * 32, v);
+          tmem_ld32(t_lane + colbase + p * 64 + half * 32, v);
           tmem_ld_wait();
           if (mine && quarter_ok(rp + t0 + t, half)) {
             if (!kp) {                                            // the scale is positive: compare raw scores
@@ -228,8 +233,8 @@ __global__ void __launch_bounds__(FWD_THREADS) k_fwd_fused(const __grid_constant
         const bool mine = t < nt;
         const int c = mine ? col_of(t0 + t) : 0;
         uint32_t v0[32], v1[32];
-        tmem_ld32(t_lane + s_col(2 * p), v0);
-        tmem_ld32(t_lane + s_col(2 * p) + 32, v1);
+        tmem_ld32(t_lane + colbase + p * 64, v0);
+        tmem_ld32(t_lane + colbase + p * 64 + 32, v1);
         tmem_ld_wait();
         float cm = -INFINITY;
         if (mine) {
@@ -255,71 +260,11 @@ __global__ void __launch_bounds__(FWD_THREADS) k_fwd_fused(const __grid_constant
         m2 = m_new;
       }
     }
-    if (!single) { tc_fence_before(); __syncthreads(); }        // the next chunk overwrites these columns
-  }
-  m2 = fmaxf(m2, mraw * sc2);
-  m2 = fmaxf(m2, __shfl_xor_sync(0xffffffffu, m2, 16));          // both owners of a row agree
-  float lse_fixed = 0.f;
-  if (online) {
-    const float l = l_part + __shfl_xor_sync(0xffffffffu, l_part, 16) + (float)(L - n_sel) * exp2f(-m2);
-    lse_fixed = m2 + log2f(l);
-    m2 = lse_fixed;                                               // pass B then produces normalised P directly
-    l_part = 0.f;
-  }
-  stamp(4);
+  };
 
-  // ------------------------------------------------------------------ pass B: exp, P -> smem, O += P V
-  for (int ch = 0; ch < nchunks && ok; ++ch) {
-    if (!single) {
-      if (q == 0) issue_loads(ch, true);
-      ok = produce_s(ch);
-      if (!ok) break;
-    }
-    const int t0 = ch * CH, nt = min(CH, nblk - t0);
-    if (STORE_P && single) {
-      // keep both tiles' exponentials packed in registers, normalise once the denominator is known
-      uint32_t wp[2][32];
-#pragma unroll
-      for (int p = 0; p < npairs; ++p) {
-        const int t = 2 * p + hf;
-        const bool mine = t < nt;
-        const int c = mine ? col_of(t0 + t) : 0;
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          uint32_t v[32];
-          tmem_ld32(t_lane + s_col(2 * p) + half * 32, v);
-          tmem_ld_wait();
-          if (mine && quarter_ok(rp + t0 + t, half)) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 2) {
-              float h0 = m2, h1 = m2;
-              if (kp) { h0 = fmaf(kp[c * BS + half * 32 + j], LOG2E, m2); h1 = fmaf(kp[c * BS + half * 32 + j + 1], LOG2E, m2); }
-              const float e0 = ex2(fmaf(__uint_as_float(v[j]), sc2, -h0)), e1 = ex2(fmaf(__uint_as_float(v[j + 1]), sc2, -h1));
-              l_part += e0 + e1;
-              wp[p][half * 16 + (j >> 1)] = pack_bf16(e0, e1);
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 16; ++j) wp[p][half * 16 + j] = 0u;
-          }
-        }
-      }
-      const float l = l_part + __shfl_xor_sync(0xffffffffu, l_part, 16) + (float)(L - n_sel) * exp2f(-m2);
-      // 1/l as a sum of two bf16 values: the packed product then carries one rounding of the result only
-      const float inv = 1.0f / l;
-      const float inv_h = bf16_hi(pack_bf16(0.f, inv));
-      const uint32_t inv_hi = pack_bf16(inv_h, inv_h), inv_lo = pack_bf16(inv - inv_h, inv - inv_h);
-      lse_fixed = m2 + log2f(l);
-#pragma unroll
-      for (int p = 0; p < npairs; ++p) {
-        const int t = 2 * p + hf;
-        if (t < nt) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) wp[p][j] = fma_bf16x2(wp[p][j], inv_hi, mul_bf16x2(wp[p][j], inv_lo));
-          store_row_swizzled(sP + t * VT_BYTES, row, wp[p]);
-        }
-      }
-    } else {
+  // Exponentials of one chunk against the fixed m2 (the row maximum, or the log-sum-exp when the
+  // denominator is already known), packed to bf16 and stored as the K-major P tiles b0 + t.
+  auto prob_math = [&](uint32_t colbase, int b0, int t0, int nt, int npairs) {
     for (int p = 0; p < npairs; ++p) {
       const int t = 2 * p + hf;
       const bool mine = t < nt;
@@ -328,7 +273,7 @@ __global__ void __launch_bounds__(FWD_THREADS) k_fwd_fused(const __grid_constant
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
         uint32_t v[32];
-        tmem_ld32(t_lane + s_col(2 * p) + half * 32, v);
+        tmem_ld32(t_lane + colbase + p * 64 + half * 32, v);
         tmem_ld_wait();
         if (mine && quarter_ok(rp + t0 + t, half)) {
 #pragma unroll
@@ -344,43 +289,161 @@ __global__ void __launch_bounds__(FWD_THREADS) k_fwd_fused(const __grid_constant
           for (int j = 0; j < 16; ++j) w[half * 16 + j] = 0u;
         }
       }
-      if (mine) store_row_swizzled(sP + t * VT_BYTES, row, w);
+      if (mine) store_row_swizzled(sP + (b0 + t) * VT_BYTES, row, w);
     }
-    }
-    fence_proxy_async();                                        // P rows -> visible to the MMA proxy
-    tc_fence_before();
-    __syncthreads();
-    stamp(5);
-    if (tid == 0) {
-      if (mbar_wait(bar_v, ph_v)) {
-        tc_fence_after();
-        for (int t = 0; t < nt; ++t) {
-          const uint32_t d_addr = tmem + ((uint32_t)((t & 1) * 16) << 16) + o_col;
-          const uint32_t first = (ch == 0 && t < 2) ? 0u : 1u;                       // first tile of each lane half
+  };
+
+  // tid 0: O += P V for the tiles of one chunk (after its V tiles have arrived), then the P tile stores
+  auto issue_pv = [&](int hb, int t0, int nt, bool first_chunk) -> bool {
+    const int b0 = 2 * hb;
+    if (!mbar_wait(hb ? bar_v1 : bar_v0, (ph_v >> hb) & 1)) { report(status, ERR_LOAD_WAIT); return false; }
+    tc_fence_after();
+    for (int t = 0; t < nt; ++t) {
+      const uint32_t d_addr = tmem + ((uint32_t)((t & 1) * 16) << 16) + o_col;
+      const uint32_t first = (first_chunk && t < 2) ? 0u : 1u;                       // first tile of each lane half
 #pragma unroll
-          for (int kk = 0; kk < BS / 16; ++kk)
-            mma_bf16(d_addr, ValTile::kmajor(sP + t * VT_BYTES, kk), T::mnmajor(sV + t * T::BYTES, kk), IDESC_O,
-                     (kk > 0) ? 1u : first);
+      for (int kk = 0; kk < BS / 16; ++kk)
+        mma_bf16(d_addr, ValTile::kmajor(sP + (b0 + t) * VT_BYTES, kk), T::mnmajor(sV + (b0 + t) * T::BYTES, kk), IDESC_O,
+                 (kk > 0) ? 1u : first);
+    }
+    if (STORE_P) {                                                // these tiles are final: store them now
+      for (int t = 0; t < nt; ++t)
+        tma_store_2d(&tmP, sP + (b0 + t) * VT_BYTES, 0, (int)(((size_t)bh * nnzb + rp + t0 + t) * BS));
+      bulk_commit();
+    }
+    return true;
+  };
+  float lse_fixed = 0.f;
+  uint32_t ph_a = 0;                                             // long rows: parity of bar_s (bit 0) and bar_o (bit 1)
+  auto finish_stats = [&]() {
+    m2 = fmaxf(m2, mraw * sc2);
+    m2 = fmaxf(m2, __shfl_xor_sync(0xffffffffu, m2, 16));        // both owners of a row agree
+    if (online) {
+      const float l = l_part + __shfl_xor_sync(0xffffffffu, l_part, 16) + (float)(L - n_sel) * exp2f(-m2);
+      lse_fixed = m2 + log2f(l);
+      m2 = lse_fixed;                                             // pass B then produces normalised P directly
+      l_part = 0.f;
+    }
+  };
+
+  if (single && nblk > 0) {
+    // ---------------------------------------------------------------- rows of at most 4 blocks
+    if (tid == 0) issue_s(0, 64u, 0u, bar_s);
+    if (!__syncthreads_and(mbar_wait(bar_s, 0))) { if (tid == 0) report(status, ERR_MMA_WAIT); ok = false; }
+    tc_fence_after();
+    stamp(3);
+    if (ok) {
+      stats_math(0u, 0, nblk, 2);
+      finish_stats();
+      stamp(4);
+      if (STORE_P) {
+        // keep both tiles' exponentials packed in registers, normalise once the denominator is known
+        uint32_t wp[2][32];
+#pragma unroll
+        for (int p = 0; p < 2; ++p) {
+          const int t = 2 * p + hf;
+          const bool mine = t < nblk;
+          const int c = mine ? col_of(t) : 0;
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            uint32_t v[32];
+            tmem_ld32(t_lane + p * 64 + half * 32, v);
+            tmem_ld_wait();
+            if (mine && quarter_ok(rp + t, half)) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 2) {
+                float h0 = m2, h1 = m2;
+                if (kp) { h0 = fmaf(kp[c * BS + half * 32 + j], LOG2E, m2); h1 = fmaf(kp[c * BS + half * 32 + j + 1], LOG2E, m2); }
+                const float e0 = ex2(fmaf(__uint_as_float(v[j]), sc2, -h0)), e1 = ex2(fmaf(__uint_as_float(v[j + 1]), sc2, -h1));
+                l_part += e0 + e1;
+                wp[p][half * 16 + (j >> 1)] = pack_bf16(e0, e1);
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) wp[p][half * 16 + j] = 0u;
+            }
+          }
         }
-        mma_commit(bar_o);
-        if (STORE_P) {                                            // these tiles are final: store them now
-          for (int t = 0; t < nt; ++t)
-            tma_store_2d(&tmP, sP + t * VT_BYTES, 0, (int)(((size_t)bh * nnzb + rp + t0 + t) * BS));
-          bulk_commit();
+        const float l = l_part + __shfl_xor_sync(0xffffffffu, l_part, 16) + (float)(L - n_sel) * exp2f(-m2);
+        // 1/l as a sum of two bf16 values: the packed product then carries one rounding of the result only
+        const float inv = 1.0f / l;
+        const float inv_h = bf16_hi(pack_bf16(0.f, inv));
+        const uint32_t inv_hi = pack_bf16(inv_h, inv_h), inv_lo = pack_bf16(inv - inv_h, inv - inv_h);
+        lse_fixed = m2 + log2f(l);
+#pragma unroll
+        for (int p = 0; p < 2; ++p) {
+          const int t = 2 * p + hf;
+          if (t < nblk) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) wp[p][j] = fma_bf16x2(wp[p][j], inv_hi, mul_bf16x2(wp[p][j], inv_lo));
+            store_row_swizzled(sP + t * VT_BYTES, row, wp[p]);
+          }
         }
       } else {
-        report(status, ERR_LOAD_WAIT);
+        prob_math(0u, 0, 0, nblk, 2);
       }
+      fence_proxy_async();                                        // P rows -> visible to the MMA proxy
+      tc_fence_before();
+      __syncthreads();
+      stamp(5);
+      if (tid == 0 && issue_pv(0, 0, nblk, true)) mma_commit(bar_o);
+      if (!__syncthreads_and(mbar_wait(bar_o, 0))) { if (tid == 0) report(status, ERR_MMA2_WAIT); ok = false; }
+      tc_fence_after();
+      stamp(6);
     }
-    ph_v ^= 1;
-    // the O MMAs read sP / sV, and the next chunk overwrites them and the S columns: wait here
-    if (!__syncthreads_and(mbar_wait(bar_o, ph_o))) { if (tid == 0) report(status, ERR_MMA2_WAIT); ok = false; break; }
-    ph_o ^= 1;
+  } else if (nblk > 0) {
+    // ---------------------------------------------------------------- longer rows: pairs of tiles, two passes
+    // Pass A (statistics): the pair of chunk c sits in columns 64 (c & 1); the MMAs of chunk c+1 are
+    // issued before the arithmetic on chunk c.  bar_s serves the even chunks, bar_o the odd ones.
+    const int n = nchunks;
+    if (tid == 0) issue_s(0, 0u, 0u, bar_s);
+    for (int c = 0; c < n && ok; ++c) {
+      const int b = c & 1;
+      if (tid == 0 && c + 1 < n) issue_s(c + 1, 0u, (uint32_t)(b ^ 1) * 64u, b ? bar_s : bar_o);
+      if (!__syncthreads_and(mbar_wait(b ? bar_o : bar_s, (ph_a >> b) & 1))) {
+        if (tid == 0) report(status, ERR_MMA_WAIT);
+        ok = false;
+        break;
+      }
+      ph_a ^= 1u << b;
+      tc_fence_after();
+      if (q == 0 && c + 2 < njobs) issue_job(c + 2);              // the S MMAs have consumed this half's K tiles
+      stats_math((uint32_t)b * 64u, 2 * c, min(2, nblk - 2 * c), 1);
+      tc_fence_before();
+      __syncthreads();                                            // chunk c+2 overwrites these columns
+    }
+    finish_stats();
+    stamp(4);
+    // Pass B: S of a chunk in columns [64,128), O accumulates in [0,64).  The tensor pipe completes in
+    // issue order: once S(c+1) has arrived, O += P V of chunk c is complete too, and its half of the
+    // buffers is requested again.
+    if (ok && tid == 0) issue_s(n, 0u, 64u, bar_s);
+    for (int c = 0; c < n && ok; ++c) {
+      const int g = n + c, hb = g & 1, t0 = 2 * c, nt = min(2, nblk - t0);
+      if (!__syncthreads_and(mbar_wait(bar_s, ph_a & 1))) { if (tid == 0) report(status, ERR_MMA_WAIT); ok = false; break; }
+      ph_a ^= 1u;
+      tc_fence_after();
+      if (c > 0 && q == 0 && g + 1 < njobs) {                     // chunk c-1 is finished: its half takes job g+1
+        if (STORE_P && lane == 0) bulk_wait_read_all();           // once the tile stores have read it
+        __syncwarp();
+        issue_job(g + 1);
+      }
+      prob_math(64u, 2 * hb, t0, nt, 1);
+      fence_proxy_async();
+      tc_fence_before();
+      __syncthreads();
+      if (tid == 0 && issue_pv(hb, t0, nt, c == 0)) {
+        if (c + 1 < n) issue_s(g + 1, 0u, 64u, bar_s);
+        else mma_commit(bar_o);
+      }
+      ph_v ^= 1u << hb;
+    }
+    if (ok && !__syncthreads_and(mbar_wait(bar_o, (ph_a >> 1) & 1))) { if (tid == 0) report(status, ERR_MMA2_WAIT); ok = false; }
     tc_fence_after();
-    if (online && tid == 0) bulk_wait_read_all();                 // before the next chunk's loads reuse the tiles
     stamp(6);
+  } else {
+    finish_stats();
   }
-
   // ------------------------------------------------------------------ epilogue
   if (ok) {
     float inv = 1.0f, lse2 = lse_fixed;
