@@ -40,7 +40,7 @@ enum { SPION_F32 = 0, SPION_BF16 = 1 };
 enum { SPION_CONV_DIAG = 0, SPION_CONV_BOX = 1 };
 enum { SPION_SELECT_PATHS = 0, SPION_SELECT_TOPK = 1 };
 enum { SPION_KIND_DENSE = 0, SPION_KIND_DENSE_KPM = 1, SPION_KIND_BLOCK = 2, SPION_KIND_BLOCK_KPM = 3 };
-enum { SPION_ENGINE_AUTO = 0, SPION_ENGINE_SIMT = 1, SPION_ENGINE_TCGEN05 = 2 };
+enum { SPION_ENGINE_AUTO = 0, SPION_ENGINE_SIMT = 1, SPION_ENGINE_TCGEN05 = 2, SPION_ENGINE_SIMT_STAGED = 3 };
 
 const char* spion_status_string(int status);
 int spion_version(void);
@@ -65,7 +65,10 @@ void spion_destroy(spion_ctx* ctx);
 int spion_set_stream(spion_ctx* ctx, void* cuda_stream);
 
 /* SPION_ENGINE_AUTO picks tcgen05 kernels where they exist (bf16, block 64/32, head_dim 64/32),
- * otherwise the SIMT kernels.  Forcing an engine that cannot run the shape gives UNSUPPORTED. */
+ * otherwise the SIMT kernels: for fp32 with block 32/64 and head_dim 32/64 the fused ones (one
+ * forward and two backward launches, no score scratch), else one kernel per stage of the
+ * reference's pipeline.  SPION_ENGINE_SIMT_STAGED forces the per-stage kernels.  Forcing an engine
+ * that cannot run the shape gives UNSUPPORTED. */
 int spion_set_engine(spion_ctx* ctx, int engine);
 
 /* Reads the context's device status word (synchronises the stream).  Non-zero means a

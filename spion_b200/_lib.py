@@ -16,7 +16,7 @@ F32, BF16 = 0, 1
 CONV_DIAG, CONV_BOX = 0, 1
 SELECT_PATHS, SELECT_TOPK = 0, 1
 KIND_DENSE, KIND_DENSE_KPM, KIND_BLOCK, KIND_BLOCK_KPM = 0, 1, 2, 3
-ENGINE_AUTO, ENGINE_SIMT, ENGINE_TCGEN05 = 0, 1, 2
+ENGINE_AUTO, ENGINE_SIMT, ENGINE_TCGEN05, ENGINE_SIMT_STAGED = 0, 1, 2, 3
 STAGE_COUNT = 17
 
 # name -> (restype, argtypes); every symbol include/spion_b200.h declares

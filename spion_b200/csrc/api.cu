@@ -110,7 +110,7 @@ extern "C" int spion_set_stream(spion_ctx* c, void* cuda_stream) {
 }
 
 extern "C" int spion_set_engine(spion_ctx* c, int engine) {
-  if (!c || engine < SPION_ENGINE_AUTO || engine > SPION_ENGINE_TCGEN05) return SPION_ERR_ARG;
+  if (!c || engine < SPION_ENGINE_AUTO || engine > SPION_ENGINE_SIMT_STAGED) return SPION_ERR_ARG;
   if (engine == SPION_ENGINE_TCGEN05 && !tc_engine_supports(c)) return SPION_ERR_UNSUPPORTED;
   c->engine = engine;
   return SPION_OK;
@@ -208,6 +208,12 @@ extern "C" const char* spion_stage_name(int stage) {
   return (stage >= 0 && stage < SPION_STAGE_COUNT) ? names[stage] : "?";
 }
 
+// fp32 contexts run the fused SIMT kernels unless the per-stage ones are forced
+static bool use_simt_fused(const spion_ctx* c, int value_mode) {
+  return c->dtype == SPION_F32 && c->engine != SPION_ENGINE_SIMT_STAGED &&
+         simt_fused_supports(c->bs, c->d, c->BH, value_mode);
+}
+
 // ============================================================ reference-layout sparse
 static int legacy_structure(spion_ctx* c, const int* offsets, const int* columns, const int* sum_mat, int nnz) {
   if (nnz < 0 || nnz % (c->bs * c->bs) != 0) return SPION_ERR_SHAPE;
@@ -236,10 +242,17 @@ extern "C" int spion_block_attn_forward(spion_ctx* c, const float* Q, const floa
   const Pattern p = ctx_pattern(c);
   const ValueLayout vl{VAL_ELEMCSR, c->L, (long long)nnz};
   const OperandLayout rm = row_major_operand(c->L, c->d), tr = transposed_operand(c->L, c->d);
+  // floor of the running maximum: -100 (models/block_attn.cu:48) or 0 (models/block_attn_mask.cu:105)
+  if (use_simt_fused(c, VAL_ELEMCSR)) {
+    rc = simt_fused_forward(Q, rm, Kt, tr, V, rm, is_kpm(c) ? keypad : nullptr, is_kpm(c) ? 0.0f : -100.0f, attn, vl, out,
+                            rm, p, c->BH, c->L, c->d, c->scale, c->stream);
+    if (!rc) prof_mark(c, SPION_STAGE_FUSED_FWD);
+    c->launches += 1;
+    return rc;
+  }
   rc = simt_sddmm(SPION_F32, SPION_F32, Q, rm, Kt, tr, attn, vl, p, c->nnzb, c->BH, c->d, c->stream);
   if (!rc) prof_mark(c, SPION_STAGE_SDDMM_S);
   if (rc) return rc;
-  // floor of the running maximum: -100 (models/block_attn.cu:48) or 0 (models/block_attn_mask.cu:105)
   rc = softmax_fwd_rows(SPION_F32, attn, vl, attn, vl, p, c->BH, c->L, c->scale, is_kpm(c) ? keypad : nullptr,
                         is_kpm(c) ? 0.0f : -100.0f, c->stream);
   if (!rc) prof_mark(c, SPION_STAGE_SOFTMAX_FWD);
@@ -264,6 +277,11 @@ extern "C" int spion_block_attn_backward(spion_ctx* c, const float* Q, const flo
   const Pattern p = ctx_pattern(c);
   const ValueLayout vl{VAL_ELEMCSR, c->L, (long long)nnz};
   const OperandLayout rm = row_major_operand(c->L, c->d), tr = transposed_operand(c->L, c->d);
+  if (use_simt_fused(c, VAL_ELEMCSR)) {
+    c->launches += 2;
+    return simt_fused_backward(Q, rm, K, rm, Vt, tr, P, vl, dO, rm, dS_scratch, vl, dQ, rm, dK, rm, dV, rm, p, c->BH, c->d,
+                               c->scale, c->stream, c);
+  }
   rc = simt_sddmm(SPION_F32, SPION_F32, dO, rm, Vt, tr, dP_scratch, vl, p, c->nnzb, c->BH, c->d, c->stream);
   if (!rc) prof_mark(c, SPION_STAGE_SDDMM_DP);
   if (rc) return rc;
@@ -357,7 +375,7 @@ extern "C" int spion_set_pattern(spion_ctx* c, const uint8_t* mat) {
 extern "C" int spion_pattern_nnzb(const spion_ctx* c) { return c ? c->nnzb : SPION_ERR_ARG; }
 
 static bool use_tc(const spion_ctx* c) {
-  if (c->engine == SPION_ENGINE_SIMT) return false;
+  if (c->engine == SPION_ENGINE_SIMT || c->engine == SPION_ENGINE_SIMT_STAGED) return false;
   return tc_engine_supports(c);
 }
 
@@ -367,12 +385,20 @@ extern "C" int spion_attn_forward_ex(spion_ctx* c, const void* Q, const void* K,
   if (is_dense(c) || c->nnzb < 0) return SPION_ERR_STATE;
   DeviceGuard guard(c->device);
   if (use_tc(c)) return tc_engine_forward(c, Q, K, V, keypad, P, O, S_scratch);
-  if (!S_scratch) return SPION_ERR_ARG;
   const Pattern p = ctx_pattern(c);
   const long long nnz = (long long)c->nnzb * c->bs * c->bs;
   const ValueLayout vl{VAL_BLOCKTILE, c->L, nnz};
   const OperandLayout rm = row_major_operand(c->L, c->d);
   prof_mark(c, -1);
+  if (use_simt_fused(c, VAL_BLOCKTILE)) {
+    int rc = simt_fused_forward((const float*)Q, rm, (const float*)K, rm, (const float*)V, rm, keypad,
+                                keypad ? 0.0f : -100.0f, (float*)P, vl, (float*)O, rm, p, c->BH, c->L, c->d, c->scale,
+                                c->stream);
+    if (!rc) prof_mark(c, SPION_STAGE_FUSED_FWD);
+    c->launches += 1;
+    return rc;
+  }
+  if (!S_scratch) return SPION_ERR_ARG;
   int rc = simt_sddmm(c->dtype, SPION_F32, Q, rm, K, rm, S_scratch, vl, p, c->nnzb, c->BH, c->d, c->stream);
   if (!rc) prof_mark(c, SPION_STAGE_SDDMM_S);
   if (rc) return rc;
@@ -397,12 +423,18 @@ extern "C" int spion_attn_backward_ex(spion_ctx* c, const void* Q, const void* K
     (void)delta;
     return tc_engine_backward(c, Q, K, V, P, O, dO, dS, dP_scratch, dQ, dK, dV);
   }
-  if (!dP_scratch) return SPION_ERR_ARG;
   const Pattern p = ctx_pattern(c);
   const long long nnz = (long long)c->nnzb * c->bs * c->bs;
   const ValueLayout vl{VAL_BLOCKTILE, c->L, nnz};
   const OperandLayout rm = row_major_operand(c->L, c->d);
   prof_mark(c, -1);
+  if (use_simt_fused(c, VAL_BLOCKTILE)) {
+    c->launches += 2;
+    return simt_fused_backward((const float*)Q, rm, (const float*)K, rm, (const float*)V, rm, (const float*)P, vl,
+                               (const float*)dO, rm, (float*)dS, vl, (float*)dQ, rm, (float*)dK, rm, (float*)dV, rm, p,
+                               c->BH, c->d, c->scale, c->stream, c);
+  }
+  if (!dP_scratch) return SPION_ERR_ARG;
   int rc = simt_sddmm(c->dtype, SPION_F32, dO, rm, V, rm, dP_scratch, vl, p, c->nnzb, c->BH, c->d, c->stream);
   if (!rc) prof_mark(c, SPION_STAGE_SDDMM_DP);
   if (rc) return rc;

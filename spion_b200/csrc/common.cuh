@@ -145,6 +145,17 @@ int softmax_bwd_rows(int dtype_p, const float* dP, ValueLayout vdp, const void* 
 int softmax_fwd_dense_t(float* S, int BH, int L, float scale, const float* keypad, float floor, cudaStream_t st);
 int softmax_bwd_dense_t(const float* dP, const float* P, float* dS, int BH, int L, float scale, cudaStream_t st);
 
+// simt_fused.cu: fused fp32 kernels (value layouts with contiguous tile rows)
+bool simt_fused_supports(int bs, int d, int BH, int value_mode);
+int simt_fused_forward(const float* Q, OperandLayout lq, const float* K, OperandLayout lk, const float* V,
+                       OperandLayout lv, const float* keypad, float floor_v, float* P, ValueLayout vl, float* O,
+                       OperandLayout lo, Pattern p, int BH, int L, int d, float scale, cudaStream_t st);
+int simt_fused_backward(const float* Q, OperandLayout lq, const float* K, OperandLayout lk, const float* V,
+                        OperandLayout lv, const float* P, ValueLayout vp, const float* dO, OperandLayout ldo,
+                        float* dS, ValueLayout vds, float* dQ, OperandLayout ldq, float* dK, OperandLayout ldk,
+                        float* dV, OperandLayout ldv, Pattern p, int BH, int d, float scale, cudaStream_t st,
+                        struct spion_ctx* prof);
+
 // tc_engine.cu: tcgen05 / TMA engine (bf16, block-tile layout)
 bool tc_engine_supports(const spion_ctx* c);
 int tc_engine_prepare(spion_ctx* c);       // after the pattern is set

@@ -114,16 +114,20 @@ def test_dense_matches_reference_softmax_attention_fixture():
 
 @pytest.mark.parametrize("B,H,L,d,bs,dens", SHAPES)
 @pytest.mark.parametrize("dtype", ["fp32", "bf16"])
-@pytest.mark.parametrize("engine", ["simt", "auto"])
+@pytest.mark.parametrize("engine", ["simt", "auto", "staged"])
 def test_native_block_tiles(B, H, L, d, bs, dens, dtype, engine):
+    """simt: fused fp32 kernels (bf16: one kernel per stage); staged: one kernel per stage; auto: tcgen05 for bf16."""
     from spion_b200 import _lib
     from spion_b200.native import BlockSparseAttention
+    if engine == "staged" and dtype == "bf16":
+        pytest.skip("same kernels as simt")
     tdt = torch.float32 if dtype == "fp32" else torch.bfloat16
     Q, K, V, dO = synthetic.qkv(11 + L + d, B, H, L, d)
     Q, K, V, dO = [t.to(tdt) for t in (Q, K, V, dO)]
     mat = synthetic.band_random_mask(L + bs + 1, L // bs, dens)
     mod = BlockSparseAttention(cfg(B, H, L, d, bs), dtype=tdt,
-                               engine=_lib.ENGINE_SIMT if engine == "simt" else _lib.ENGINE_AUTO)
+                               engine={"simt": _lib.ENGINE_SIMT, "auto": _lib.ENGINE_AUTO,
+                                       "staged": _lib.ENGINE_SIMT_STAGED}[engine])
     matf = torch.as_tensor(mat, dtype=torch.float32).cuda()
     out, P, dq, dk, dv = run_module(mod, Q, K, V, dO, None, matf)
     mod.check_device_status()
