@@ -42,6 +42,7 @@ WORKLOADS = {
     "sweep_L1024_bs64_d10": (8, 8, 1024, 64, 64, 0.10, "bf16"),
     "sweep_L16384_bs64_d02": (8, 8, 16384, 64, 64, 0.02, "bf16"),
     "config1_L1024_fp32": (8, 2, 1024, 32, 32, 0.15, "fp32"),
+    "image_L1024_fp32_B256": (256, 2, 1024, 32, 32, 0.15, "fp32"),   # attention layer of the image-shaped training step
     "tiny": (2, 2, 512, 64, 64, 0.25, "bf16"),
 }
 
@@ -338,7 +339,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="sweep_L4096_bs64_d05",
                     choices=sorted(WORKLOADS) + sorted(TRAIN_WORKLOADS) + ["pattern_L4096_bs64", "pattern_L1024_bs32"])
-    ap.add_argument("--engine", default="auto", choices=["auto", "simt", "tcgen05"])
+    ap.add_argument("--engine", default="auto", choices=["auto", "simt", "tcgen05", "staged"])
     ap.add_argument("--mode", default="auto", choices=["auto", "fused", "staged"],
                     help="fused: S/P/dP/dS stay on chip (tcgen05 engine); staged: one kernel per stage")
     ap.add_argument("--no-graph", action="store_true", help="training workloads: launch the step eagerly")
@@ -378,7 +379,8 @@ def main():
     BH, nb = B * H, L // bs
     cfg = {"head_dim": d, "num_head": H, "max_seq_len": L, "batch_size": B, "block_size": bs,
            "transformer_dim": H * d, "task": "sweep"}
-    engine = {"auto": _lib.ENGINE_AUTO, "simt": _lib.ENGINE_SIMT, "tcgen05": _lib.ENGINE_TCGEN05}[args.engine]
+    engine = {"auto": _lib.ENGINE_AUTO, "simt": _lib.ENGINE_SIMT, "tcgen05": _lib.ENGINE_TCGEN05,
+              "staged": _lib.ENGINE_SIMT_STAGED}[args.engine]
     mod = BlockSparseAttention(cfg, dtype=tdt, engine=engine, device=dev,
                                fused=None if args.mode == "auto" else (args.mode == "fused"))
     fused_fwd = mod.fused

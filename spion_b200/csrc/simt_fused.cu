@@ -59,26 +59,38 @@ __device__ __forceinline__ void load_vec(const float* row, int tx, int TX, float
   }
 }
 
-// Copy a [ROWS x COLS] tile (element (i, n) at src + i*s_row + n*s_col) into shared memory, row-major
-// with the given stride, by the NT threads of one problem.
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void cp_async16(float* dst, const float* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async4(float* dst, const float* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_addr(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// Start the asynchronous copy of a [ROWS x COLS] tile (element (i, n) at src + i*s_row + n*s_col) into
+// shared memory, row-major with the given stride, by the NT threads of one problem.  The caller
+// commits the group, waits for it and synchronises before the tile is read.
 template <int ROWS, int COLS, int NT>
 __device__ __forceinline__ void load_tile(float* dst, int stride, const float* __restrict__ src, long long s_row,
                                           long long s_col, int t) {
   if (s_col == 1 && (s_row & 3) == 0 && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+#pragma unroll
     for (int idx = t; idx < ROWS * COLS / 4; idx += NT) {
       const int row = idx / (COLS / 4), c4 = idx % (COLS / 4);
-      *reinterpret_cast<float4*>(dst + row * stride + c4 * 4) =
-          *reinterpret_cast<const float4*>(src + (long long)row * s_row + c4 * 4);
+      cp_async16(dst + row * stride + c4 * 4, src + (long long)row * s_row + c4 * 4);
     }
   } else if (s_col == 1) {
     for (int idx = t; idx < ROWS * COLS; idx += NT) {
       const int row = idx / COLS, col = idx % COLS;
-      dst[row * stride + col] = src[(long long)row * s_row + col];
+      cp_async4(dst + row * stride + col, src + (long long)row * s_row + col);
     }
   } else {
     for (int idx = t; idx < ROWS * COLS; idx += NT) {
       const int row = idx % ROWS, col = idx / ROWS;
-      dst[row * stride + col] = src[(long long)row * s_row + (long long)col * s_col];
+      cp_async4(dst + row * stride + col, src + (long long)row * s_row + (long long)col * s_col);
     }
   }
 }
@@ -184,14 +196,17 @@ __device__ __forceinline__ void store_out(float* __restrict__ out, OperandLayout
 
 // ------------------------------------------------------------------------------ forward
 //   v = S*scale - keypad[col];  m = max(floor, max v);  Z = sum exp(v-m) + (L-n_i) exp(-m);  P = exp(v-m)/Z
+// The K (pass 1) and V (pass 2) tiles are double-buffered: the copy of tile k+1 is in flight while
+// tile k is used.
 template <int BS, int D>
-__global__ void __launch_bounds__(256) fused_fwd_kernel(const float* __restrict__ Q, OperandLayout lq,
-                                                        const float* __restrict__ K, OperandLayout lk,
-                                                        const float* __restrict__ V, OperandLayout lv,
-                                                        const float* __restrict__ keypad, float floor_v, float* P,
-                                                        ValueLayout vl, float* __restrict__ O, OperandLayout lo,
-                                                        Pattern p, int BH, int L, float scale) {
+__global__ void __launch_bounds__(256, 3) fused_fwd_kernel(const float* __restrict__ Q, OperandLayout lq,
+                                                           const float* __restrict__ K, OperandLayout lk,
+                                                           const float* __restrict__ V, OperandLayout lv,
+                                                           const float* __restrict__ keypad, float floor_v, float* P,
+                                                           ValueLayout vl, float* __restrict__ O, OperandLayout lo,
+                                                           Pattern p, int BH, int L, float scale) {
   using C = Cfg<BS, D>;
+  constexpr int TILE = BS * C::SA;
   extern __shared__ __align__(16) float smem[];
   const int g = threadIdx.x / C::NT, t = threadIdx.x % C::NT;
   const int ty = t / C::TX, tx = t % C::TX;
@@ -199,36 +214,44 @@ __global__ void __launch_bounds__(256) fused_fwd_kernel(const float* __restrict_
   const int bh_raw = blockIdx.y * C::G + g;
   const bool active = bh_raw < BH;
   const int bh = active ? bh_raw : BH - 1;                       // idle problems shadow the last one, store nothing
-  float* Qs = smem + g * (2 * BS * C::SA + BS * C::SP);
-  float* Bs = Qs + BS * C::SA;                                  // K tile, then V tile
-  float* Ps = Bs + BS * C::SA;
+  float* Qs = smem + g * (3 * TILE + BS * C::SP);
+  float* Bs = Qs + TILE;                                        // two buffers: K tiles, then V tiles
+  float* Ps = Qs + 3 * TILE;
 
   const int rp = p.row_ptr[r], nblk = p.row_ptr[r + 1] - rp;
+  const int* cols = p.col_idx + rp;
   const float* Qb = Q + (long long)bh * lq.bh_stride + (long long)r * BS * lq.sl;
   const float* Kb = K + (long long)bh * lk.bh_stride;
   const float* Vb = V + (long long)bh * lv.bh_stride;
   float* Pb = P + (long long)bh * vl.bh_stride;
   const float* kp = keypad ? keypad + (long long)bh * L : nullptr;
 
+  int c_cur = nblk > 0 ? cols[0] : 0, c_nxt = nblk > 1 ? cols[1] : 0;
   load_tile<BS, D, C::NT>(Qs, C::SA, Qb, lq.sl, lq.sd, t);
+  if (nblk > 0) load_tile<BS, D, C::NT>(Bs, C::SA, Kb + (long long)c_cur * BS * lk.sl, lk.sl, lk.sd, t);
+  cp_async_commit();
 
   // ---- pass 1: scores into the P tiles, running maximum and denominator per row
   float m[4], l[4];
 #pragma unroll
   for (int x = 0; x < 4; ++x) { m[x] = floor_v; l[x] = 0.f; }
   for (int k = 0; k < nblk; ++k) {
-    const int blk = rp + k, c = p.col_idx[blk];
-    __syncthreads();
-    load_tile<BS, D, C::NT>(Bs, C::SA, Kb + (long long)c * BS * lk.sl, lk.sl, lk.sd, t);
-    __syncthreads();
+    const int c = c_cur;
+    if (k + 1 < nblk)
+      load_tile<BS, D, C::NT>(Bs + ((k + 1) & 1) * TILE, C::SA, Kb + (long long)c_nxt * BS * lk.sl, lk.sl, lk.sd, t);
+    cp_async_commit();
+    c_cur = c_nxt;
+    c_nxt = k + 2 < nblk ? cols[k + 2] : 0;
+    cp_async_wait<1>();
+    __syncthreads();                                             // tile k (and Q) have landed
     float acc[4][4];
 #pragma unroll
     for (int x = 0; x < 4; ++x)
 #pragma unroll
       for (int y = 0; y < 4; ++y) acc[x][y] = 0.f;
-    tile_abt<BS, D>(Qs, Bs, ty, tx, acc);
+    tile_abt<BS, D>(Qs, Bs + (k & 1) * TILE, ty, tx, acc);
     long long base, si, sj;
-    tile_address(vl, p, r, c, blk, base, si, sj);
+    tile_address(vl, p, r, c, rp + k, base, si, sj);
     float* tile = Pb + base;
 #pragma unroll
     for (int x = 0; x < 4; ++x) {
@@ -251,6 +274,7 @@ __global__ void __launch_bounds__(256) fused_fwd_kernel(const float* __restrict_
       l[x] = l[x] * __expf(m[x] - m_new) + s;
       m[x] = m_new;
     }
+    __syncthreads();                                             // buffer k&1 may be refilled
   }
   float inv[4];
 #pragma unroll
@@ -265,13 +289,20 @@ __global__ void __launch_bounds__(256) fused_fwd_kernel(const float* __restrict_
   for (int x = 0; x < 4; ++x)
 #pragma unroll
     for (int y = 0; y < C::TN; ++y) o[x][y] = 0.f;
+  c_cur = nblk > 0 ? cols[0] : 0;
+  c_nxt = nblk > 1 ? cols[1] : 0;
+  if (nblk > 0) load_tile<BS, D, C::NT>(Bs, C::SA, Vb + (long long)c_cur * BS * lv.sl, lv.sl, lv.sd, t);
+  cp_async_commit();
   for (int k = 0; k < nblk; ++k) {
-    const int blk = rp + k, c = p.col_idx[blk];
+    const int c = c_cur;
+    if (k + 1 < nblk)
+      load_tile<BS, D, C::NT>(Bs + ((k + 1) & 1) * TILE, C::SA, Vb + (long long)c_nxt * BS * lv.sl, lv.sl, lv.sd, t);
+    cp_async_commit();
+    c_cur = c_nxt;
+    c_nxt = k + 2 < nblk ? cols[k + 2] : 0;
     long long base, si, sj;
-    tile_address(vl, p, r, c, blk, base, si, sj);
+    tile_address(vl, p, r, c, rp + k, base, si, sj);
     float* tile = Pb + base;
-    __syncthreads();                                             // previous product has read Bs / Ps
-    load_tile<BS, D, C::NT>(Bs, C::SA, Vb + (long long)c * BS * lv.sl, lv.sl, lv.sd, t);
 #pragma unroll
     for (int x = 0; x < 4; ++x)
 #pragma unroll
@@ -282,22 +313,26 @@ __global__ void __launch_bounds__(256) fused_fwd_kernel(const float* __restrict_
         if (active) *e = pv;
         Ps[(ty * 4 + x) * C::SP + j] = pv;
       }
-    __syncthreads();
-    tile_ab<BS, D>(Ps, Bs, ty, tx, o);
+    cp_async_wait<1>();
+    __syncthreads();                                             // V tile k has landed, Ps is complete
+    tile_ab<BS, D>(Ps, Bs + (k & 1) * TILE, ty, tx, o);
+    __syncthreads();                                             // Ps and buffer k&1 may be overwritten
   }
+  cp_async_wait<0>();
   if (active) store_out<BS, D>(O + (long long)bh * lo.bh_stride, lo, r * BS, ty, tx, o);
 }
 
 // ------------------------------------------------------------------------------ backward, row side
 //   t = dP.P ; s = rowsum(t) ; dS = (t - P s) scale ; dQ = dS K     (models/block_attn.cu:90-130, :498-516)
 template <int BS, int D>
-__global__ void __launch_bounds__(256) fused_bwd_row_kernel(const float* __restrict__ dO, OperandLayout ldo,
-                                                            const float* __restrict__ V, OperandLayout lv,
-                                                            const float* __restrict__ K, OperandLayout lk,
-                                                            const float* __restrict__ P, ValueLayout vp, float* dS,
-                                                            ValueLayout vds, float* __restrict__ dQ,
-                                                            OperandLayout ldq, Pattern p, int BH, float scale) {
+__global__ void __launch_bounds__(256, 3) fused_bwd_row_kernel(const float* __restrict__ dO, OperandLayout ldo,
+                                                               const float* __restrict__ V, OperandLayout lv,
+                                                               const float* __restrict__ K, OperandLayout lk,
+                                                               const float* __restrict__ P, ValueLayout vp, float* dS,
+                                                               ValueLayout vds, float* __restrict__ dQ,
+                                                               OperandLayout ldq, Pattern p, int BH, float scale) {
   using C = Cfg<BS, D>;
+  constexpr int TILE = BS * C::SA;
   extern __shared__ __align__(16) float smem[];
   const int g = threadIdx.x / C::NT, t = threadIdx.x % C::NT;
   const int ty = t / C::TX, tx = t % C::TX;
@@ -305,42 +340,55 @@ __global__ void __launch_bounds__(256) fused_bwd_row_kernel(const float* __restr
   const int bh_raw = blockIdx.y * C::G + g;
   const bool active = bh_raw < BH;
   const int bh = active ? bh_raw : BH - 1;
-  float* As = smem + g * (2 * BS * C::SA + BS * C::SP);          // dO tile
-  float* Bs = As + BS * C::SA;                                  // V tile, then K tile
-  float* Ss = Bs + BS * C::SA;                                  // dS tile
+  float* As = smem + g * (3 * TILE + BS * C::SP);               // dO tile
+  float* Bs = As + TILE;                                        // two buffers: V tiles, then K tiles
+  float* Ss = As + 3 * TILE;                                    // dS tile
 
   const int rp = p.row_ptr[r], nblk = p.row_ptr[r + 1] - rp;
+  const int* cols = p.col_idx + rp;
   const float* Vb = V + (long long)bh * lv.bh_stride;
   const float* Kb = K + (long long)bh * lk.bh_stride;
   const float* Pb = P + (long long)bh * vp.bh_stride;
   float* dSb = dS + (long long)bh * vds.bh_stride;
 
+  int c_cur = nblk > 0 ? cols[0] : 0, c_nxt = nblk > 1 ? cols[1] : 0;
   load_tile<BS, D, C::NT>(As, C::SA, dO + (long long)bh * ldo.bh_stride + (long long)r * BS * ldo.sl, ldo.sl, ldo.sd, t);
+  if (nblk > 0) load_tile<BS, D, C::NT>(Bs, C::SA, Vb + (long long)c_cur * BS * lv.sl, lv.sl, lv.sd, t);
+  cp_async_commit();
 
   // ---- pass 1: dP into the dS tiles, row sums of dP.P
   float s[4] = {0.f, 0.f, 0.f, 0.f};
   for (int k = 0; k < nblk; ++k) {
-    const int blk = rp + k, c = p.col_idx[blk];
-    __syncthreads();
-    load_tile<BS, D, C::NT>(Bs, C::SA, Vb + (long long)c * BS * lv.sl, lv.sl, lv.sd, t);
+    const int c = c_cur;
+    if (k + 1 < nblk)
+      load_tile<BS, D, C::NT>(Bs + ((k + 1) & 1) * TILE, C::SA, Vb + (long long)c_nxt * BS * lv.sl, lv.sl, lv.sd, t);
+    cp_async_commit();
+    c_cur = c_nxt;
+    c_nxt = k + 2 < nblk ? cols[k + 2] : 0;
+    long long b1, s1, t1, b2, s2, t2;
+    tile_address(vp, p, r, c, rp + k, b1, s1, t1);
+    tile_address(vds, p, r, c, rp + k, b2, s2, t2);
+    float pv[4][4];                                              // requested before the wait: both latencies overlap
+#pragma unroll
+    for (int x = 0; x < 4; ++x)
+#pragma unroll
+      for (int y = 0; y < 4; ++y) pv[x][y] = Pb[b1 + (long long)(ty * 4 + x) * s1 + tx + y * C::TX];
+    cp_async_wait<1>();
     __syncthreads();
     float acc[4][4];
 #pragma unroll
     for (int x = 0; x < 4; ++x)
 #pragma unroll
       for (int y = 0; y < 4; ++y) acc[x][y] = 0.f;
-    tile_abt<BS, D>(As, Bs, ty, tx, acc);
-    long long b1, s1, t1, b2, s2, t2;
-    tile_address(vp, p, r, c, blk, b1, s1, t1);
-    tile_address(vds, p, r, c, blk, b2, s2, t2);
+    tile_abt<BS, D>(As, Bs + (k & 1) * TILE, ty, tx, acc);
 #pragma unroll
     for (int x = 0; x < 4; ++x)
 #pragma unroll
       for (int y = 0; y < 4; ++y) {
-        const int j = tx + y * C::TX;
-        s[x] = fmaf(acc[x][y], Pb[b1 + (long long)(ty * 4 + x) * s1 + j], s[x]);
-        if (active) dSb[b2 + (long long)(ty * 4 + x) * s2 + j] = acc[x][y];
+        s[x] = fmaf(acc[x][y], pv[x][y], s[x]);
+        if (active) dSb[b2 + (long long)(ty * 4 + x) * s2 + tx + y * C::TX] = acc[x][y];
       }
+    __syncthreads();
   }
 #pragma unroll
   for (int x = 0; x < 4; ++x) s[x] = group_sum<C::TX>(s[x]);
@@ -351,13 +399,20 @@ __global__ void __launch_bounds__(256) fused_bwd_row_kernel(const float* __restr
   for (int x = 0; x < 4; ++x)
 #pragma unroll
     for (int y = 0; y < C::TN; ++y) o[x][y] = 0.f;
+  c_cur = nblk > 0 ? cols[0] : 0;
+  c_nxt = nblk > 1 ? cols[1] : 0;
+  if (nblk > 0) load_tile<BS, D, C::NT>(Bs, C::SA, Kb + (long long)c_cur * BS * lk.sl, lk.sl, lk.sd, t);
+  cp_async_commit();
   for (int k = 0; k < nblk; ++k) {
-    const int blk = rp + k, c = p.col_idx[blk];
+    const int c = c_cur;
+    if (k + 1 < nblk)
+      load_tile<BS, D, C::NT>(Bs + ((k + 1) & 1) * TILE, C::SA, Kb + (long long)c_nxt * BS * lk.sl, lk.sl, lk.sd, t);
+    cp_async_commit();
+    c_cur = c_nxt;
+    c_nxt = k + 2 < nblk ? cols[k + 2] : 0;
     long long b1, s1, t1, b2, s2, t2;
-    tile_address(vp, p, r, c, blk, b1, s1, t1);
-    tile_address(vds, p, r, c, blk, b2, s2, t2);
-    __syncthreads();
-    load_tile<BS, D, C::NT>(Bs, C::SA, Kb + (long long)c * BS * lk.sl, lk.sl, lk.sd, t);
+    tile_address(vp, p, r, c, rp + k, b1, s1, t1);
+    tile_address(vds, p, r, c, rp + k, b2, s2, t2);
 #pragma unroll
     for (int x = 0; x < 4; ++x)
 #pragma unroll
@@ -369,22 +424,27 @@ __global__ void __launch_bounds__(256) fused_bwd_row_kernel(const float* __restr
         if (active) *e = ds;
         Ss[(ty * 4 + x) * C::SP + j] = ds;
       }
+    cp_async_wait<1>();
     __syncthreads();
-    tile_ab<BS, D>(Ss, Bs, ty, tx, o);
+    tile_ab<BS, D>(Ss, Bs + (k & 1) * TILE, ty, tx, o);
+    __syncthreads();
   }
+  cp_async_wait<0>();
   if (active) store_out<BS, D>(dQ + (long long)bh * ldq.bh_stride, ldq, r * BS, ty, tx, o);
 }
 
 // ------------------------------------------------------------------------------ backward, column side
 //   dK[c] = sum_r dS(r,c)^T Q[r],  dV[c] = sum_r P(r,c)^T dO[r]     (models/block_attn.cu:526-536)
+// Two stages per entry of the column: (dS, Q) for dK and (P, dO) for dV; the copy of one stage is in
+// flight while the other is used.
 template <int BS, int D>
-__global__ void __launch_bounds__(256) fused_bwd_col_kernel(const float* __restrict__ dS, ValueLayout vds,
-                                                            const float* __restrict__ P, ValueLayout vp,
-                                                            const float* __restrict__ Q, OperandLayout lq,
-                                                            const float* __restrict__ dO, OperandLayout ldo,
-                                                            float* __restrict__ dK, OperandLayout ldk,
-                                                            float* __restrict__ dV, OperandLayout ldv, Pattern p,
-                                                            int BH) {
+__global__ void __launch_bounds__(256, 3) fused_bwd_col_kernel(const float* __restrict__ dS, ValueLayout vds,
+                                                               const float* __restrict__ P, ValueLayout vp,
+                                                               const float* __restrict__ Q, OperandLayout lq,
+                                                               const float* __restrict__ dO, OperandLayout ldo,
+                                                               float* __restrict__ dK, OperandLayout ldk,
+                                                               float* __restrict__ dV, OperandLayout ldv, Pattern p,
+                                                               int BH) {
   using C = Cfg<BS, D>;
   extern __shared__ __align__(16) float smem[];
   const int g = threadIdx.x / C::NT, t = threadIdx.x % C::NT;
@@ -394,9 +454,9 @@ __global__ void __launch_bounds__(256) fused_bwd_col_kernel(const float* __restr
   const bool active = bh_raw < BH;
   const int bh = active ? bh_raw : BH - 1;
   float* dSs = smem + g * (2 * BS * C::SA + 2 * BS * C::SP);
-  float* Ps = dSs + BS * C::SP;
-  float* Qs = Ps + BS * C::SP;
-  float* Os = Qs + BS * C::SA;
+  float* Qs = dSs + BS * C::SP;
+  float* Ps = Qs + BS * C::SA;
+  float* Os = Ps + BS * C::SP;
 
   const float* dSb = dS + (long long)bh * vds.bh_stride;
   const float* Pb = P + (long long)bh * vp.bh_stride;
@@ -409,27 +469,47 @@ __global__ void __launch_bounds__(256) fused_bwd_col_kernel(const float* __restr
 #pragma unroll
     for (int y = 0; y < C::TN; ++y) { ak[x][y] = 0.f; av[x][y] = 0.f; }
 
-  for (int e = p.col_ptr[c]; e < p.col_ptr[c + 1]; ++e) {
-    const int r = p.row_idx[e], blk = p.csc_pos[e];
-    long long b1, s1, t1, b2, s2, t2;
+  const int e0 = p.col_ptr[c], e1 = p.col_ptr[c + 1];
+  auto fetch_k = [&](int r, int blk) {                          // stage A: dS tile and Q rows of entry (r, blk)
+    long long b1, s1, t1;
     tile_address(vds, p, r, c, blk, b1, s1, t1);
-    tile_address(vp, p, r, c, blk, b2, s2, t2);
-    __syncthreads();
     load_tile<BS, BS, C::NT>(dSs, C::SP, dSb + b1, s1, t1, t);
-    load_tile<BS, BS, C::NT>(Ps, C::SP, Pb + b2, s2, t2, t);
     load_tile<BS, D, C::NT>(Qs, C::SA, Qb + (long long)r * BS * lq.sl, lq.sl, lq.sd, t);
+  };
+  auto fetch_v = [&](int r, int blk) {                          // stage B: P tile and dO rows
+    long long b2, s2, t2;
+    tile_address(vp, p, r, c, blk, b2, s2, t2);
+    load_tile<BS, BS, C::NT>(Ps, C::SP, Pb + b2, s2, t2, t);
     load_tile<BS, D, C::NT>(Os, C::SA, dOb + (long long)r * BS * ldo.sl, ldo.sl, ldo.sd, t);
-    __syncthreads();
+  };
+  int r_cur = e0 < e1 ? p.row_idx[e0] : 0, b_cur = e0 < e1 ? p.csc_pos[e0] : 0;
+  if (e0 < e1) fetch_k(r_cur, b_cur);
+  cp_async_commit();
+  for (int e = e0; e < e1; ++e) {
+    const int r_nxt = e + 1 < e1 ? p.row_idx[e + 1] : 0, b_nxt = e + 1 < e1 ? p.csc_pos[e + 1] : 0;
+    fetch_v(r_cur, b_cur);                                       // stage B was released at the end of the last iteration
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();                                             // stage A has landed
     tile_atb<BS, D>(dSs, Qs, ty, tx, ak);
+    __syncthreads();                                             // stage A may be refilled
+    if (e + 1 < e1) fetch_k(r_nxt, b_nxt);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();                                             // stage B has landed
     tile_atb<BS, D>(Ps, Os, ty, tx, av);
+    __syncthreads();
+    r_cur = r_nxt;
+    b_cur = b_nxt;
   }
+  cp_async_wait<0>();
   if (active) {
     store_out<BS, D>(dK + (long long)bh * ldk.bh_stride, ldk, c * BS, ty, tx, ak);
     store_out<BS, D>(dV + (long long)bh * ldv.bh_stride, ldv, c * BS, ty, tx, av);
   }
 }
 
-template <int BS, int D> constexpr size_t smem_row() { return sizeof(float) * Cfg<BS, D>::G * (2 * BS * Cfg<BS, D>::SA + BS * Cfg<BS, D>::SP); }
+template <int BS, int D> constexpr size_t smem_row() { return sizeof(float) * Cfg<BS, D>::G * (3 * BS * Cfg<BS, D>::SA + BS * Cfg<BS, D>::SP); }
 template <int BS, int D> constexpr size_t smem_col() { return sizeof(float) * Cfg<BS, D>::G * (2 * BS * Cfg<BS, D>::SA + 2 * BS * Cfg<BS, D>::SP); }
 
 template <int BS, int D>
