@@ -230,6 +230,11 @@ int spion_attn_backward_ex(spion_ctx* ctx, const void* Q, const void* K, const v
                            void* dS, float* dP_scratch, float* delta,
                            void* dQ, void* dK, void* dV);
 
+/* 1 when spion_attn_forward_ex / spion_attn_backward_ex of this context need their fp32 scratch
+ * arguments (the per-stage SIMT kernels run), 0 when they may be NULL.  No reference counterpart
+ * (the reference allocates its backward scratch on every call, models/attention_blockcuda.py:84-85). */
+int spion_needs_scratch(const spion_ctx* ctx);
+
 /* Fused native forward (tcgen05 engine only; UNSUPPORTED otherwise).  S never reaches HBM: one
  * kernel computes the scores of a block row in tensor memory, the sparse row softmax in registers and
  * O = P V from shared memory.  It writes O and one fp32 log-sum-exp value per row (lse [BH*L], log2

@@ -27,6 +27,7 @@ SIGNATURES = {
     "spion_destroy": (None, [c_void_p]),
     "spion_set_stream": (c_int, [c_void_p, c_void_p]),
     "spion_set_engine": (c_int, [c_void_p, c_int]),
+    "spion_needs_scratch": (c_int, [c_void_p]),
     "spion_check_device_status": (c_int, [c_void_p]),
     "spion_set_trace_buffer": (c_int, [c_void_p, c_void_p]),
     "spion_selftest_bounded_wait": (c_int, [c_void_p, c_longlong]),

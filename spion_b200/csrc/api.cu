@@ -279,7 +279,7 @@ extern "C" int spion_block_attn_backward(spion_ctx* c, const float* Q, const flo
   const OperandLayout rm = row_major_operand(c->L, c->d), tr = transposed_operand(c->L, c->d);
   if (use_simt_fused(c, VAL_ELEMCSR)) {
     c->launches += 2;
-    return simt_fused_backward(Q, rm, K, rm, Vt, tr, P, vl, dO, rm, dS_scratch, vl, dQ, rm, dK, rm, dV, rm, p, c->BH, c->d,
+    return simt_fused_backward(Q, rm, K, rm, Vt, tr, P, vl, nullptr, rm, dO, rm, dS_scratch, vl, dQ, rm, dK, rm, dV, rm, p, c->BH, c->d,
                                c->scale, c->stream, c);
   }
   rc = simt_sddmm(SPION_F32, SPION_F32, dO, rm, Vt, tr, dP_scratch, vl, p, c->nnzb, c->BH, c->d, c->stream);
@@ -431,7 +431,7 @@ extern "C" int spion_attn_backward_ex(spion_ctx* c, const void* Q, const void* K
   if (use_simt_fused(c, VAL_BLOCKTILE)) {
     c->launches += 2;
     return simt_fused_backward((const float*)Q, rm, (const float*)K, rm, (const float*)V, rm, (const float*)P, vl,
-                               (const float*)dO, rm, (float*)dS, vl, (float*)dQ, rm, (float*)dK, rm, (float*)dV, rm, p,
+                               (const float*)O, rm, (const float*)dO, rm, (float*)dS, vl, (float*)dQ, rm, (float*)dK, rm, (float*)dV, rm, p,
                                c->BH, c->d, c->scale, c->stream, c);
   }
   if (!dP_scratch) return SPION_ERR_ARG;
@@ -451,6 +451,11 @@ extern "C" int spion_attn_backward_ex(spion_ctx* c, const void* Q, const void* K
   if (!rc) prof_mark(c, SPION_STAGE_SPMM_DV);
   c->launches += 5;
   return rc;
+}
+
+extern "C" int spion_needs_scratch(const spion_ctx* c) {
+  if (!c || is_dense(c)) return 0;
+  return (use_tc(c) || use_simt_fused(c, VAL_BLOCKTILE)) ? 0 : 1;
 }
 
 extern "C" int spion_supports_fused(const spion_ctx* c) {

@@ -151,10 +151,10 @@ int simt_fused_forward(const float* Q, OperandLayout lq, const float* K, Operand
                        OperandLayout lv, const float* keypad, float floor_v, float* P, ValueLayout vl, float* O,
                        OperandLayout lo, Pattern p, int BH, int L, int d, float scale, cudaStream_t st);
 int simt_fused_backward(const float* Q, OperandLayout lq, const float* K, OperandLayout lk, const float* V,
-                        OperandLayout lv, const float* P, ValueLayout vp, const float* dO, OperandLayout ldo,
-                        float* dS, ValueLayout vds, float* dQ, OperandLayout ldq, float* dK, OperandLayout ldk,
-                        float* dV, OperandLayout ldv, Pattern p, int BH, int d, float scale, cudaStream_t st,
-                        struct spion_ctx* prof);
+                        OperandLayout lv, const float* P, ValueLayout vp, const float* O_or_null, OperandLayout lo,
+                        const float* dO, OperandLayout ldo, float* dS, ValueLayout vds, float* dQ, OperandLayout ldq,
+                        float* dK, OperandLayout ldk, float* dV, OperandLayout ldv, Pattern p, int BH, int d,
+                        float scale, cudaStream_t st, struct spion_ctx* prof);
 
 // tc_engine.cu: tcgen05 / TMA engine (bf16, block-tile layout)
 bool tc_engine_supports(const spion_ctx* c);

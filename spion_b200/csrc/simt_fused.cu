@@ -293,13 +293,21 @@ __global__ void __launch_bounds__(256, 3) fused_fwd_kernel(const float* __restri
   c_nxt = nblk > 1 ? cols[1] : 0;
   if (nblk > 0) load_tile<BS, D, C::NT>(Bs, C::SA, Vb + (long long)c_cur * BS * lv.sl, lv.sl, lv.sd, t);
   cp_async_commit();
+  float sc[4][4];                                                // scores of the tile about to be used
+  auto fetch_scores = [&](int k, int c) {
+    long long base, si, sj;
+    tile_address(vl, p, r, c, rp + k, base, si, sj);
+#pragma unroll
+    for (int x = 0; x < 4; ++x)
+#pragma unroll
+      for (int y = 0; y < 4; ++y) sc[x][y] = Pb[base + (long long)(ty * 4 + x) * si + tx + y * C::TX];
+  };
+  if (nblk > 0) fetch_scores(0, c_cur);
   for (int k = 0; k < nblk; ++k) {
     const int c = c_cur;
     if (k + 1 < nblk)
       load_tile<BS, D, C::NT>(Bs + ((k + 1) & 1) * TILE, C::SA, Vb + (long long)c_nxt * BS * lv.sl, lv.sl, lv.sd, t);
     cp_async_commit();
-    c_cur = c_nxt;
-    c_nxt = k + 2 < nblk ? cols[k + 2] : 0;
     long long base, si, sj;
     tile_address(vl, p, r, c, rp + k, base, si, sj);
     float* tile = Pb + base;
@@ -308,11 +316,13 @@ __global__ void __launch_bounds__(256, 3) fused_fwd_kernel(const float* __restri
 #pragma unroll
       for (int y = 0; y < 4; ++y) {
         const int j = tx + y * C::TX;
-        float* e = tile + (long long)(ty * 4 + x) * si + j;
-        const float pv = (inv[x] == 0.f) ? 0.f : __expf(*e - m[x]) * inv[x];
-        if (active) *e = pv;
+        const float pv = (inv[x] == 0.f) ? 0.f : __expf(sc[x][y] - m[x]) * inv[x];
+        if (active) tile[(long long)(ty * 4 + x) * si + j] = pv;
         Ps[(ty * 4 + x) * C::SP + j] = pv;
       }
+    if (k + 1 < nblk) fetch_scores(k + 1, c_nxt);                // in flight during the product below
+    c_cur = c_nxt;
+    c_nxt = k + 2 < nblk ? cols[k + 2] : 0;
     cp_async_wait<1>();
     __syncthreads();                                             // V tile k has landed, Ps is complete
     tile_ab<BS, D>(Ps, Bs + (k & 1) * TILE, ty, tx, o);
@@ -433,6 +443,109 @@ __global__ void __launch_bounds__(256, 3) fused_bwd_row_kernel(const float* __re
   if (active) store_out<BS, D>(dQ + (long long)bh * ldq.bh_stride, ldq, r * BS, ty, tx, o);
 }
 
+// Row backward when O is at hand: rowsum(dP.P) = rowsum(dO.O) (delta), so dS of a tile needs nothing
+// from the other tiles of its row and one pass suffices.  Two stages per block, V tile (for dP) and
+// K tile (for dQ); the copy of one is in flight while the other is used.
+template <int BS, int D>
+__global__ void __launch_bounds__(256, 3) fused_bwd_row_delta_kernel(const float* __restrict__ dO, OperandLayout ldo,
+                                                                     const float* __restrict__ O, OperandLayout lo,
+                                                                     const float* __restrict__ V, OperandLayout lv,
+                                                                     const float* __restrict__ K, OperandLayout lk,
+                                                                     const float* __restrict__ P, ValueLayout vp,
+                                                                     float* __restrict__ dS, ValueLayout vds,
+                                                                     float* __restrict__ dQ, OperandLayout ldq,
+                                                                     Pattern p, int BH, float scale) {
+  using C = Cfg<BS, D>;
+  constexpr int TILE = BS * C::SA;
+  extern __shared__ __align__(16) float smem[];
+  const int g = threadIdx.x / C::NT, t = threadIdx.x % C::NT;
+  const int ty = t / C::TX, tx = t % C::TX;
+  const int r = blockIdx.x;
+  const int bh_raw = blockIdx.y * C::G + g;
+  const bool active = bh_raw < BH;
+  const int bh = active ? bh_raw : BH - 1;
+  float* As = smem + g * (3 * TILE + BS * C::SP);               // dO tile
+  float* Vs = As + TILE;
+  float* Ks = As + 2 * TILE;
+  float* Ss = As + 3 * TILE;                                    // dS tile
+
+  const int rp = p.row_ptr[r], nblk = p.row_ptr[r + 1] - rp;
+  const int* cols = p.col_idx + rp;
+  const float* Vb = V + (long long)bh * lv.bh_stride;
+  const float* Kb = K + (long long)bh * lk.bh_stride;
+  const float* Pb = P + (long long)bh * vp.bh_stride;
+  float* dSb = dS + (long long)bh * vds.bh_stride;
+
+  int c_cur = nblk > 0 ? cols[0] : 0, c_nxt = nblk > 1 ? cols[1] : 0;
+  load_tile<BS, D, C::NT>(As, C::SA, dO + (long long)bh * ldo.bh_stride + (long long)r * BS * ldo.sl, ldo.sl, ldo.sd, t);
+  if (nblk > 0) load_tile<BS, D, C::NT>(Vs, C::SA, Vb + (long long)c_cur * BS * lv.sl, lv.sl, lv.sd, t);
+  cp_async_commit();
+  if (nblk > 0) load_tile<BS, D, C::NT>(Ks, C::SA, Kb + (long long)c_cur * BS * lk.sl, lk.sl, lk.sd, t);
+  cp_async_commit();
+
+  float delta[4] = {0.f, 0.f, 0.f, 0.f};
+  float o[4][C::TN];
+#pragma unroll
+  for (int x = 0; x < 4; ++x)
+#pragma unroll
+    for (int y = 0; y < C::TN; ++y) o[x][y] = 0.f;
+
+  for (int k = 0; k < nblk; ++k) {
+    const int c = c_cur;
+    long long b1, s1, t1, b2, s2, t2;
+    tile_address(vp, p, r, c, rp + k, b1, s1, t1);
+    tile_address(vds, p, r, c, rp + k, b2, s2, t2);
+    float pv[4][4];                                              // requested before the wait: the latencies overlap
+#pragma unroll
+    for (int x = 0; x < 4; ++x)
+#pragma unroll
+      for (int y = 0; y < 4; ++y) pv[x][y] = Pb[b1 + (long long)(ty * 4 + x) * s1 + tx + y * C::TX];
+    cp_async_wait<1>();
+    __syncthreads();                                             // V tile k (and dO) have landed
+    if (k == 0) {
+      const float* Ob = O + (long long)bh * lo.bh_stride + (long long)(r * BS + ty * 4) * lo.sl;
+#pragma unroll
+      for (int x = 0; x < 4; ++x) {
+        float a = 0.f;
+#pragma unroll
+        for (int y = 0; y < C::TN; ++y) {
+          const int n = out_col<BS, D>(tx, y);
+          a = fmaf(As[(ty * 4 + x) * C::SA + n], Ob[(long long)x * lo.sl + (long long)n * lo.sd], a);
+        }
+        delta[x] = group_sum<C::TX>(a);
+      }
+    }
+    float acc[4][4];
+#pragma unroll
+    for (int x = 0; x < 4; ++x)
+#pragma unroll
+      for (int y = 0; y < 4; ++y) acc[x][y] = 0.f;
+    tile_abt<BS, D>(As, Vs, ty, tx, acc);
+#pragma unroll
+    for (int x = 0; x < 4; ++x)
+#pragma unroll
+      for (int y = 0; y < 4; ++y) {
+        const int j = tx + y * C::TX;
+        const float ds = pv[x][y] * (acc[x][y] - delta[x]) * scale;
+        if (active) dSb[b2 + (long long)(ty * 4 + x) * s2 + j] = ds;
+        Ss[(ty * 4 + x) * C::SP + j] = ds;
+      }
+    __syncthreads();                                             // Ss complete, V buffer free
+    if (k + 1 < nblk) load_tile<BS, D, C::NT>(Vs, C::SA, Vb + (long long)c_nxt * BS * lv.sl, lv.sl, lv.sd, t);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();                                             // K tile k has landed
+    tile_ab<BS, D>(Ss, Ks, ty, tx, o);
+    __syncthreads();                                             // Ss and the K buffer are free
+    if (k + 1 < nblk) load_tile<BS, D, C::NT>(Ks, C::SA, Kb + (long long)c_nxt * BS * lk.sl, lk.sl, lk.sd, t);
+    cp_async_commit();
+    c_cur = c_nxt;
+    c_nxt = k + 2 < nblk ? cols[k + 2] : 0;
+  }
+  cp_async_wait<0>();
+  if (active) store_out<BS, D>(dQ + (long long)bh * ldq.bh_stride, ldq, r * BS, ty, tx, o);
+}
+
 // ------------------------------------------------------------------------------ backward, column side
 //   dK[c] = sum_r dS(r,c)^T Q[r],  dV[c] = sum_r P(r,c)^T dO[r]     (models/block_attn.cu:526-536)
 // Two stages per entry of the column: (dS, Q) for dK and (P, dO) for dV; the copy of one stage is in
@@ -520,6 +633,7 @@ int set_attrs() {
   if (dev < 64 && done[dev]) return SPION_OK;
   SPION_CUDA_TRY(cudaFuncSetAttribute(fused_fwd_kernel<BS, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_row<BS, D>()));
   SPION_CUDA_TRY(cudaFuncSetAttribute(fused_bwd_row_kernel<BS, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_row<BS, D>()));
+  SPION_CUDA_TRY(cudaFuncSetAttribute(fused_bwd_row_delta_kernel<BS, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_row<BS, D>()));
   SPION_CUDA_TRY(cudaFuncSetAttribute(fused_bwd_col_kernel<BS, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_col<BS, D>()));
   if (dev < 64) done[dev] = true;
   return SPION_OK;
@@ -540,14 +654,18 @@ int fwd_launch(const float* Q, OperandLayout lq, const float* K, OperandLayout l
 
 template <int BS, int D>
 int bwd_launch(const float* Q, OperandLayout lq, const float* K, OperandLayout lk, const float* V, OperandLayout lv,
-               const float* P, ValueLayout vp, const float* dO, OperandLayout ldo, float* dS, ValueLayout vds,
-               float* dQ, OperandLayout ldq, float* dK, OperandLayout ldk, float* dV, OperandLayout ldv, Pattern p,
-               int BH, float scale, cudaStream_t st, spion_ctx* prof) {
+               const float* P, ValueLayout vp, const float* O, OperandLayout lo, const float* dO, OperandLayout ldo,
+               float* dS, ValueLayout vds, float* dQ, OperandLayout ldq, float* dK, OperandLayout ldk, float* dV,
+               OperandLayout ldv, Pattern p, int BH, float scale, cudaStream_t st, spion_ctx* prof) {
   int rc = set_attrs<BS, D>();
   if (rc) return rc;
   const dim3 grid(p.nb, (BH + Cfg<BS, D>::G - 1) / Cfg<BS, D>::G);
-  fused_bwd_row_kernel<BS, D><<<grid, 256, smem_row<BS, D>(), st>>>(dO, ldo, V, lv, K, lk, P, vp, dS, vds, dQ, ldq, p,
-                                                                   BH, scale);
+  if (O)
+    fused_bwd_row_delta_kernel<BS, D><<<grid, 256, smem_row<BS, D>(), st>>>(dO, ldo, O, lo, V, lv, K, lk, P, vp, dS, vds,
+                                                                           dQ, ldq, p, BH, scale);
+  else
+    fused_bwd_row_kernel<BS, D><<<grid, 256, smem_row<BS, D>(), st>>>(dO, ldo, V, lv, K, lk, P, vp, dS, vds, dQ, ldq, p,
+                                                                     BH, scale);
   SPION_LAUNCH_CHECK();
   if (prof) prof_mark(prof, SPION_STAGE_BWD_ROW);
   fused_bwd_col_kernel<BS, D><<<grid, 256, smem_col<BS, D>(), st>>>(dS, vds, P, vp, Q, lq, dO, ldo, dK, ldk, dV, ldv, p,
@@ -581,11 +699,11 @@ int simt_fused_forward(const float* Q, OperandLayout lq, const float* K, Operand
 }
 
 int simt_fused_backward(const float* Q, OperandLayout lq, const float* K, OperandLayout lk, const float* V,
-                        OperandLayout lv, const float* P, ValueLayout vp, const float* dO, OperandLayout ldo,
-                        float* dS, ValueLayout vds, float* dQ, OperandLayout ldq, float* dK, OperandLayout ldk,
-                        float* dV, OperandLayout ldv, Pattern p, int BH, int d, float scale, cudaStream_t st,
-                        spion_ctx* prof) {
+                        OperandLayout lv, const float* P, ValueLayout vp, const float* O, OperandLayout lo,
+                        const float* dO, OperandLayout ldo, float* dS, ValueLayout vds, float* dQ, OperandLayout ldq,
+                        float* dK, OperandLayout ldk, float* dV, OperandLayout ldv, Pattern p, int BH, int d,
+                        float scale, cudaStream_t st, spion_ctx* prof) {
   if (!simt_fused_supports(p.bs, d, BH, vp.mode) || vds.mode != vp.mode) return SPION_ERR_UNSUPPORTED;
-  SPION_FUSED_DISPATCH(bwd_launch, Q, lq, K, lk, V, lv, P, vp, dO, ldo, dS, vds, dQ, ldq, dK, ldk, dV, ldv, p, BH, scale,
-                       st, prof);
+  SPION_FUSED_DISPATCH(bwd_launch, Q, lq, K, lk, V, lv, P, vp, O, lo, dO, ldo, dS, vds, dQ, ldq, dK, ldk, dV, ldv, p, BH,
+                       scale, st, prof);
 }

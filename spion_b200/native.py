@@ -42,6 +42,7 @@ class BlockSparseAttention(nn.Module):
         self.handle = _lib.c_void_p(h)
         check(lib.spion_set_engine(self.handle, engine), "spion_set_engine")
         self.engine = engine
+        self.needs_scratch = bool(lib.spion_needs_scratch(self.handle))
         # fused kernels (S, P, dP, dS stay on chip) where the tensor-core engine covers the shape
         can_fuse = bool(lib.spion_supports_fused(self.handle))
         if fused and not can_fuse:
@@ -179,7 +180,7 @@ def _make_function(mod: BlockSparseAttention):
             n = mod.BH * mod.nnz
             P = torch.empty(n, dtype=mod.dtype, device=dev)
             O = torch.empty_like(q)
-            scratch = torch.empty(n, dtype=torch.float32, device=dev) if mod.engine != _lib.ENGINE_TCGEN05 else None
+            scratch = torch.empty(n, dtype=torch.float32, device=dev) if mod.needs_scratch else None
             check(lib.spion_set_stream(mod.handle, _lib.current_stream_ptr()))
             check(lib.spion_attn_forward_ex(mod.handle, ptr(q), ptr(k), ptr(v), ptr(pen), ptr(P), ptr(O), ptr(scratch)),
                   "spion_attn_forward_ex")
@@ -194,7 +195,7 @@ def _make_function(mod: BlockSparseAttention):
             go = grad_output.to(mod.dtype).contiguous()
             n = mod.BH * mod.nnz
             dS = torch.empty(n, dtype=mod.dtype, device=dev)
-            scratch = torch.empty(n, dtype=torch.float32, device=dev) if mod.engine != _lib.ENGINE_TCGEN05 else None
+            scratch = torch.empty(n, dtype=torch.float32, device=dev) if mod.needs_scratch else None
             delta = torch.empty(mod.BH * mod.L, dtype=torch.float32, device=dev)
             dq, dk, dv = torch.empty_like(q), torch.empty_like(q), torch.empty_like(q)
             check(lib.spion_set_stream(mod.handle, _lib.current_stream_ptr()))
