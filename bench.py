@@ -58,9 +58,17 @@ TRAIN_WORKLOADS = {
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch, from the ncu capture summarised in
-# profiles/tcgen05_fused_pipeline_sweep_L4096_bs64_d05.md (same workload, same kernels)
+# profiles/tcgen05_fused_pipeline_sweep_L4096_bs64_d05.md and profiles/simt_fused_fp32_image_L1024_bs32.md
+# (same workloads, same kernels)
 NCU_TRAFFIC = {
-    "sweep_L4096_bs64_d05": {"fused_fwd": 193.9e6, "bwd_row": 352.5e6, "spmm_dkdv": 332.6e6},
+    "sweep_L4096_bs64_d05": {"fused_fwd": 251.5e6, "bwd_row": 349.0e6, "spmm_dkdv": 333.0e6},
+    "image_L1024_fp32_B256": {"fused_fwd": 581.9e6, "bwd_row": 971.0e6, "spmm_dkdv": 903.6e6},
+}
+
+
+NCU_TRAFFIC_SOURCE = {
+    "sweep_L4096_bs64_d05": "ncu dram bytes per launch, profiles/tcgen05_fused_pipeline_sweep_L4096_bs64_d05.md",
+    "image_L1024_fp32_B256": "ncu dram bytes per launch, profiles/simt_fused_fp32_image_L1024_bs32.md",
 }
 
 
@@ -473,7 +481,7 @@ def main():
     achieved = dom_bytes / (stages[dom] * 1e-3) / 1e9
     roofline = {"kernel": dom, "bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                 "frac": achieved / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC.get(args.workload, {}).get(dom),
-                "traffic_source": "ncu dram bytes per launch, profiles/tcgen05_fused_pipeline_sweep_L4096_bs64_d05.md",
+                "traffic_source": NCU_TRAFFIC_SOURCE.get(args.workload),
                 "peak_source": peaks["source"],
                 "algorithmic_bytes_per_launch": dom_bytes, "ms_per_launch": stages[dom]}
     step_bound_ms = max(flops / (peaks["bf16_tflops"] * 1e12), fused_bytes / (peaks["hbm_gbs"] * 1e9)) * 1e3
