@@ -339,6 +339,66 @@ def run_pattern(args, rank, local_rank):
         "cpu_baseline": cpu, "gpu_launches": 3 * args.steps}))
 
 
+def run_sweep_table(args, rank, world, local_rank):
+    """Benchmark config 4 in full: L x block x density grid (B=8, H=8, d=64, bf16), fwd+bwd of one layer through
+    the C ABI with inputs resident in HBM, CUDA events; one JSON line whose "sweep" key holds the table.  Every
+    rank runs the same grid on its own shard (no collective); the value reported per cell is rank 0's."""
+    from spion_b200 import _lib, synthetic
+    from spion_b200._lib import check, lib, ptr
+    from spion_b200.native import BlockSparseAttention
+    dev = torch.device("cuda", local_rank)
+    B, H, d = 8, 8, 64
+    steps = min(args.steps, 20)
+    rows = []
+    for L in (1024, 2048, 4096, 8192, 16384):
+        g = torch.Generator().manual_seed(7 + L)
+        Q, K, V, dO = [torch.randn(B, H, L, d, generator=g).to(torch.bfloat16).to(dev) for _ in range(4)]
+        O = torch.empty_like(Q); dQ = torch.empty_like(Q); dK = torch.empty_like(Q); dV = torch.empty_like(Q)
+        lse = torch.empty(B * H * L, dtype=torch.float32, device=dev)
+        for bs in (32, 64):
+            cfg = {"head_dim": d, "num_head": H, "max_seq_len": L, "batch_size": B, "block_size": bs,
+                   "transformer_dim": H * d, "task": "sweep"}
+            mod = BlockSparseAttention(cfg, dtype=torch.bfloat16, device=dev)
+            check(lib.spion_set_stream(mod.handle, _lib.current_stream_ptr()))
+            for dens in (0.02, 0.05, 0.10, 0.30):
+                mat = synthetic.band_random_mask(2024 + bs, L // bs, dens)
+                nnzb = mod.set_mask(torch.as_tensor(mat).to(dev))
+                n = B * H * nnzb * bs * bs
+                P = torch.empty(n, dtype=torch.bfloat16, device=dev); dS = torch.empty_like(P)
+
+                def step():
+                    check(lib.spion_attn_forward_fused(mod.handle, ptr(Q), ptr(K), ptr(V), None, ptr(O), ptr(lse), ptr(P)))
+                    check(lib.spion_attn_backward_ex(mod.handle, ptr(Q), ptr(K), ptr(V), ptr(P), ptr(O), ptr(dO),
+                                                     ptr(dS), None, None, ptr(dQ), ptr(dK), ptr(dV)))
+                for _ in range(3):
+                    step()
+                mod.check_device_status()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                e0.record()
+                for _ in range(steps):
+                    step()
+                e1.record()
+                torch.cuda.synchronize()
+                ms = e0.elapsed_time(e1) / steps
+                rows.append({"L": L, "block": bs, "density": round(nnzb / float((L // bs) ** 2), 4), "nnzb": nnzb,
+                             "ms_per_step": round(ms, 4), "Mtokens_per_s": round(B * L / (ms * 1e-3) / 1e6, 2)})
+                del P, dS
+            del mod
+        del Q, K, V, dO, O, dQ, dK, dV
+        torch.cuda.empty_cache()
+    if rank == 0:
+        head = next(r for r in rows if r["L"] == 4096 and r["block"] == 64 and abs(r["density"] - 0.05) < 0.01)
+        print(json.dumps({"metric": "sparse-attn fwd+bwd Mtokens/s", "value": head["Mtokens_per_s"] * world,
+                          "unit": "Mtokens/s", "n_gpus": world, "steps": steps, "warmup": 3,
+                          "ms_per_step": head["ms_per_step"], "higher_is_better": True, "scaling": "weak",
+                          "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                          "config": {"workload": "sweep_table", "B": B, "H": H, "d_head": d,
+                                     "timing": "inputs resident in HBM; working set of every cell larger than L2 "
+                                               "except L=1024"},
+                          "sweep": rows}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -346,7 +406,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="sweep_L4096_bs64_d05",
-                    choices=sorted(WORKLOADS) + sorted(TRAIN_WORKLOADS) + ["pattern_L4096_bs64", "pattern_L1024_bs32"])
+                    choices=sorted(WORKLOADS) + sorted(TRAIN_WORKLOADS) +
+                    ["pattern_L4096_bs64", "pattern_L1024_bs32", "sweep_table"])
     ap.add_argument("--engine", default="auto", choices=["auto", "simt", "tcgen05", "staged"])
     ap.add_argument("--mode", default="auto", choices=["auto", "fused", "staged"],
                     help="fused: S/P/dP/dS stay on chip (tcgen05 engine); staged: one kernel per stage")
@@ -379,6 +440,9 @@ def main():
         return
     if args.workload.startswith("pattern_"):
         run_pattern(args, rank, local_rank)
+        return
+    if args.workload == "sweep_table":
+        run_sweep_table(args, rank, world, local_rank)
         return
 
     B, H, L, d, bs, dens, dt = WORKLOADS[args.workload]

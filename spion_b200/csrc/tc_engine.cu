@@ -442,85 +442,107 @@ __global__ void __launch_bounds__(128) k_spmm(const __grid_constant__ CUtensorMa
                                               const __grid_constant__ CUtensorMap tmB1,
                                               __nv_bfloat16* __restrict__ out0, __nv_bfloat16* __restrict__ out1,
                                               const int* __restrict__ line_ptr, const int* __restrict__ idx,
-                                              const int* __restrict__ pos, int L, int nnzb, int* status) {
+                                              const int* __restrict__ pos, const int* __restrict__ order, int L,
+                                              int nnzb, int* status) {
   using T = OpTile<D>;
   constexpr int NP = DUAL ? 2 : 1;                                // products per entry
   constexpr int STAGE_BYTES = NP * (VT_BYTES + T::BYTES);
   extern __shared__ uint8_t smem_raw[];
   const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t bar_load = sbase + NST * STAGE_BYTES;
-  const uint32_t bar_mma = bar_load + 8;
-  const uint32_t slot = bar_mma + 8;
+  // ring of NST stages, one entry of the line each: full[s] (tiles landed), empty[s] (MMAs that read them done)
+  const uint32_t bar_full = sbase + NST * STAGE_BYTES;
+  const uint32_t bar_empty = bar_full + 8 * NST;
+  const uint32_t bar_done = bar_empty + 8 * NST;
+  const uint32_t slot = bar_done + 8;
   uint32_t* slot_ptr = reinterpret_cast<uint32_t*>(smem_raw + (slot - smem_u32(smem_raw)));
 
-  const int line = blockIdx.x, bh = blockIdx.y;
+  // One (b,h) matrix after the other (the value tiles of a matrix were written together, and a grid that
+  // interleaves the matrices measured slower); inside a matrix the longest lines first when an order is given.
+  const int bh = blockIdx.y, line = order ? order[blockIdx.x] : (int)blockIdx.x;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   constexpr uint32_t TMEM_COLS = (NP * D) < 32 ? 32 : (NP * D);   // 32, 64 or 128: powers of two
   __shared__ int s_abort;                                         // an earlier CTA gave up: do not pile on
-  if (tid == 0) s_abort = *reinterpret_cast<volatile int*>(status);
+  const int beg = line_ptr[line], end = line_ptr[line + 1];
+  const int n = end - beg;
+
+  // warp 0, all lanes: request entry e into stage st (one copy per lane)
+  auto fill = [&](int st, int e) {
+    const uint32_t sa = sbase + st * STAGE_BYTES;
+    if (lane == 0) mbar_expect_tx(bar_full + 8 * st, STAGE_BYTES);
+    __syncwarp();
+    if (lane < 2 * NP) {
+      const int other = idx[e];                                    // block column (CSR) or block row (CSC)
+      const int blk = DUAL ? pos[e] : e;                           // CSR block id of the value tile
+      const int vrow = (int)(((size_t)bh * nnzb + blk) * BS);
+      const int orow = bh * L + other * BS;
+      if (lane == 0) tma_load_2d(sa, &tmV0, bar_full + 8 * st, 0, vrow);
+      if (lane == 1) tma_load_2d(sa + VT_BYTES, &tmB0, bar_full + 8 * st, 0, orow);
+      if (DUAL && lane == 2) tma_load_2d(sa + VT_BYTES + T::BYTES, &tmV1, bar_full + 8 * st, 0, vrow);
+      if (DUAL && lane == 3) tma_load_2d(sa + 2 * VT_BYTES + T::BYTES, &tmB1, bar_full + 8 * st, 0, orow);
+    }
+  };
+
+  if (warp == 0) {
+    if (lane == 0) {
+      s_abort = *reinterpret_cast<volatile int*>(status);
+      for (int st = 0; st < NST; ++st) { mbar_init(bar_full + 8 * st, 1); mbar_init(bar_empty + 8 * st, 1); }
+      mbar_init(bar_done, 1);
+      fence_barrier_init();
+    }
+  }
   __syncthreads();
   if (s_abort != 0) return;
-
   if (warp == 0) {
     tmem_alloc(slot, TMEM_COLS);
     tmem_relinquish();
-  }
-  if (tid == 0) {
-    mbar_init(bar_load, 1);
-    mbar_init(bar_mma, 1);
-    fence_barrier_init();
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *slot_ptr;
-
-  const int beg = line_ptr[line], end = line_ptr[line + 1];
   constexpr uint32_t IDESC = make_idesc_bf16(64, D, DUAL ? 1 : 0, 1);
-  uint32_t ph_load = 0, ph_mma = 0;
   bool ok = true;
 
-  for (int e0 = beg; e0 < end && ok; e0 += NST) {
-    const int nt = min(NST, end - e0);
-    if (tid == 0) {
-      mbar_expect_tx(bar_load, nt * STAGE_BYTES);
-      for (int t = 0; t < nt; ++t) {
-        const int e = e0 + t;
-        const int other = idx[e];                                  // block column (CSR) or block row (CSC)
-        const int blk = DUAL ? pos[e] : e;                         // CSR block id of the value tile
-        const uint32_t st = sbase + t * STAGE_BYTES;
-        const int vrow = (int)(((size_t)bh * nnzb + blk) * BS);
-        tma_load_2d(st, &tmV0, bar_load, 0, vrow);
-        tma_load_2d(st + VT_BYTES, &tmB0, bar_load, 0, bh * L + other * BS);
-        if (DUAL) {
-          tma_load_2d(st + VT_BYTES + T::BYTES, &tmV1, bar_load, 0, vrow);
-          tma_load_2d(st + 2 * VT_BYTES + T::BYTES, &tmB1, bar_load, 0, bh * L + other * BS);
-        }
-      }
-    }
-    if (!__syncthreads_and(mbar_wait(bar_load, ph_load))) { if (tid == 0) report(status, ERR_LOAD_WAIT); ok = false; break; }
-    ph_load ^= 1;
-    if (tid == 0) {
-      tc_fence_after();
-      for (int t = 0; t < nt; ++t) {
-        const uint32_t st = sbase + t * STAGE_BYTES;
-        const uint32_t first = (e0 == beg && t == 0) ? 0u : 1u;
+  if (warp == 0) {
+    // (requesting the first tiles before the TMEM allocation measured slower for this kernel)
+    for (int t = 0; t < NST && t < n; ++t) fill(t, beg + t);
+    for (int i = 0; i < n; ++i) {
+      const int st = i % NST;
+      const uint32_t ph = (uint32_t)(i / NST) & 1u;
+      if (!__all_sync(0xffffffffu, mbar_wait(bar_full + 8 * st, ph))) { if (lane == 0) report(status, ERR_LOAD_WAIT); ok = false; break; }
+      if (lane == 0) {
+        tc_fence_after();
+        const uint32_t sa = sbase + st * STAGE_BYTES;
+        const uint32_t first = i == 0 ? 0u : 1u;
 #pragma unroll
         for (int kk = 0; kk < BS / 16; ++kk) {
-          const uint64_t a0 = DUAL ? ValTile::mnmajor(st, kk) : ValTile::kmajor(st, kk);
-          mma_bf16(tmem, a0, T::mnmajor(st + VT_BYTES, kk), IDESC, (kk > 0) ? 1u : first);
+          const uint64_t a0 = DUAL ? ValTile::mnmajor(sa, kk) : ValTile::kmajor(sa, kk);
+          mma_bf16(tmem, a0, T::mnmajor(sa + VT_BYTES, kk), IDESC, (kk > 0) ? 1u : first);
         }
         if (DUAL) {
 #pragma unroll
           for (int kk = 0; kk < BS / 16; ++kk)
-            mma_bf16(tmem + D, ValTile::mnmajor(st + VT_BYTES + T::BYTES, kk),
-                     T::mnmajor(st + 2 * VT_BYTES + T::BYTES, kk), IDESC, (kk > 0) ? 1u : first);
+            mma_bf16(tmem + D, ValTile::mnmajor(sa + VT_BYTES + T::BYTES, kk),
+                     T::mnmajor(sa + 2 * VT_BYTES + T::BYTES, kk), IDESC, (kk > 0) ? 1u : first);
         }
+        if (i + 1 == n) mma_commit(bar_done);
+        else mma_commit(bar_empty + 8 * st);
       }
-      mma_commit(bar_mma);
+      __syncwarp();
+      if (i + NST < n) {                                           // this stage takes entry i + NST once its MMAs are done
+        if (!__all_sync(0xffffffffu, mbar_wait(bar_empty + 8 * st, ph))) { if (lane == 0) report(status, ERR_MMA_WAIT); ok = false; break; }
+        fill(st, beg + i + NST);
+      }
     }
-    if (!__syncthreads_and(mbar_wait(bar_mma, ph_mma))) { if (tid == 0) report(status, ERR_MMA_WAIT); ok = false; break; }
-    ph_mma ^= 1;
+  }
+  {
+    // only warp 0 polls the barrier of the last MMAs; the other warps sleep in the CTA barrier
+    bool w = true;
+    if (warp == 0) {
+      w = (n > 0 && ok) ? mbar_wait(bar_done, 0) : (n == 0);
+      tc_fence_before();
+    }
+    if (!__syncthreads_and(w)) { if (tid == 0 && ok) report(status, ERR_MMA_WAIT); ok = false; } else ok = true;
     tc_fence_after();
   }
 
@@ -625,6 +647,19 @@ __global__ void k_row_info(const int32_t* __restrict__ row_ptr, const int32_t* _
   }
 }
 
+// Lines (block columns) sorted by descending number of entries (ties: ascending index).  One CTA.
+__global__ void k_line_order(const int32_t* __restrict__ line_ptr, int nb, int* __restrict__ order) {
+  __shared__ int s_n[SPION_MAX_NB];
+  for (int c = threadIdx.x; c < nb; c += blockDim.x) s_n[c] = line_ptr[c + 1] - line_ptr[c];
+  __syncthreads();
+  for (int c = threadIdx.x; c < nb; c += blockDim.x) {
+    const int n = s_n[c];
+    int rank = 0;
+    for (int o = 0; o < nb; ++o) rank += (s_n[o] > n) || (s_n[o] == n && o < c);
+    order[rank] = c;
+  }
+}
+
 // Self-test of the bounded wait: one CTA waits on an mbarrier that nothing ever arrives on, with a
 // short limit; it must give up, record ERR_LOAD_WAIT in the status word and return normally.
 __global__ void k_wait_selftest(int* status, long long limit_cycles) {
@@ -642,7 +677,7 @@ __global__ void k_wait_selftest(int* status, long long limit_cycles) {
 constexpr int NST_N = 4, NST_T = 2;
 
 template <int D> constexpr size_t smem_dp_ds() { return 1024 + (size_t)5 * OpTile<D>::BYTES + 4 * VT_BYTES + 64; }
-template <int D> constexpr size_t smem_spmm(int nst, int np) { return 1024 + (size_t)nst * np * (VT_BYTES + OpTile<D>::BYTES) + 64; }
+template <int D> constexpr size_t smem_spmm(int nst, int np) { return 1024 + (size_t)nst * np * (VT_BYTES + OpTile<D>::BYTES) + 128; }
 
 template <int D>
 int set_attrs() {
@@ -701,15 +736,16 @@ int run_backward(spion_ctx* c, TcState* s, const void* Q, const void* K, const v
                                                           vw.nnzb, c->scale, c->status_dev);
     SPION_LAUNCH_CHECK();
     prof_mark(c, SPION_STAGE_FUSED_DP_DS);
-    k_spmm<D, false, NST_N><<<grid, 128, smem_spmm<D>(NST_N, 1), c->stream>>>(
-        mds, mds, mk, mk, (__nv_bfloat16*)dQ, nullptr, vw.row_ptr, vw.col_idx, nullptr, c->L, vw.nnzb, c->status_dev);
+    k_spmm<D, false, NST_N><<<dim3(vw.nb, c->BH), 128, smem_spmm<D>(NST_N, 1), c->stream>>>(
+        mds, mds, mk, mk, (__nv_bfloat16*)dQ, nullptr, vw.row_ptr, vw.col_idx, nullptr, nullptr, c->L, vw.nnzb,
+        c->status_dev);
     SPION_LAUNCH_CHECK();
     c->launches += 2;
     prof_mark(c, SPION_STAGE_SPMM_DQ);
   }
-  k_spmm<D, true, NST_T><<<grid, 128, smem_spmm<D>(NST_T, 2), c->stream>>>(
-      mds, mp, mq, mdo, (__nv_bfloat16*)dK, (__nv_bfloat16*)dV, vw.col_ptr, vw.row_idx, vw.csc_pos, c->L, vw.nnzb,
-      c->status_dev);
+  k_spmm<D, true, NST_T><<<dim3(vw.nb, c->BH), 128, smem_spmm<D>(NST_T, 2), c->stream>>>(
+      mds, mp, mq, mdo, (__nv_bfloat16*)dK, (__nv_bfloat16*)dV, vw.col_ptr, vw.row_idx, vw.csc_pos,
+      s->col_order, c->L, vw.nnzb, c->status_dev);
   SPION_LAUNCH_CHECK();
   c->launches += 1;
   prof_mark(c, SPION_STAGE_SPMM_DKDV);
@@ -801,7 +837,10 @@ int tc_engine_prepare(spion_ctx* c) {
   if (!s->row_info && cudaMalloc(&s->row_info, (size_t)SPION_MAX_NB * sizeof(int4)) != cudaSuccess) return SPION_ERR_ALLOC;
   k_row_info<<<1, 512, 0, c->stream>>>(vw.row_ptr, vw.col_idx, vw.nb, s->row_info);
   SPION_LAUNCH_CHECK();
-  c->launches += 1;
+  if (!s->col_order && cudaMalloc(&s->col_order, (size_t)SPION_MAX_NB * sizeof(int)) != cudaSuccess) return SPION_ERR_ALLOC;
+  k_line_order<<<1, 512, 0, c->stream>>>(vw.col_ptr, vw.nb, s->col_order);
+  SPION_LAUNCH_CHECK();
+  c->launches += 2;
   return SPION_OK;
 }
 
@@ -811,6 +850,7 @@ void tc_engine_release(spion_ctx* c) {
   free_super(s);
   cudaFree(s->lse_ws);
   cudaFree(s->row_info);
+  cudaFree(s->col_order);
   delete s;
   c->tc = nullptr;
 }

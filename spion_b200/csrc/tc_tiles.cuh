@@ -63,6 +63,7 @@ struct TcState {
   EncodeTiledFn encode = nullptr;
   int stages = 0;               // debugging switches (SPION_TC_STAGES): bit 6 = split row kernels
   float* lse_ws = nullptr;      // [BH*L] log-sum-exp workspace for the calls that do not expose it
+  int* col_order = nullptr;     // block columns from the longest to the shortest
   int4* row_info = nullptr;     // per block row: {row_ptr, blocks, col0 | col1 << 16, col2 | col3 << 16}: one load instead of two dependent ones
   // 32-wide masks run on 64-wide super-blocks: derived structure + which 32x32 quarters are selected
   bool super = false;
