@@ -261,15 +261,18 @@ __global__ void __launch_bounds__(128) k_bwd_row(const __grid_constant__ CUtenso
       fence_barrier_init();
     }
     __syncwarp();
-    if (s_abort == 0 && nblk > 0) issue_loads(0);
+    // long rows ask for their first tiles before the (larger) TMEM allocation, short rows after it:
+    // each order measured faster for its case
+    if (s_abort == 0 && nblk > 0 && !single) issue_loads(0);
   }
-  a_loaded = true;
   __syncthreads();
   if (s_abort != 0) return;
   if (q == 0) {
     tmem_alloc(slot, ncols);
     tmem_relinquish();
+    if (nblk > 0 && single) issue_loads(0);
   }
+  a_loaded = true;
   float delta;
   {
     const size_t off = ((size_t)bh * L + r * BS + row) * D + hf * (D / 2);
