@@ -244,7 +244,9 @@ def run_training(args, rank, world, local_rank):
     dens = [float(m.mean()) for m in mat_lst[0]]
     del maps
     torch.cuda.empty_cache()
-    use_graph = not args.no_graph
+    # The captured step holds no collective: with more than one rank the step runs eagerly (a capture that
+    # included the gradient all-reduce did not finish on 8 GPUs).
+    use_graph = not args.no_graph and world == 1
     if use_graph:
         tr.capture_sparse_step(ids, y)
     run_step = (lambda a, b: tr.step_graph(a, b)) if use_graph else (lambda a, b: tr.step(a, b)[0])

@@ -41,6 +41,11 @@ def init_from_env(backend: str | None = None, timeout_s: float = 600.0):
     return rank, world
 
 
+def world_size() -> int:
+    """Ranks in the job (1 when no process group was set up)."""
+    return dist.get_world_size() if dist.is_available() and dist.is_initialized() else 1
+
+
 def shard_range(global_batch: int, rank: int, world: int):
     """Contiguous, even split of the global batch (the benchmark configs divide evenly)."""
     if global_batch % world != 0:

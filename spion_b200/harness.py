@@ -151,6 +151,8 @@ class Trainer:
         calls are plain stream-ordered launches with caller-owned buffers, which is what capture needs."""
         if self.mat_lst is None:
             raise RuntimeError("capture the step after discover()")
+        if dp.world_size() > 1:
+            raise RuntimeError("the captured step must not contain the gradient all-reduce: run multi-rank steps eagerly")
         dual = isinstance(ids, (tuple, list))
         self._g_ids = tuple(t.clone() for t in ids) if dual else ids.clone()
         self._g_lab = label.clone()
