@@ -57,9 +57,8 @@ TRAIN_WORKLOADS = {
 }
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch, from the ncu capture summarised in
-# profiles/tcgen05_fused_pipeline_sweep_L4096_bs64_d05.md and profiles/simt_fused_fp32_image_L1024_bs32.md
-# (same workloads, same kernels)
+# dram__bytes_read.sum + dram__bytes_write.sum per launch, from one ncu capture of the same workload and
+# kernels (the summaries are kept under profiles/; NCU_TRAFFIC_SOURCE names the one each entry comes from)
 NCU_TRAFFIC = {
     "sweep_L4096_bs64_d05": {"fused_fwd": 251.5e6, "bwd_row": 349.0e6, "spmm_dkdv": 333.0e6},
     "image_L1024_fp32_B256": {"fused_fwd": 581.9e6, "bwd_row": 971.0e6, "spmm_dkdv": 903.6e6},

@@ -15,10 +15,12 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT = os.path.join(HERE, "_ref")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+# where the reference checkout lies unless a path is given: $SPION_REFERENCE_ROOT, else ~/reference
+DEFAULT_ROOT = os.environ.get("SPION_REFERENCE_ROOT", os.path.join(os.path.expanduser("~"), "reference"))
 FILES = {"attn": "-lcublas", "attn_mask": "-lcublas", "block_attn": "-lcusparse", "block_attn_mask": "-lcusparse"}
 
 
-def build(ref_root="/root/reference", force=False):
+def build(ref_root=DEFAULT_ROOT, force=False):
     if not os.path.isdir(os.path.join(ref_root, "models")):
         return []
     os.makedirs(OUT, exist_ok=True)
@@ -39,4 +41,4 @@ def build(ref_root="/root/reference", force=False):
 
 if __name__ == "__main__":
     roots = [a for a in sys.argv[1:] if not a.startswith("-")]
-    print("\n".join(build(roots[0] if roots else "/root/reference", force="--force" in sys.argv)))
+    print("\n".join(build(roots[0] if roots else DEFAULT_ROOT, force="--force" in sys.argv)))

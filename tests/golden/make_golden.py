@@ -186,4 +186,5 @@ def main(ref_root):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    main(sys.argv[1] if len(sys.argv) > 1 else
+         os.environ.get("SPION_REFERENCE_ROOT", os.path.join(os.path.expanduser("~"), "reference")))
