@@ -1,5 +1,5 @@
 // C ABI of spion_b200: contexts, the reference-layout entry points and the native ones.
-// Orchestration only; kernels live in simt_attn.cu, structure.cu, pattern.cu, tc_engine.cu.
+// Orchestration only; kernels live in simt_fused.cu, simt_attn.cu, structure.cu, pattern.cu, tc_fused.cu, tc_engine.cu.
 //
 // Pipelines (reference: Attention::attn_forward / attn_backward, models/block_attn.cu:453-545):
 //   forward   S = Q K^T on the mask  ->  P = sparse row softmax(S)  ->  O = P V
