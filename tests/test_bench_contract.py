@@ -36,3 +36,20 @@ def test_algorithmic_formulas():
     assert bench.stage_bytes("bwd_row", BH, L, d, nnz, e, e) == 5 * ld + 2 * e * v
     assert bench.stage_bytes("spmm_dkdv", BH, L, d, nnz, e, e) == 2 * e * v + 4 * ld
     assert bench.stage_flops("bwd_row", BH, d, nnz) == 4.0 * nnz * d * BH
+
+
+def test_workload_tables_are_consistent():
+    """Every workload names a block size that divides L; the traffic table only names known workloads and stages."""
+    sys.path.insert(0, ROOT)
+    import bench
+    for name, (B, H, L, d, bs, dens, dt) in bench.WORKLOADS.items():
+        assert L % bs == 0 and d in (32, 64) and dt in ("bf16", "fp32") and 0 < dens <= 1, name
+    for name, per_stage in bench.NCU_TRAFFIC.items():
+        assert name in bench.WORKLOADS and name in bench.NCU_TRAFFIC_SOURCE
+        B, H, L, d, bs, dens, dt = bench.WORKLOADS[name]
+        esz = 2 if dt == "bf16" else 4
+        nnz = int(round(dens * (L // bs) ** 2)) * bs * bs
+        for stage, traffic in per_stage.items():
+            # measured DRAM traffic of a launch is within a small factor of the algorithmic bytes
+            alg = bench.stage_bytes(stage, B * H, L, d, nnz, esz, esz, p_stored=True)
+            assert 0.3 * alg < traffic < 1.5 * alg, (name, stage, traffic, alg)

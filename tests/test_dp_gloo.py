@@ -14,8 +14,9 @@ def _worker(rank, world, port, out):
     sys.path.insert(0, ROOT)
     os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     from spion_b200 import dp
+    assert dp.world_size() == 1                                   # before the group exists
     r, w = dp.init_from_env("gloo", timeout_s=60)
-    assert (r, w) == (rank, world)
+    assert (r, w) == (rank, world) and dp.world_size() == world
     torch.manual_seed(0)
     model = torch.nn.Sequential(torch.nn.Linear(8, 16), torch.nn.ReLU(), torch.nn.Linear(16, 3))
     bucket = dp.FlatGradBucket(model.parameters())
