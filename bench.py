@@ -147,24 +147,19 @@ def stage_bytes(stage, BH, L, d, nnz, esz, psz, p_stored=False):
         "sddmm_s": 2 * ld + 4 * v, "softmax_fwd": 4 * v + psz * v, "spmm_o": psz * v + 2 * ld,
         "sddmm_dp": 2 * ld + 4 * v, "softmax_bwd": 4 * v + psz * v + psz * v, "spmm_dq": psz * v + 2 * ld,
         "spmm_dk": psz * v + 2 * ld, "spmm_dv": psz * v + 2 * ld,
-        "fused_s_p": 2 * ld + psz * v, "fused_dp_ds": 2 * ld + 2 * psz * v + 4 * BH * L,
-        "delta": 2 * ld + 4 * BH * L, "spmm_dkdv": 2 * psz * v + 4 * ld, "structure": 0,
+        "fused_dp_ds": 2 * ld + 2 * psz * v + 4 * BH * L,
+        "spmm_dkdv": 2 * psz * v + 4 * ld, "structure": 0,
         # fused kernels: operands once, no S/P/dP/dS (P written only when the staged backward needs it)
         "fused_fwd": 4 * ld + 4 * BH * L + (psz * v if p_stored else 0),
-        "fused_bwd_row": 6 * ld + 8 * BH * L, "fused_bwd_col": 6 * ld + 8 * BH * L,
         "bwd_row": 5 * ld + 2 * psz * v,
     }[stage]
 
 
 def stage_flops(stage, BH, d, nnz):
-    if stage in ("sddmm_s", "spmm_o", "sddmm_dp", "spmm_dq", "spmm_dk", "spmm_dv", "fused_s_p", "fused_dp_ds"):
+    if stage in ("sddmm_s", "spmm_o", "sddmm_dp", "spmm_dq", "spmm_dk", "spmm_dv", "fused_dp_ds"):
         return 2.0 * nnz * d * BH
     if stage in ("spmm_dkdv", "fused_fwd", "bwd_row"):
         return 4.0 * nnz * d * BH
-    if stage == "fused_bwd_row":
-        return 6.0 * nnz * d * BH
-    if stage == "fused_bwd_col":
-        return 8.0 * nnz * d * BH
     return 0.0
 
 

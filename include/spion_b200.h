@@ -104,15 +104,11 @@ enum {
   SPION_STAGE_SPMM_DQ = 6,     /* dQ = dS K                                        */
   SPION_STAGE_SPMM_DK = 7,     /* dK = dS^T Q                                      */
   SPION_STAGE_SPMM_DV = 8,     /* dV = P^T dO                                      */
-  SPION_STAGE_RESERVED_9 = 9,
-  SPION_STAGE_FUSED_DP_DS = 10,/* tcgen05: dP tiles + softmax backward -> dS (split row kernel) */
-  SPION_STAGE_DELTA = 11,      /* row sums of dO*O                                 */
-  SPION_STAGE_SPMM_DKDV = 12,  /* tcgen05: dK and dV in one kernel                 */
-  SPION_STAGE_FUSED_FWD = 13,  /* tcgen05: S, softmax, P V in one kernel            */
-  SPION_STAGE_RESERVED_14 = 14,
-  SPION_STAGE_RESERVED_15 = 15,
-  SPION_STAGE_BWD_ROW = 16,    /* tcgen05: dP, dS and dQ per block row (P read, dS written) */
-  SPION_STAGE_COUNT = 17
+  SPION_STAGE_FUSED_DP_DS = 9, /* tcgen05: dP tiles + softmax backward -> dS (split row kernel) */
+  SPION_STAGE_SPMM_DKDV = 10,  /* fused kernels: dK and dV in one kernel           */
+  SPION_STAGE_FUSED_FWD = 11,  /* fused kernels: S, softmax, P V in one kernel     */
+  SPION_STAGE_BWD_ROW = 12,    /* fused kernels: dP, dS and dQ per block row (P read, dS written) */
+  SPION_STAGE_COUNT = 13
 };
 int spion_profile(spion_ctx* ctx, int enable);
 int spion_profile_get(spion_ctx* ctx, int stage, double* total_ms, long long* launches);

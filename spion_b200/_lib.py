@@ -17,7 +17,7 @@ CONV_DIAG, CONV_BOX = 0, 1
 SELECT_PATHS, SELECT_TOPK = 0, 1
 KIND_DENSE, KIND_DENSE_KPM, KIND_BLOCK, KIND_BLOCK_KPM = 0, 1, 2, 3
 ENGINE_AUTO, ENGINE_SIMT, ENGINE_TCGEN05, ENGINE_SIMT_STAGED = 0, 1, 2, 3
-STAGE_COUNT = 17
+STAGE_COUNT = 13
 
 # name -> (restype, argtypes); every symbol include/spion_b200.h declares
 SIGNATURES = {

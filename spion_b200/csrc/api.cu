@@ -204,7 +204,7 @@ extern "C" int spion_profile_reset(spion_ctx* c) {
 extern "C" const char* spion_stage_name(int stage) {
   static const char* names[SPION_STAGE_COUNT] = {
       "structure", "sddmm_s", "softmax_fwd", "spmm_o", "sddmm_dp", "softmax_bwd", "spmm_dq", "spmm_dk", "spmm_dv",
-      "reserved9", "fused_dp_ds", "delta", "spmm_dkdv", "fused_fwd", "reserved14", "reserved15", "bwd_row"};
+      "fused_dp_ds", "spmm_dkdv", "fused_fwd", "bwd_row"};
   return (stage >= 0 && stage < SPION_STAGE_COUNT) ? names[stage] : "?";
 }
 
