@@ -463,8 +463,7 @@ def main():
     n = BH * nnz
     P = torch.empty(n, dtype=tdt, device=dev); dS = torch.empty(n, dtype=tdt, device=dev)
     O = torch.empty_like(Q); dQ = torch.empty_like(Q); dK = torch.empty_like(Q); dV = torch.empty_like(Q)
-    scr = torch.empty(n, dtype=torch.float32, device=dev)
-    delta = torch.empty(BH * L, dtype=torch.float32, device=dev)
+    scr = torch.empty(n, dtype=torch.float32, device=dev) if mod.needs_scratch else None
     check(lib.spion_set_stream(mod.handle, _lib.current_stream_ptr()))
 
     lse = torch.empty(BH * L, dtype=torch.float32, device=dev)
@@ -475,7 +474,7 @@ def main():
         else:
             check(lib.spion_attn_forward_ex(mod.handle, ptr(Q), ptr(K), ptr(V), None, ptr(P), ptr(O), ptr(scr)))
         check(lib.spion_attn_backward_ex(mod.handle, ptr(Q), ptr(K), ptr(V), ptr(P), ptr(O), ptr(dO), ptr(dS),
-                                         ptr(scr), ptr(delta), ptr(dQ), ptr(dK), ptr(dV)))
+                                         ptr(scr), None, ptr(dQ), ptr(dK), ptr(dV)))
 
     def barrier():
         torch.cuda.synchronize()

@@ -211,15 +211,19 @@ int spion_pattern_nnzb(const spion_ctx* ctx);
  *   Q, K, V, O  [BH,L,d] row-major (no transposed copies: compare attention_blockcuda.py:48)
  *   P           [BH, nnzb, bs, bs] block tiles in CSR block order (out; needed by backward)
  *   keypad      [BH*L] fp32 penalty (1e6 on padded keys) or NULL
- *   S_scratch   [BH*nnzb*bs*bs] fp32, used by the SIMT engine only (may be NULL otherwise).
- * On the tcgen05 engine this is the fused forward kernel with the probabilities stored. */
+ *   S_scratch   [BH*nnzb*bs*bs] fp32, used by the per-stage SIMT kernels only (NULL allowed when
+ *               spion_needs_scratch() is 0).
+ * On the tcgen05 engine and with the fused fp32 kernels this is one forward kernel with the
+ * probabilities stored. */
 int spion_attn_forward_ex(spion_ctx* ctx, const void* Q, const void* K, const void* V,
                           const float* keypad, void* P, void* O, float* S_scratch);
 
 /* Native backward.
  *   dS          [BH, nnzb, bs, bs] elements of the context dtype (scratch, written)
- *   dP_scratch  [BH*nnzb*bs*bs] fp32, used by the SIMT engine only
- *   delta       unused (kept for ABI stability; may be NULL)
+ *   O           the forward output: required on the tcgen05 engine; the fused fp32 kernels use it
+ *               when given (one pass over a block row instead of two), NULL allowed there
+ *   dP_scratch  [BH*nnzb*bs*bs] fp32, used by the per-stage SIMT kernels only
+ *   delta       unused (may be NULL)
  *   dQ, dK, dV  [BH,L,d] (out). */
 int spion_attn_backward_ex(spion_ctx* ctx, const void* Q, const void* K, const void* V,
                            const void* P, const void* O, const void* dO,

@@ -196,11 +196,10 @@ def _make_function(mod: BlockSparseAttention):
             n = mod.BH * mod.nnz
             dS = torch.empty(n, dtype=mod.dtype, device=dev)
             scratch = torch.empty(n, dtype=torch.float32, device=dev) if mod.needs_scratch else None
-            delta = torch.empty(mod.BH * mod.L, dtype=torch.float32, device=dev)
             dq, dk, dv = torch.empty_like(q), torch.empty_like(q), torch.empty_like(q)
             check(lib.spion_set_stream(mod.handle, _lib.current_stream_ptr()))
             check(lib.spion_attn_backward_ex(mod.handle, ptr(q), ptr(k), ptr(v), ptr(P), ptr(O), ptr(go), ptr(dS),
-                                             ptr(scratch), ptr(delta), ptr(dq), ptr(dk), ptr(dv)),
+                                             ptr(scratch), None, ptr(dq), ptr(dk), ptr(dv)),
                   "spion_attn_backward_ex")
             return dq, dk, dv, None
 
