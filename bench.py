@@ -163,6 +163,24 @@ def stage_flops(stage, BH, d, nnz):
     return 0.0
 
 
+def time_c_port(Q, K, V, dO, mat, bs, reps=3):
+    """Seconds per fwd+bwd of the plain-C restatement (row-wise, selected blocks only, OpenMP over the host cores),
+    or None when the library cannot be built or loaded.  A second CPU figure beside the dense-masked torch path."""
+    try:
+        from oracle import c_oracle
+        lib = c_oracle.load()
+    except Exception:
+        return None
+    if lib is None:
+        return None
+    q, k, v, g = [t.numpy() for t in (Q, K, V, dO)]
+    c_oracle.attention_step(q, k, v, mat, bs, g)
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        c_oracle.attention_step(q, k, v, mat, bs, g)
+    return {"s_per_step": (time.perf_counter() - t0) / reps, "threads": int(lib.oracle_threads())}
+
+
 def run_reference(args, rank):
     """--impl reference: the oracle's dense-masked PyTorch path on the host cores (the reference has
     no CPU implementation of the sparse kernels; this restates models/block_attn.cu:453-545)."""
@@ -186,12 +204,17 @@ def run_reference(args, rank):
     dt_s = (time.perf_counter() - t0) / steps
     val = Bs * L / dt_s / 1e6
     sample = f"B={Bs} of {B} batch elements (H={H}, L={L}, d={d}), fp32, {steps} timed steps"
+    cport = time_c_port(Q, K, V, dO, mat, bs)
+    if cport:
+        cport["value"] = Bs * L / cport["s_per_step"] / 1e6
+        cport["unit"] = "Mtokens/s"
     print(json.dumps({
         "impl": "reference", "metric": "sparse-attn fwd+bwd Mtokens/s at L=%d" % L, "value": val, "unit": "Mtokens/s",
         "n_gpus": args.gpus, "steps": steps, "warmup": 1, "ms_per_step": dt_s * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": args.workload, "B": Bs, "H": H, "L": L, "d_head": d, "block": bs, "density": dens},
-        "cpu_baseline": {"value": val, "unit": "Mtokens/s", "cores": cores, "kind": "port", "sample": sample},
+        "cpu_baseline": {"value": val, "unit": "Mtokens/s", "cores": cores, "kind": "port", "sample": sample,
+                         "c_port": cport},
         "e2e": {"value": val, "unit": "Mtokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
 
@@ -628,9 +651,13 @@ def main():
         for _ in range(reps):
             oatt.fwd_bwd_step(cQ, cK, cV, cdO, M)
         cs = (time.perf_counter() - t0) / reps
+        cport = time_c_port(cQ, cK, cV, cdO, mat, bs)
+        if cport:
+            cport["value"] = Bs * L / cport["s_per_step"] / 1e6
+            cport["unit"] = "Mtokens/s"
         cpu = {"value": Bs * L / cs / 1e6, "unit": "Mtokens/s", "cores": cores, "kind": "port",
                "sample": f"B={Bs} of {B} batch elements (H={H}, L={L}, d={d}), fp32 dense-masked torch, {reps} timed steps",
-               "s_per_step": cs}
+               "s_per_step": cs, "c_port": cport}
 
     if rank == 0:
         line = {

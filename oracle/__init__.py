@@ -23,4 +23,8 @@ Pinning status
   (``sparse_attention_rowwise``) and is cross-checked against the dense-masked
   closed form; on a GPU box it is additionally compared with the reference's
   own CUDA file compiled into ``oracle/_ref`` (see ``oracle/build_ref.py``).
+* plain-C restatement (``oracle/spion_oracle.c``, bound by ``oracle.c_oracle``, built by
+  ``oracle/build_c.py``): a second, independent restatement of all three parts.
+  ``tests/test_oracle_c.py`` requires it to reproduce the golden masks, the pooled map, the
+  threshold and the CSR arrays bit for bit and the attention step within fp32 rounding.
 """
