@@ -146,9 +146,10 @@ class Trainer:
         return loss.detach(), maps
 
     def capture_sparse_step(self, ids, label, warmup: int = 3):
-        """Record one sparse step (forward, backward, all-reduce, optimizer) as a CUDA graph: the step is
-        a few hundred small launches, so replaying it removes most of the host time.  The library's
-        calls are plain stream-ordered launches with caller-owned buffers, which is what capture needs."""
+        """Record one sparse step (forward, backward, optimizer) of a single-rank job as a CUDA graph: the
+        step is a few hundred small launches, so replaying it removes most of the host time.  The library's
+        calls are plain stream-ordered launches with caller-owned buffers, which is what capture needs.
+        With more than one rank the step contains the gradient all-reduce and is not captured."""
         if self.mat_lst is None:
             raise RuntimeError("capture the step after discover()")
         if dp.world_size() > 1:
