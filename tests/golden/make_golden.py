@@ -2,7 +2,9 @@
 
 Run once, in a container where the reference checkout is importable:
 
-    python tests/golden/make_golden.py /path/to/SPION
+    python tests/golden/make_golden.py /path/to/SPION [--large]
+
+(``--large`` writes only pattern_reference_large.npz: the two largest block counts, minutes of CPU time.)
 
 It imports ``main_conv_ff.flood_fill`` and ``models.attention.SoftmaxAttention`` from the
 reference and executes the reference driver's pattern lines (main_conv_ff.py:255-279)
@@ -116,6 +118,13 @@ PATTERN_CASES = [
 ]
 
 
+# largest block counts of the kernel sweep (nb = 256, 512); stored without the pooled map (mask, threshold, CSR hash)
+LARGE_CASES = [
+    ("st_L8192_bs32_q97_diag31", "st", 28, 8192, 32, 0.97, 31, "diag"),     # nb = 256
+    ("st_L16384_bs32_q99_diag31", "st", 29, 16384, 32, 0.99, 31, "diag"),   # nb = 512
+]
+
+
 def make_map(kind, seed, L):
     if kind == "qk":
         Q, K = synthetic.qkv(seed, 2, 2, L, 32, n=2)
@@ -131,6 +140,23 @@ def main(ref_root):
     import main_conv_ff                                    # the reference driver module
     from models.attention import SoftmaxAttention          # the reference dense oracle
     os.chdir(cwd)
+
+    if "--large" in sys.argv:
+        big = {}
+        for name, kind, seed, L, bs, q, Fk, ck in LARGE_CASES:
+            A = make_map(kind, seed, L)
+            mat, thresh, _ = reference_pattern(main_conv_ff.flood_fill, A, bs, q, Fk, ck)
+            sm, off, col, nnz = reference_csr(mat, bs, 1)
+            big[name + "/meta"] = np.array([seed, L, bs, Fk, 0 if ck == "diag" else 1, 0 if kind == "qk" else 1], np.int64)
+            big[name + "/q"] = np.float64(q)
+            big[name + "/sha"] = np.frombuffer(bytes.fromhex(sha(A.numpy())), dtype=np.uint8)
+            big[name + "/mat"] = np.packbits(mat)
+            big[name + "/thresh"] = thresh
+            big[name + "/csr_sha"] = np.frombuffer(bytes.fromhex(sha(np.concatenate([sm, off, col]))), dtype=np.uint8)
+            big[name + "/nnz"] = np.int64(nnz)
+            print(name, "nnzb", int(mat.sum()), "density %.4f" % (mat.mean()), "thresh", thresh)
+        np.savez_compressed(os.path.join(HERE, "pattern_reference_large.npz"), **big)
+        return
 
     pat = {}
     for name, kind, seed, L, bs, q, Fk, ck in PATTERN_CASES:
@@ -186,5 +212,5 @@ def main(ref_root):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else
+    main(sys.argv[1] if len(sys.argv) > 1 and not sys.argv[1].startswith("-") else
          os.environ.get("SPION_REFERENCE_ROOT", os.path.join(os.path.expanduser("~"), "reference")))

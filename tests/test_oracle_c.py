@@ -106,3 +106,29 @@ def test_c_attention_row_emulation_small():
     wP = np.stack([np.concatenate(rows) for rows in Pv])
     for got, want in ((O, wO), (P, wP), (dQ, wQ), (dK, wK), (dV, wV)):
         assert float(np.abs(got - want).max()) <= 5e-6
+
+
+LARGE = np.load(os.path.join(GOLD, "pattern_reference_large.npz"))
+LARGE_CASES = sorted({k.split("/")[0] for k in LARGE.files})
+
+
+@pytest.mark.parametrize("case", LARGE_CASES)
+def test_c_mask_at_the_largest_block_counts(case):
+    """nb = 256 and nb = 512 (the largest of the kernel sweep): the reference's own walkers against the C
+    restatement (and, at nb = 256, the numpy one too; at nb = 512 that one takes minutes)."""
+    A, L, bs, F, ck = _map(LARGE[case + "/meta"])
+    assert hashlib.sha256(np.ascontiguousarray(A).tobytes()).digest() == LARGE[case + "/sha"].tobytes()
+    nb = L // bs
+    gold = np.unpackbits(LARGE[case + "/mat"])[:nb * nb].reshape(nb, nb)
+    q = float(LARGE[case + "/q"])
+    mat_c, thr_c, pooled_c = c_oracle.discover(A, bs, q, F, ck)
+    assert np.array_equal(mat_c, gold)
+    # the reference's float stages sum in another order: the threshold agrees to rounding, the mask exactly
+    assert abs(float(thr_c) - float(LARGE[case + "/thresh"])) <= 2e-5 * abs(float(thr_c))
+    sm, off, col, nnz = c_oracle.element_csr(gold, bs, 1)
+    assert nnz == int(LARGE[case + "/nnz"])
+    assert hashlib.sha256(np.concatenate([sm, off, col]).tobytes()).digest() == LARGE[case + "/csr_sha"].tobytes()
+    if nb <= 256:
+        mat_n, thr_n, pooled_n = opat.discover_block_mask(A, bs, q, F, ck, float_path="fixed")
+        assert np.array_equal(pooled_c.view(np.uint32), pooled_n.view(np.uint32))
+        assert np.float32(thr_c).tobytes() == np.float32(thr_n).tobytes() and np.array_equal(mat_n, gold)
