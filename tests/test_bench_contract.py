@@ -53,3 +53,13 @@ def test_workload_tables_are_consistent():
             # measured DRAM traffic of a launch is within a small factor of the algorithmic bytes
             alg = bench.stage_bytes(stage, B * H, L, d, nnz, esz, esz, p_stored=True)
             assert 0.3 * alg < traffic < 1.5 * alg, (name, stage, traffic, alg)
+
+
+def test_reference_arm_other_ranks_exit_quietly():
+    """Under torchrun only rank 0 times the CPU path; the other ranks leave at once with status 0 and no line."""
+    env = dict(os.environ, RANK="1", WORLD_SIZE="2", LOCAL_RANK="1")
+    out = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--gpus", "2",
+                          "--workload", "tiny", "--steps", "1", "--warmup", "1"], stdout=subprocess.PIPE,
+                         stderr=subprocess.PIPE, text=True, timeout=300, env=env)
+    assert out.returncode == 0, out.stderr[-2000:]
+    assert out.stdout.strip() == ""
