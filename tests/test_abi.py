@@ -68,3 +68,32 @@ def test_create_rejects_bad_shapes_without_touching_cuda():
     assert not L.spion_create(9, 32, 128, 4, 32, _lib.F32, -1)                    # kind
     assert not L.spion_create(_lib.KIND_BLOCK, 32, 128, 4, 32, 7, -1)             # dtype
     assert not L.spion_create(_lib.KIND_BLOCK, 0, 128, 4, 32, _lib.F32, -1)
+
+
+def test_header_is_plain_c(tmp_path):
+    """The boundary is a C ABI: the public header must compile as C99 on its own, and a C translation unit that
+    takes the address of every declared entry point must link against the library."""
+    import re
+    import shutil
+    import subprocess
+    cc = shutil.which("gcc") or shutil.which("cc")
+    if cc is None:
+        pytest.skip("no C compiler")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    header = os.path.join(root, "include", "spion_b200.h")
+    r = subprocess.run([cc, "-std=c99", "-Wall", "-Wextra", "-Werror", "-fsyntax-only", "-x", "c", header],
+                       stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    assert r.returncode == 0, r.stdout
+    names = sorted(set(re.findall(r"\b(spion_[a-z0-9_]+)\s*\(", open(header).read())))
+    src = tmp_path / "link_all.c"
+    body = "\n".join(f"  p[{i}] = (void*)&{n};" for i, n in enumerate(names))
+    src.write_text('#include "spion_b200.h"\n#include <stdio.h>\nint main(void) {\n  void* p[%d];\n%s\n'
+                   '  printf("%%p\\n", p[0]);\n  return 0;\n}\n' % (len(names), body))
+    libdir = os.path.join(root, "spion_b200", "lib")
+    if not os.path.exists(os.path.join(libdir, "libspion_b200.so")):
+        pytest.skip("library not built")
+    exe = tmp_path / "link_all"
+    r = subprocess.run([cc, "-std=c99", "-I", os.path.join(root, "include"), str(src), "-o", str(exe), "-L", libdir,
+                        "-lspion_b200", "-Wl,-rpath," + libdir], stdout=subprocess.PIPE, stderr=subprocess.STDOUT,
+                       text=True)
+    assert r.returncode == 0, r.stdout
