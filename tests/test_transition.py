@@ -73,3 +73,28 @@ def test_needs_three_checks_and_latches():
     assert det.update([m + 0.2 for m in maps]) is False     # distance doubled: 100 % change, keep training dense
     assert det.update([m + 0.41 for m in maps]) is True      # distance 0.8 -> 0.84 against the refreshed map: 5 % < 15 %
     assert det.update(maps) is True                          # latched
+
+
+def test_mask_pickle_round_trip(tmp_path):
+    """The mask list travels as the reference pickles it (main_conv_ff.py:298-306): a [4, layers, nb, nb] fp32
+    tensor dumped with pickle; a file written the reference's way loads through load_mask_pickle and back."""
+    import pickle
+    import numpy as np
+    import torch
+    from oracle import pattern as opat
+    from spion_b200 import pattern, synthetic
+    mats = [synthetic.band_random_mask(1, 8, 0.3), synthetic.band_random_mask(2, 8, 0.2)]
+    mat_lst = torch.as_tensor(opat.stack_for_reference(mats))
+    assert mat_lst.shape == (4, 2, 8, 8) and mat_lst.dtype == torch.float32
+    ours = tmp_path / "mat_lst_ours.pickle"
+    pattern.save_mask_pickle(mat_lst, str(ours))
+    with open(ours, "rb") as f:                                   # readable the reference's way (main_inference.py:164-166)
+        back = pickle.load(f)
+    assert torch.equal(back, mat_lst)
+    theirs = tmp_path / "mat_lst_theirs.pickle"
+    with open(theirs, "wb") as f:                                 # written the reference's way
+        pickle.dump(mat_lst, f, pickle.HIGHEST_PROTOCOL)
+    got = pattern.load_mask_pickle(str(theirs))
+    assert torch.equal(got, mat_lst)
+    for layer in range(2):
+        assert np.array_equal(got[0][layer].numpy().astype(np.uint8), mats[layer])
