@@ -358,6 +358,95 @@ def run_pattern(args, rank, local_rank):
         "cpu_baseline": cpu, "gpu_launches": 3 * args.steps}))
 
 
+REFCUDA_WORKLOADS = {
+    # name: (B, H, L, d, bs, density) -- fp32, the reference's own layouts
+    "refcuda_config1_L1024": (8, 2, 1024, 32, 32, 0.15),
+    "refcuda_L4096_bs64_d05": (4, 2, 4096, 64, 64, 0.05),
+}
+
+
+def run_refcuda(args, rank, local_rank):
+    """The reference's own CUDA path (its four .cu files compiled unchanged for sm_100a into oracle/_ref:
+    cuSPARSE SDDMM / SpMM + its softmax kernels, models/block_attn.cu:453-545) and this library, behind the
+    same entry points (init / attn_forward / attn_backward) with the same fp32 buffers, timed back to back
+    with CUDA events.  Operand copies the reference's Python makes per call are outside the timed loop for
+    both; the zero-fill of the dP scratch, which its caller does on every backward, is inside for both."""
+    if rank != 0:
+        return
+    import ctypes
+    from spion_b200 import synthetic
+    from spion_b200.attention import Attention
+    from spion_b200.pattern import pattern_from_mask
+    B, H, L, d, bs, dens = REFCUDA_WORKLOADS[args.workload]
+    line = {"metric": "sparse-attn fwd+bwd Mtokens/s at L=%d (reference entry points, fp32)" % L, "unit": "Mtokens/s",
+            "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": args.workload, "B": B, "H": H, "L": L, "d_head": d, "block": bs}}
+    ref_path = os.path.join(ROOT, "oracle", "_ref", "block_attn.so")
+    if not os.path.exists(ref_path):
+        line.update({"value": None, "reference_cuda": {"unavailable": "oracle/_ref/block_attn.so was not built "
+                                                                       "(needs the reference checkout at build time)"}})
+        print(json.dumps(line))
+        return
+    dev = torch.device("cuda", local_rank)
+    BH = B * H
+    P = ctypes.c_void_p
+    ref = ctypes.CDLL(ref_path)
+    ref.init.argtypes = [ctypes.c_int] * 4
+    ref.init.restype = P
+    ref.attn_forward.argtypes = [P] * 9 + [ctypes.c_int]
+    ref.attn_backward.argtypes = [P] * 14 + [ctypes.c_int]
+    ref.attn_forward.restype = None
+    ref.attn_backward.restype = None
+    mine = Attention._blockcuda_compile_module()
+    Q, K, V, dO = [t.to(dev).contiguous() for t in synthetic.qkv(3, B, H, L, d)]
+    mat = synthetic.band_random_mask(77, L // bs, dens)
+    pat = pattern_from_mask(torch.as_tensor(mat).to(dev), bs)
+    sm, off, col, nnz = pat.element_csr(BH)                       # Columns repeated per (b,h), as the reference passes them
+    Kt = K.permute(0, 1, 3, 2).contiguous()
+    Vt = V.permute(0, 1, 3, 2).contiguous()
+    f32 = dict(dtype=torch.float32, device=dev)
+    attn = torch.empty(BH * nnz, **f32); out = torch.empty(BH * L * d, **f32)
+    dP = torch.zeros(BH * nnz, **f32); dS = torch.empty(BH * nnz, **f32)
+    dQ, dK, dV = [torch.empty(BH * L * d, **f32) for _ in range(3)]
+    p = lambda t: P(t.data_ptr())
+
+    def step(lib, handle):
+        lib.attn_forward(handle, p(Q), p(Kt), p(V), p(attn), p(out), p(off), p(col), p(sm), nnz)
+        dP.zero_()
+        lib.attn_backward(handle, p(Q), p(K), p(Vt), p(attn), p(dO), p(dP), p(dS), p(dQ), p(dK), p(dV),
+                          p(off), p(col), p(sm), nnz)
+
+    res, outs = {}, {}
+    for name, lib in (("reference_cuda", ref), ("spion_b200", mine)):
+        h = lib.init(d, L, BH, bs)
+        for _ in range(args.warmup):
+            step(lib, h)
+        torch.cuda.synchronize()
+        reps = []
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for _ in range(args.repeats):
+            e0.record()
+            for _ in range(args.steps):
+                step(lib, h)
+            e1.record()
+            torch.cuda.synchronize()
+            reps.append(e0.elapsed_time(e1) / args.steps)
+        ms = statistics.median(reps)
+        res[name] = {"ms_per_step": ms, "min_ms": min(reps), "max_ms": max(reps), "Mtokens_per_s": B * L / (ms * 1e-3) / 1e6}
+        outs[name] = [t.clone() for t in (out, dQ, dK, dV)]
+        if lib is mine:
+            lib.destroy(h)
+    diff = max(float((a - b).abs().max()) for a, b in zip(outs["reference_cuda"], outs["spion_b200"]))
+    line.update({"value": res["spion_b200"]["Mtokens_per_s"], "ms_per_step": res["spion_b200"]["ms_per_step"],
+                 "reference_cuda": res["reference_cuda"], "spion_b200": res["spion_b200"],
+                 "speedup_over_reference_cuda": res["reference_cuda"]["ms_per_step"] / res["spion_b200"]["ms_per_step"],
+                 "max_abs_difference_of_outputs_and_gradients": diff})
+    line["config"]["density"] = float(mat.mean())
+    line["config"]["l2_policy"] = "working set %.0f MB" % ((4 * Q.numel() * 4 + 3 * attn.numel() * 4) / 1e6)
+    print(json.dumps(line))
+
+
 def run_sweep_table(args, rank, world, local_rank):
     """Benchmark config 4 in full: L x block x density grid (B=8, H=8, d=64, bf16), fwd+bwd of one layer through
     the C ABI with inputs resident in HBM, CUDA events; one JSON line whose "sweep" key holds the table.  Every
@@ -425,16 +514,18 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="sweep_L4096_bs64_d05",
-                    choices=sorted(WORKLOADS) + sorted(TRAIN_WORKLOADS) +
+                    choices=sorted(WORKLOADS) + sorted(TRAIN_WORKLOADS) + sorted(REFCUDA_WORKLOADS) +
                     ["pattern_L4096_bs64", "pattern_L1024_bs32", "sweep_table"])
     ap.add_argument("--engine", default="auto", choices=["auto", "simt", "tcgen05", "staged"])
     ap.add_argument("--mode", default="auto", choices=["auto", "fused", "staged"],
                     help="fused: S/P/dP/dS stay on chip (tcgen05 engine); staged: one kernel per stage")
+    ap.add_argument("--repeats", type=int, default=5, help="how often the timed loop of --steps steps is repeated")
     ap.add_argument("--no-graph", action="store_true", help="training workloads: launch the step eagerly")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-clocks", action="store_true", help="do not sample nvidia-smi (profiler runs)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    args.repeats = max(args.repeats, 1)
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -462,6 +553,9 @@ def main():
         return
     if args.workload == "sweep_table":
         run_sweep_table(args, rank, world, local_rank)
+        return
+    if args.workload in REFCUDA_WORKLOADS:
+        run_refcuda(args, rank, local_rank)
         return
 
     B, H, L, d, bs, dens, dt = WORKLOADS[args.workload]
@@ -528,15 +622,20 @@ def main():
     barrier()
     l0 = mod.launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        step_device()
-    e1.record()
-    barrier()
+    # the timed loop of `steps` steps is repeated; the line reports the median repeat and the spread
+    rep_ms = []
+    for _ in range(args.repeats):
+        barrier()
+        e0.record()
+        for _ in range(args.steps):
+            step_device()
+        e1.record()
+        barrier()
+        rep_ms.append(max_over_ranks(e0.elapsed_time(e1)) / args.steps)
     launches = mod.launch_count() - l0
-    ms_total = max_over_ranks(e0.elapsed_time(e1))
     clocks = sampler.stop() if rank == 0 else None
-    ms_step = ms_total / args.steps
+    ms_step = statistics.median(rep_ms)
+    spread = {"repeats": args.repeats, "min_ms": min(rep_ms), "max_ms": max(rep_ms), "median_ms": ms_step}
     value = world * B * L / (ms_step * 1e-3) / 1e6
 
     # ---------------- per-kernel times, live, CUDA events on the launch stream -----------------
@@ -612,27 +711,50 @@ def main():
         for st in (s_in, s_cmp, s_out):
             main_stream.wait_stream(st)
 
+    def timed(fn_step, n):
+        """n calls of fn_step(i) on the three streams between two events on the main stream; ms per call, max over ranks"""
+        barrier()
+        for st in (s_in, s_cmp, s_out):
+            st.wait_stream(main_stream)
+        e0.record()
+        for st in (s_in, s_cmp, s_out):
+            st.wait_stream(main_stream)
+        for i in range(n):
+            fn_step(i)
+        e2e_sync()
+        e1.record()
+        barrier()
+        return max_over_ranks(e0.elapsed_time(e1)) / n
+
     for st in (s_in, s_cmp, s_out):
         st.wait_stream(main_stream)
     for i in range(4):
         step_e2e(i)
     e2e_sync()
-    barrier()
-    for st in (s_in, s_cmp, s_out):
-        st.wait_stream(main_stream)
-    e0.record()
-    for st in (s_in, s_cmp, s_out):
-        st.wait_stream(main_stream)
-    for i in range(args.steps):
-        step_e2e(i)
-    e2e_sync()
-    e1.record()
-    barrier()
-    e2e_ms = max_over_ranks(e0.elapsed_time(e1)) / args.steps
+    e2e_steps = min(args.steps, 100)
+    e2e_rep = [timed(step_e2e, e2e_steps) for _ in range(min(args.repeats, 3))]
+    e2e_ms = statistics.median(e2e_rep)
     h2d = 4 * hQ.numel() * esz
     d2h = 4 * hQ.numel() * esz
+
+    # The same copies with no compute between them (every rank at once): what the host <-> device path
+    # alone allows for this step's bytes, to read the e2e figure against.
+    def step_copies(i):
+        b = i & 1
+        with torch.cuda.stream(s_in):
+            for dst, src in zip(dbuf[b], (hQ, hK, hV, hdO)):
+                dst.copy_(src, non_blocking=True)
+        with torch.cuda.stream(s_out):
+            for dst, src in zip((hO, hdQ, hdK, hdV), dbuf[b ^ 1]):
+                dst.copy_(src, non_blocking=True)
+
+    copy_ms = timed(step_copies, min(e2e_steps, 50))
     e2e = {"value": world * B * L / (e2e_ms * 1e-3) / 1e6, "unit": "Mtokens/s", "ms_per_step": e2e_ms,
-           "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+           "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
+           "spread": {"repeats": len(e2e_rep), "min_ms": min(e2e_rep), "max_ms": max(e2e_rep)},
+           "host_copy_ceiling": {"ms_per_step": copy_ms, "value": world * B * L / (copy_ms * 1e-3) / 1e6,
+                                 "unit": "Mtokens/s", "GBps_each_way_per_rank": h2d / (copy_ms * 1e-3) / 1e9,
+                                 "note": "the step's pinned H2D and D2H copies alone, both directions at once, all ranks together"},
            "note": "public module (autograd); copies of step i+1 / i-1 overlap the compute of step i on separate streams"}
     mod.check_device_status()
 
@@ -663,7 +785,7 @@ def main():
         line = {
             "metric": "sparse-attn fwd+bwd Mtokens/s at L=%d" % L, "value": value, "unit": "Mtokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "spread": spread,
             "dtype": "bf16" if dt == "bf16" else "f32", "data": "synthetic",
             "config": {"workload": args.workload, "B_per_gpu": B, "H": H, "L": L, "d_head": d, "block": bs,
                        "density": nnzb / float(nb * nb), "nnzb": nnzb, "engine": args.engine,

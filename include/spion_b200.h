@@ -75,9 +75,14 @@ int spion_set_engine(spion_ctx* ctx, int engine);
  * bounded wait inside a kernel gave up; the word is cleared. */
 int spion_check_device_status(spion_ctx* ctx);
 
-/* Debugging aid: the fused kernels write 8 nanosecond timestamps (%globaltimer) per CTA, at their
- * phase boundaries, into this device buffer (8 * grid size uint64; NULL switches it off). */
-int spion_set_trace_buffer(spion_ctx* ctx, void* device_buffer);
+/* Operand layout of the native (_ex / _fused) calls on the tcgen05 engine.
+ *   heads == 0 (default): Q, K, V, O, dO, dQ, dK, dV are [BH, L, d], one matrix per (b,h) pair.
+ *   heads == H > 0: they are [B, L, H, d] (B = num_batches / H), i.e. the [B, L, H*d] tensor a linear
+ *   projection writes, read in place through a 2-D tensor map with a [64, d] box at column h*d.  This
+ *   removes the head split / merge copies of models/attention.py:84-96,131-139 and the per-call
+ *   flatten / permute copies of models/attention_blockcuda.py:47-49,78-80.  P, dS, lse and keypad keep
+ *   their (b*H + h)-major layouts.  UNSUPPORTED on contexts the tcgen05 engine cannot run. */
+int spion_set_head_layout(spion_ctx* ctx, int heads);
 
 /* Failure-path self-test that faults nothing: launches one CTA that waits, with the given limit
  * in clock cycles (at most 2e9), on a barrier nobody arrives on.  The kernel gives up, records the
@@ -104,7 +109,7 @@ enum {
   SPION_STAGE_SPMM_DQ = 6,     /* dQ = dS K                                        */
   SPION_STAGE_SPMM_DK = 7,     /* dK = dS^T Q                                      */
   SPION_STAGE_SPMM_DV = 8,     /* dV = P^T dO                                      */
-  SPION_STAGE_FUSED_DP_DS = 9, /* tcgen05: dP tiles + softmax backward -> dS (split row kernel) */
+  SPION_STAGE_FUSED_DP_DS = 9, /* (unused; kept so that the stage numbers stay stable)      */
   SPION_STAGE_SPMM_DKDV = 10,  /* fused kernels: dK and dV in one kernel           */
   SPION_STAGE_FUSED_FWD = 11,  /* fused kernels: S, softmax, P V in one kernel     */
   SPION_STAGE_BWD_ROW = 12,    /* fused kernels: dP, dS and dQ per block row (P read, dS written) */
@@ -135,6 +140,14 @@ int spion_block_attn_backward(spion_ctx* ctx, const float* Q, const float* K, co
                               const float* P, const float* dO, float* dP_scratch, float* dS_scratch,
                               float* dQ, float* dK, float* dV,
                               const int* offsets, const int* columns, const int* sum_mat, int nnz);
+
+/* No counterpart in the reference.  stable != 0: the caller promises that the (offsets, columns,
+ * sum_mat) arrays it passes to the two calls above stay allocated and unchanged for as long as it
+ * passes them (a cache per mask, as spion_b200/attention_blockcuda.py keeps).  The block structure is
+ * then rebuilt only when one of the three pointers or nnz changes, instead of on every forward and
+ * every backward.  Default 0: the reference's own Python builds fresh arrays per call, whose
+ * addresses are recycled and identify nothing. */
+int spion_csr_arrays_are_stable(spion_ctx* ctx, int stable);
 
 /* ------------------------------------------- reference-layout dense attention ---- */
 
@@ -260,7 +273,9 @@ int spion_softmax_backward_ex(spion_ctx* ctx, const float* dP, const void* P, vo
  * held by every GPU that loads the library).  num_batches*nnzb*block_size^2 beyond that is
  * refused with SPION_ERR_SHAPE.  The array is shared by all calls on a device: calls that overlap
  * on the GPU race.  The first call on each device looks up the array's address; make it outside
- * stream capture.  row_ptr [nb+1], col_idx [nnzb], blk_row [nnzb]: block CSR (device). */
+ * stream capture (the address is kept per device and does not survive a device reset).
+ * row_ptr [nb+1], col_idx [nnzb], blk_row [nnzb]: block CSR (device); nnzb must be that CSR's own
+ * block count (row_ptr[nb] == nnzb; nnzb > nb*nb is refused), because the capacity check uses it. */
 size_t spion_static_scratch_capacity(void);
 int spion_attn_forward_static(const void* Q, const void* K, const void* V, const float* keypad,
                               void* P, void* O, const int32_t* row_ptr, const int32_t* col_idx,

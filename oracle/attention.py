@@ -111,6 +111,54 @@ def sparse_attention_rowwise(Q, K, V, mat, bs: int, keypad=None, dO=None, floor=
     return Pvals, O, dQ, dK, dV
 
 
+def sparse_attention_blockwise(Q, K, V, mat, bs: int, keypad=None, dO=None, floor=None):
+    """The same semantics block row by block row in numpy fp64, for ONE (b,h) matrix: Q, K, V, dO are
+    [L, d]; keypad [L] of 1 (keep) / 0 (pad) or None.  Never forms an [L, L] array, so it reaches the
+    largest sequence lengths of the kernel sweep (L = 16384, nb = 512) in seconds.  Follows
+    models/block_attn.cu:33-130 per row (maximum with floor, the (L - n) exp(-m) term, backward through
+    the selected entries only) and :453-545 for the products.
+
+    Returns (O, P_tiles[, dQ, dK, dV]) with P_tiles [nnzb, bs, bs] in CSR block order.
+    """
+    Q = np.asarray(Q, np.float64); K = np.asarray(K, np.float64); V = np.asarray(V, np.float64)
+    L, d = Q.shape
+    nb = L // bs
+    scale = 1.0 / math.sqrt(d)
+    if floor is None:
+        floor = -100.0 if keypad is None else 0.0
+    mat = np.asarray(mat) != 0
+    g = None if dO is None else np.asarray(dO, np.float64)
+    kp = None if keypad is None else np.asarray(keypad, np.float64)
+    O = np.zeros((L, d)); dQ = np.zeros((L, d)); dK = np.zeros((L, d)); dV = np.zeros((L, d))
+    tiles = []
+    for r in range(nb):
+        cs = np.nonzero(mat[r])[0]
+        rows = slice(r * bs, (r + 1) * bs)
+        if cs.size == 0:
+            continue
+        cols = (cs[:, None] * bs + np.arange(bs)[None, :]).reshape(-1)
+        v = (Q[rows] @ K[cols].T) * scale                                  # [bs, n]
+        if kp is not None:
+            v = v - 1e6 * (1.0 - kp[cols])[None, :]
+        m = np.maximum(floor, v.max(axis=1, keepdims=True))
+        e = np.exp(v - m)
+        Z = e.sum(axis=1, keepdims=True) + (L - cols.size) * np.exp(-m)
+        p = e / Z
+        tiles.append(p.reshape(bs, cs.size, bs).transpose(1, 0, 2))
+        O[rows] = p @ V[cols]
+        if g is not None:
+            dP = g[rows] @ V[cols].T
+            t = dP * p
+            dS = (t - p * t.sum(axis=1, keepdims=True)) * scale
+            dQ[rows] = dS @ K[cols]
+            dK[cols] += dS.T @ Q[rows]
+            dV[cols] += p.T @ g[rows]
+    P_tiles = np.concatenate(tiles, 0) if tiles else np.zeros((0, bs, bs))
+    if g is None:
+        return O, P_tiles
+    return O, P_tiles, dQ, dK, dV
+
+
 def csr_values_from_dense(P_dense, mat, bs: int) -> np.ndarray:
     """Gather a dense [B,H,L,L] tensor into the reference's value layout [BH, nnz]
     (element rows in order, selected element columns ascending; attention_blockcuda.py:51,67)."""

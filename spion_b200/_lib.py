@@ -29,7 +29,8 @@ SIGNATURES = {
     "spion_set_engine": (c_int, [c_void_p, c_int]),
     "spion_needs_scratch": (c_int, [c_void_p]),
     "spion_check_device_status": (c_int, [c_void_p]),
-    "spion_set_trace_buffer": (c_int, [c_void_p, c_void_p]),
+    "spion_set_head_layout": (c_int, [c_void_p, c_int]),
+    "spion_csr_arrays_are_stable": (c_int, [c_void_p, c_int]),
     "spion_selftest_bounded_wait": (c_int, [c_void_p, c_longlong]),
     "spion_launch_count": (c_longlong, [c_void_p]),
     "spion_profile": (c_int, [c_void_p, c_int]),
@@ -81,6 +82,22 @@ lib = _load()
 def check(rc: int, what: str = "spion_b200 call") -> None:
     if rc != 0:
         raise SpionError(f"{what} failed: {lib.spion_status_string(rc).decode()} ({rc})")
+
+
+def check_operands(want_shape, **tensors) -> None:
+    """The native calls take every size from the context they were created with, never from the
+    tensors: operands of another shape (a short last batch, an evaluation batch) or on another device
+    would make the kernels read and write past the buffers, so they are refused here."""
+    dev = None
+    for name, t in tensors.items():
+        if tuple(t.shape) != tuple(want_shape):
+            raise SpionError(f"{name} has shape {tuple(t.shape)}; the attention context was created for "
+                             f"{tuple(want_shape)} (batch_size, num_head, max_seq_len, head_dim of its config)")
+        if not t.is_cuda:
+            raise SpionError(f"{name} is not a CUDA tensor (there is no CPU path)")
+        if dev is not None and t.device != dev:
+            raise SpionError(f"{name} is on {t.device}, other operands are on {dev}")
+        dev = t.device
 
 
 def ptr(t):

@@ -24,19 +24,24 @@ from .pattern import pattern_from_mask
 
 
 class _CsrCache:
-    """Element CSR of the most recent mask tensor (keyed on storage pointer and version)."""
+    """Element CSR of the most recent mask tensor, keyed on storage pointer and version.  The keyed
+    tensor is kept alive, so its address cannot be given to a different mask while the key is in use."""
 
-    def __init__(self, block_size: int):
+    def __init__(self, block_size: int, on_new=None):
         self.block_size = block_size
         self.key = None
+        self.ref = None
         self.value = None
+        self.on_new = on_new          # called whenever new arrays replace the cached ones
 
     def get(self, mat: torch.Tensor):
         key = (mat.data_ptr(), mat._version, tuple(mat.shape), str(mat.device))
         if key != self.key:
             pat = pattern_from_mask(mat, self.block_size)
             sum_mat, offsets, columns, nnz = pat.element_csr(1)
-            self.key, self.value = key, (sum_mat, offsets, columns, nnz)
+            self.key, self.ref, self.value = key, mat, (sum_mat, offsets, columns, nnz)
+            if self.on_new is not None:
+                self.on_new()
         return self.value
 
 
@@ -53,12 +58,16 @@ def make_block_function(config, attn_cpp, attn_handle, with_keypad: bool):
     batch_size = config["batch_size"]
     block_size = config["block_size"]
     num_batches = batch_size * num_heads
-    cache = _CsrCache(block_size)
     handle = _lib.c_void_p(attn_handle) if not isinstance(attn_handle, _lib.c_void_p) else attn_handle
+    # The cache keeps the element-CSR arrays of the current mask alive and unchanged, so the library may
+    # keep the block structure it derived from them; new arrays (a new mask) may reuse the old addresses,
+    # so the library is told to forget what it has each time the cache is refilled.
+    cache = _CsrCache(block_size, on_new=lambda: lib.spion_csr_arrays_are_stable(handle, 1))
 
     class BlockAttnFunction(torch.autograd.Function):
         @staticmethod
         def forward(ctx, query, key, value, mask, mat):
+            _lib.check_operands((batch_size, num_heads, seq_len, emb_dim), query=query, key=key, value=value)
             sum_mat, offsets, columns, nnz = cache.get(mat)
             dev = query.device
             lib.spion_set_stream(handle, _lib.current_stream_ptr())

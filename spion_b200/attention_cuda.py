@@ -26,6 +26,7 @@ def make_dense_function(config, attn_cpp, attn_handle, with_keypad: bool):
     class AttnFunction(torch.autograd.Function):
         @staticmethod
         def forward(ctx, query, key, value, mask):
+            _lib.check_operands((batch_size, num_heads, seq_len, emb_dim), query=query, key=key, value=value)
             dev = query.device
             f32 = dict(dtype=torch.float32, device=dev)
             lib.spion_set_stream(handle, _lib.current_stream_ptr())

@@ -74,7 +74,8 @@ extern "C" spion_ctx* spion_create(int kind, int head_dim, int seq_len, int num_
   c->nnzb = -1;
   c->launches = 0;
   c->tc = nullptr;
-  c->trace = nullptr;
+  c->heads = 0;
+  c->csr_stable = 0; c->csr_key[0] = c->csr_key[1] = c->csr_key[2] = nullptr; c->csr_nnz = -1;
   c->prof_on = 0; c->prof_n = 0;
   for (int i = 0; i < SPION_PROF_MAX_MARKS; ++i) { c->prof_ev[i] = nullptr; c->prof_stage[i] = -1; }
   for (int i = 0; i < SPION_STAGE_COUNT; ++i) { c->prof_ms[i] = 0; c->prof_cnt[i] = 0; }
@@ -112,6 +113,7 @@ extern "C" int spion_set_stream(spion_ctx* c, void* cuda_stream) {
 extern "C" int spion_set_engine(spion_ctx* c, int engine) {
   if (!c || engine < SPION_ENGINE_AUTO || engine > SPION_ENGINE_SIMT_STAGED) return SPION_ERR_ARG;
   if (engine == SPION_ENGINE_TCGEN05 && !tc_engine_supports(c)) return SPION_ERR_UNSUPPORTED;
+  if ((engine == SPION_ENGINE_SIMT || engine == SPION_ENGINE_SIMT_STAGED) && c->heads != 0) return SPION_ERR_UNSUPPORTED;
   c->engine = engine;
   return SPION_OK;
 }
@@ -129,9 +131,21 @@ extern "C" int spion_check_device_status(spion_ctx* c) {
   return SPION_OK;
 }
 
-extern "C" int spion_set_trace_buffer(spion_ctx* c, void* device_buffer) {
+extern "C" int spion_csr_arrays_are_stable(spion_ctx* c, int stable) {
   if (!c) return SPION_ERR_ARG;
-  c->trace = device_buffer;
+  c->csr_stable = stable != 0;
+  c->csr_key[0] = c->csr_key[1] = c->csr_key[2] = nullptr;
+  c->csr_nnz = -1;
+  return SPION_OK;
+}
+
+extern "C" int spion_set_head_layout(spion_ctx* c, int heads) {
+  if (!c || heads < 0) return SPION_ERR_ARG;
+  if (heads > 0) {
+    if (is_dense(c) || !tc_engine_supports(c)) return SPION_ERR_UNSUPPORTED;   // the SIMT kernels address [BH, L, d] only
+    if (c->BH % heads != 0) return SPION_ERR_SHAPE;
+  }
+  c->heads = heads;
   return SPION_OK;
 }
 
@@ -215,10 +229,21 @@ static bool use_simt_fused(const spion_ctx* c, int value_mode) {
 }
 
 // ============================================================ reference-layout sparse
+// The block structure is derived from the caller's element CSR on every call: the reference's Python
+// rebuilds those arrays for each forward (models/attention_blockcuda.py:26-43), usually into recycled
+// allocations, so their addresses say nothing about their contents.  A caller that keeps the arrays
+// alive and unchanged for as long as it passes them (spion_csr_arrays_are_stable) skips the rebuild
+// when the same three pointers and nnz come back.
 static int legacy_structure(spion_ctx* c, const int* offsets, const int* columns, const int* sum_mat, int nnz) {
   if (nnz < 0 || nnz % (c->bs * c->bs) != 0) return SPION_ERR_SHAPE;
   const int nnzb = nnz / (c->bs * c->bs);
   if (nnzb > c->nb * c->nb) return SPION_ERR_SHAPE;
+  if (c->csr_stable && c->csr_key[0] == offsets && c->csr_key[1] == columns && c->csr_key[2] == sum_mat &&
+      c->csr_nnz == nnz && c->nnzb == nnzb) {
+    prof_mark(c, -1);
+    return SPION_OK;
+  }
+  c->csr_key[0] = offsets; c->csr_key[1] = columns; c->csr_key[2] = sum_mat; c->csr_nnz = nnz;
   prof_mark(c, -1);
   int rc = spion_launch_mat_from_elemcsr(offsets, columns, sum_mat, c->nb, c->bs, c->mat, c->stream);
   if (rc) return rc;
@@ -385,6 +410,7 @@ extern "C" int spion_attn_forward_ex(spion_ctx* c, const void* Q, const void* K,
   if (is_dense(c) || c->nnzb < 0) return SPION_ERR_STATE;
   DeviceGuard guard(c->device);
   if (use_tc(c)) return tc_engine_forward(c, Q, K, V, keypad, P, O, S_scratch);
+  if (c->heads != 0) return SPION_ERR_UNSUPPORTED;
   const Pattern p = ctx_pattern(c);
   const long long nnz = (long long)c->nnzb * c->bs * c->bs;
   const ValueLayout vl{VAL_BLOCKTILE, c->L, nnz};
@@ -423,6 +449,7 @@ extern "C" int spion_attn_backward_ex(spion_ctx* c, const void* Q, const void* K
     (void)delta;
     return tc_engine_backward(c, Q, K, V, P, O, dO, dS, dP_scratch, dQ, dK, dV);
   }
+  if (c->heads != 0) return SPION_ERR_UNSUPPORTED;
   const Pattern p = ctx_pattern(c);
   const long long nnz = (long long)c->nnzb * c->bs * c->bs;
   const ValueLayout vl{VAL_BLOCKTILE, c->L, nnz};

@@ -72,15 +72,18 @@ __device__ __forceinline__ void tile_address(const ValueLayout& vl, const Patter
 // Context (host side).
 struct spion_ctx {
   int kind, d, L, BH, bs, nb, dtype, device, engine;
+  int heads;                // 0: operands [BH, L, d]; H > 0: operands [B, L, H, d] (tensor-core engine only)
   float scale;
   cudaStream_t stream;
   // structure workspace (device), capacity nb*nb blocks
   uint8_t* mat;
   int32_t *row_ptr, *col_idx, *blk_row, *col_ptr, *row_idx, *csc_pos, *work, *nnzb_dev;
   int nnzb;                 // block count of the current pattern (host copy), -1 if none
+  int csr_stable;           // reference-layout calls: the caller keeps its element-CSR arrays alive and unchanged
+  const void* csr_key[3];   // ... and these are the arrays the current structure was built from
+  int csr_nnz;
   int* status_dev;          // device status word written by bounded waits
   long long launches;
-  void* trace;              // optional device buffer for per-CTA phase timestamps (debugging aid)
   void* tc;                 // tensor-core engine state (tensor maps, ...), owned by tc_engine.cu
   // per-stage timing (off by default): events recorded between the kernels of a pipeline
   int prof_on;

@@ -280,11 +280,10 @@ extern "C" int spion_discover_pattern(const float* A, int L, int block_size, int
 
   const int T = bs + F - 1;
   size_t smem = (((size_t)T * T * sizeof(float) + 15) & ~(size_t)15) + ((size_t)bs * bs + bs) * sizeof(double);
-  static size_t smem_opted = 0;
-  if (smem > 48 * 1024 && smem > smem_opted) {
+  // The opt-in above 48 KB belongs to the current device only (a process may drive several), and the
+  // call is cheap: make it on every launch that needs it instead of remembering one process-wide size.
+  if (smem > 48 * 1024)
     SPION_CUDA_TRY(cudaFuncSetAttribute(conv_pool_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    smem_opted = smem;
-  }
   conv_pool_kernel<<<dim3(nb, nb), 256, smem, st>>>(A, L, bs, conv_kind, F, pooled);
   SPION_LAUNCH_CHECK();
 

@@ -17,7 +17,11 @@
 //     cleared; but two calls that overlap on the GPU (different streams, or different host threads)
 //     race on it -- serialise them;
 //   * the first call on each device looks up the array's device address (cudaGetSymbolAddress);
-//     make that first call outside any stream capture.
+//     make that first call outside any stream capture.  The address is remembered per device
+//     ordinal for the life of the process (concurrent first calls from several host threads store
+//     the same value); it does not survive a cudaDeviceReset of that device;
+//   * nnzb must be the block count of the CSR that is passed (row_ptr[nb] == nnzb, nnzb <= nb^2): the
+//     capacity check is made on nnzb, the kernels index the array by the block ids row_ptr yields.
 // The entry point calls no cudaMalloc / cudaFree / allocating library routine.
 #include "common.cuh"
 
@@ -58,6 +62,9 @@ extern "C" int spion_attn_forward_static(const void* Q, const void* K, const voi
   if (dtype != SPION_F32 && dtype != SPION_BF16) return SPION_ERR_ARG;
   if (head_dim < 1 || seq_len < 1 || num_batches < 1 || block_size < 1 || nnzb < 0) return SPION_ERR_ARG;
   if (seq_len % block_size != 0 || seq_len / block_size > SPION_MAX_NB) return SPION_ERR_SHAPE;
+  // The kernels walk the device row_ptr and index the scratch by block id, so the count the capacity
+  // check uses must be the CSR's own: row_ptr[nb] == nnzb is the caller's contract, nnzb <= nb^2 is checked.
+  if ((long long)nnzb > (long long)(seq_len / block_size) * (seq_len / block_size)) return SPION_ERR_SHAPE;
   const unsigned long long need = (unsigned long long)num_batches * (unsigned long long)nnzb * block_size * block_size;
   if (need > (unsigned long long)SPION_STATIC_SCRATCH_FLOATS) {
     fprintf(stderr,

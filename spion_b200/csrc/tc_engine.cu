@@ -5,8 +5,7 @@
 // kernels (models/block_attn.cu:453-545):
 //   k_fwd_fused (tc_fused.cu)  S = Q K^T on the mask, sparse row softmax, O = P V        (:459-478)
 //   k_bwd_row                  dP = dO V^T on the mask, softmax backward -> dS, dQ = dS K  (:498-516)
-//   k_dp_ds + k_spmm<false>    the same two steps as separate kernels (debugging switch)
-//   k_spmm<true>               dK = dS^T Q and dV = P^T dO in one pass over a block column (:526, :536)
+//   k_bwd_col                  dK = dS^T Q and dV = P^T dO in one pass over a block column (:526, :536)
 // Masks with 32-wide blocks run on derived 64-wide super-blocks whose unselected quarters are
 // masked inside the forward softmax (P = 0 there, so the backward needs no special handling).
 //
@@ -17,6 +16,10 @@
 // products need no transposed copies: P/dS tiles and Q/K/V/dO tiles are read as MN-major operands.
 // The softmax backward uses  sum_j dP_ij P_ij = sum_n dO_in O_in  (delta), so every dS tile is
 // independent of the others and no second pass over the row is needed.
+//
+// All three kernels are persistent: the grid is the number of CTAs the device holds at once, every
+// CTA initialises its barriers and allocates its tensor memory once and then walks its share of the
+// work units, asking for the next unit's tiles while the current unit's results are written.
 //
 // All waits on mbarriers are bounded; on a time-out the CTA records a code in the context's
 // status word, frees its TMEM and returns.
@@ -29,185 +32,33 @@ using namespace tc;
 
 namespace {
 
-// =====================================================================================
-// dP tiles of one block row + softmax backward -> dS (used when the row kernel below is split):
-// 4 warps (one per TMEM quadrant), two tiles per 64 columns (lane halves 0-15 / 16-31) so every
-// lane owns a row, operands requested before TMEM is set up, P tiles brought in by TMA and the
-// dS tiles written over them in shared memory and sent out by TMA stores (full-line writes).
-template <int D>
-__global__ void __launch_bounds__(128) k_dp_ds(const __grid_constant__ CUtensorMap tmdO,
-                                               const __grid_constant__ CUtensorMap tmV,
-                                               const __grid_constant__ CUtensorMap tmP,
-                                               const __grid_constant__ CUtensorMap tmdS,
-                                               const __nv_bfloat16* __restrict__ dOg,
-                                               const __nv_bfloat16* __restrict__ Og,
-                                               const int4* __restrict__ row_info, const int* __restrict__ col_idx,
-                                               int L, int nnzb, float scale, int* status) {
-  using T = OpTile<D>;
-  constexpr int NCH = 4;
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t raw = smem_u32(smem_raw);
-  const uint32_t sbase = (raw + 1023u) & ~1023u;
-  const uint32_t sA = sbase;                                   // dO tile
-  const uint32_t sB = sA + T::BYTES;                           // V tiles
-  const uint32_t sP = sB + NCH * T::BYTES;                     // P tiles in, dS tiles out
-  const uint32_t bars = sP + NCH * VT_BYTES;
-  const uint32_t bar_k = bars, bar_p = bars + 8, bar_s = bars + 16, slot = bars + 24;
-  uint32_t* slot_ptr = reinterpret_cast<uint32_t*>(smem_raw + (slot - raw));
-  __shared__ int s_abort;
-
-  const int bh = blockIdx.y;
-  const int tid = threadIdx.x, q = tid >> 5, lane = tid & 31;
-  const int hf = lane >> 4;
-  const int row = q * 16 + (lane & 15);
-  const int4 ri = row_info[blockIdx.x];                        // records are sorted, longest row first
-  const int rp = ri.x, nblk = ri.y & 0xffff, r = ri.y >> 16;
-  auto col_of = [&](int t) -> int {                            // block column of the row's t-th block
-    return t < 4 ? ((t & 2 ? ri.w : ri.z) >> ((t & 1) * 16)) & 0xffff : col_idx[rp + t];
-  };
-  const int nchunks = (nblk + NCH - 1) / NCH;
-  bool a_loaded = false;
-
-  auto issue_loads = [&](int ch) {                             // all lanes of warp 0: one copy per lane
-    const int t0 = ch * NCH, nt = min(NCH, nblk - t0);
-    if (lane == 0) {
-      mbar_expect_tx(bar_k, (a_loaded ? 0 : T::BYTES) + nt * T::BYTES);
-      mbar_expect_tx(bar_p, nt * VT_BYTES);
-    }
-    __syncwarp();
-    if (lane == 0 && !a_loaded) tma_load_2d(sA, &tmdO, bar_k, 0, bh * L + r * BS);
-    if (lane >= 1 && lane <= nt) tma_load_2d(sB + (lane - 1) * T::BYTES, &tmV, bar_k, 0, bh * L + col_of(t0 + lane - 1) * BS);
-    if (lane >= 9 && lane < 9 + nt)
-      tma_load_2d(sP + (lane - 9) * VT_BYTES, &tmP, bar_p, 0, (int)(((size_t)bh * nnzb + rp + t0 + lane - 9) * BS));
-  };
-
-  if (q == 0) {
-    if (lane == 0) {
-      s_abort = *reinterpret_cast<volatile int*>(status);
-      mbar_init(bar_k, 1);
-      mbar_init(bar_p, 1);
-      mbar_init(bar_s, 1);
-      fence_barrier_init();
-    }
-    __syncwarp();
-    if (s_abort == 0 && nblk > 0) issue_loads(0);
-  }
-  a_loaded = true;
-  __syncthreads();
-  if (s_abort != 0) return;
-  if (q == 0) {
-    tmem_alloc(slot, 128);
-    tmem_relinquish();
-  }
-  // delta_i = sum_n dO_in O_in: the two owners of a row take one half of the head dimension each
-  float delta;
-  {
-    const size_t off = ((size_t)bh * L + r * BS + row) * D + hf * (D / 2);
-    const uint4* a4 = reinterpret_cast<const uint4*>(dOg + off);
-    const uint4* b4 = reinterpret_cast<const uint4*>(Og + off);
-    float acc = 0.f;
-#pragma unroll
-    for (int u = 0; u < D / 16; ++u) {
-      const uint4 a = a4[u], b = b4[u];
-      acc += bf16_lo(a.x) * bf16_lo(b.x) + bf16_hi(a.x) * bf16_hi(b.x) + bf16_lo(a.y) * bf16_lo(b.y) +
-             bf16_hi(a.y) * bf16_hi(b.y) + bf16_lo(a.z) * bf16_lo(b.z) + bf16_hi(a.z) * bf16_hi(b.z) +
-             bf16_lo(a.w) * bf16_lo(b.w) + bf16_hi(a.w) * bf16_hi(b.w);
-    }
-    delta = acc + __shfl_xor_sync(0xffffffffu, acc, 16);
-  }
-  const float nds = -delta * scale;
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = *slot_ptr;
-  const uint32_t t_lane = tmem + ((uint32_t)(q * 32) << 16);
-  constexpr uint32_t IDESC = make_idesc_bf16(64, 64, 0, 0);
-  uint32_t ph_k = 0, ph_p = 0, ph_s = 0;
-  bool ok = true;
-
-  for (int ch = 0; ch < nchunks && ok; ++ch) {
-    const int t0 = ch * NCH, nt = min(NCH, nblk - t0);
-    if (ch > 0 && q == 0) {
-      if (lane == 0) bulk_wait_read_all();                     // the previous dS tiles have left shared memory
-      __syncwarp();
-      issue_loads(ch);
-    }
-    if (!__syncthreads_and(mbar_wait(bar_k, ph_k))) { if (tid == 0) report(status, ERR_LOAD_WAIT); ok = false; break; }
-    ph_k ^= 1;
-    if (tid == 0) {
-      tc_fence_after();
-      for (int t = 0; t < nt; ++t) {
-        const uint32_t d_addr = tmem + ((uint32_t)((t & 1) * 16) << 16) + (t >> 1) * 64;
-#pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk)
-          mma_bf16(d_addr, T::kmajor(sA, kk), T::kmajor(sB + t * T::BYTES, kk), IDESC, kk > 0);
-      }
-      mma_commit(bar_s);
-    }
-    const bool w1 = mbar_wait(bar_s, ph_s);
-    const bool w2 = mbar_wait(bar_p, ph_p);
-    if (!__syncthreads_and(w1 && w2)) { if (tid == 0) report(status, ERR_MMA_WAIT); ok = false; break; }
-    ph_s ^= 1; ph_p ^= 1;
-    tc_fence_after();
-    for (int p = 0; p < 2; ++p) {
-      const int t = 2 * p + hf;
-      const bool mine = t < nt;
-      const uint32_t tile = sP + t * VT_BYTES;
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        uint32_t v[32];
-        tmem_ld32(t_lane + p * 64 + half * 32, v);
-        tmem_ld_wait();
-        if (mine) {
-#pragma unroll
-          for (int cc = 0; cc < 4; ++cc) {
-            const int c = half * 4 + cc;
-            const uint32_t addr = tile + row * 128 + ((c ^ (row & 7)) << 4);
-            uint32_t w[4];
-            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]) : "r"(addr) : "memory");
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-              const float p0 = bf16_lo(w[u]), p1 = bf16_hi(w[u]);
-              const float g0 = __uint_as_float(v[cc * 8 + 2 * u]), g1 = __uint_as_float(v[cc * 8 + 2 * u + 1]);
-              w[u] = pack_bf16(p0 * fmaf(g0, scale, nds), p1 * fmaf(g1, scale, nds));
-            }
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
-          }
-        }
-      }
-    }
-    fence_proxy_async();
-    tc_fence_before();
-    __syncthreads();
-    if (tid == 0) {
-      for (int t = 0; t < nt; ++t)
-        tma_store_2d(&tmdS, sP + t * VT_BYTES, 0, (int)(((size_t)bh * nnzb + rp + t0 + t) * BS));
-      bulk_commit();
-    }
-  }
-  if (tid == 0) bulk_wait_read_all();
-  tc_fence_before();
-  __syncthreads();
-  if (q == 0) tmem_dealloc(tmem, 128);
-}
+constexpr int ROW_THREADS = 128;
+constexpr int COL_THREADS = 160;          // warp 0: loads + MMA issue; warps 1-4: one TMEM quadrant each
+constexpr int COL_NST = 2;                // ring stages of the column kernel (one entry of a column each)
 
 // =====================================================================================
-// Backward, row side: k_dp_ds plus dQ = dS K in the same CTA.  The K tiles are fetched into the
-// V buffers as soon as the dP MMAs have consumed them (that load overlaps the dS arithmetic),
-// the dS tiles in shared memory feed both the second product and the TMA stores, and for rows of
-// at most 4 blocks the dQ accumulator reuses the TMEM columns of the first dP pair.
+// Backward, row side.  Unit = (sorted block row, bh).  Per unit: dP tiles (dO V^T) in TMEM, P tiles by
+// TMA, dS = P (dP - delta) scale written over P in shared memory, stored by TMA and used in place for
+// dQ = dS K; the K tiles arrive in the V buffers as soon as the dP MMAs have consumed V.
+// Rows of at most 4 blocks are one chunk (dP in all 128 columns, the dQ accumulator then reuses the
+// first 64).  Longer rows stream pairs of tiles over the two halves of the buffers: dP of a pair in
+// columns [64,128), dQ accumulating in [0,64); the dP MMAs of pair c+1 are issued right after the dQ
+// MMAs of pair c, and because the tensor pipe retires in issue order the arrival of dP(c+1) also
+// tells that dQ(c) is done and its half of the buffers can be refilled.
 template <int D>
-__global__ void __launch_bounds__(128) k_bwd_row(const __grid_constant__ CUtensorMap tmdO,
-                                                 const __grid_constant__ CUtensorMap tmV,
-                                                 const __grid_constant__ CUtensorMap tmK,
-                                                 const __grid_constant__ CUtensorMap tmP,
-                                                 const __grid_constant__ CUtensorMap tmdS,
-                                                 const __nv_bfloat16* __restrict__ dOg,
-                                                 const __nv_bfloat16* __restrict__ Og, __nv_bfloat16* __restrict__ dQ,
-                                                 const int4* __restrict__ row_info, const int* __restrict__ col_idx,
-                                                 int L, int nnzb, float scale, int* status) {
+__global__ void __launch_bounds__(ROW_THREADS, 3) k_bwd_row(const __grid_constant__ CUtensorMap tmdO,
+                                                            const __grid_constant__ CUtensorMap tmV,
+                                                            const __grid_constant__ CUtensorMap tmK,
+                                                            const __grid_constant__ CUtensorMap tmP,
+                                                            const __grid_constant__ CUtensorMap tmdS,
+                                                            const __nv_bfloat16* __restrict__ dOg,
+                                                            const __nv_bfloat16* __restrict__ Og,
+                                                            __nv_bfloat16* __restrict__ dQ,
+                                                            const int4* __restrict__ row_info,
+                                                            const int* __restrict__ col_idx, int L, int nnzb, int BH,
+                                                            int nrows, int heads, float scale, int* status) {
   using T = OpTile<D>;
-  constexpr int NCH = 4;
+  constexpr int NCH = ROW_NCH;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t sbase = (raw + 1023u) & ~1023u;
@@ -215,80 +66,61 @@ __global__ void __launch_bounds__(128) k_bwd_row(const __grid_constant__ CUtenso
   const uint32_t sB = sA + T::BYTES;                           // V tiles, then K tiles
   const uint32_t sP = sB + NCH * T::BYTES;                     // P tiles in, dS tiles out
   const uint32_t bars = sP + NCH * VT_BYTES;
-  const uint32_t bar_v = bars, bar_p = bars + 8, bar_s = bars + 16, bar_k = bars + 24, bar_o = bars + 32, slot = bars + 40;
+  // per half of the buffers: bar_v (dO + V tiles), bar_p (P tiles), bar_k (K tiles); bar_s: dP MMAs, bar_o: last dQ MMA
+  const uint32_t bar_v = bars, bar_p = bars + 16, bar_k = bars + 32, bar_s = bars + 48, bar_o = bars + 56, slot = bars + 64;
   uint32_t* slot_ptr = reinterpret_cast<uint32_t*>(smem_raw + (slot - raw));
   __shared__ int s_abort;
 
-  // (b,h) matrices are walked in descending order: the forward pass wrote P in ascending order, so the
-  // most recently written tiles (still in L2) are read first, and the dS tiles this kernel writes
-  // last are the ones the column kernel, which ascends, reads first.
-  const int bh = gridDim.y - 1 - blockIdx.y;
   const int tid = threadIdx.x, q = tid >> 5, lane = tid & 31;
   const int hf = lane >> 4;
   const int row = q * 16 + (lane & 15);
-  const int4 ri = row_info[blockIdx.x];                        // records are sorted, longest row first
-  const int rp = ri.x, nblk = ri.y & 0xffff, r = ri.y >> 16;
-  auto col_of = [&](int t) -> int {                            // block column of the row's t-th block
-    return t < 4 ? ((t & 2 ? ri.w : ri.z) >> ((t & 1) * 16)) & 0xffff : col_idx[rp + t];
-  };
-  const int nchunks = (nblk + NCH - 1) / NCH;
-  const bool single = nblk <= NCH;
-  const uint32_t ncols = single ? 128u : 256u;
-  const uint32_t dq_col = single ? 0u : 128u;
-  bool a_loaded = false;
+  const int total = nrows * BH;
+  constexpr uint32_t ncols = 128u;
 
-  auto issue_loads = [&](int ch) {                             // all lanes of warp 0: one copy per lane
-    const int t0 = ch * NCH, nt = min(NCH, nblk - t0);
+  // Warp 0, all lanes: request chunk ch of a unit (dO with the first chunk; V and P tiles) into half hb.
+  auto issue_loads = [&](const RowRec& R, int bh, int ch) {
+    const int CH = R.chunk();
+    const int t0 = ch * CH, nt = min(CH, R.nblk - t0);
+    const int hb = R.single() ? 0 : (ch & 1), b0 = 2 * hb;
+    const OpPos pos = op_pos(bh, L, heads, D);
     if (lane == 0) {
-      mbar_expect_tx(bar_v, (a_loaded ? 0 : T::BYTES) + nt * T::BYTES);
-      mbar_expect_tx(bar_p, nt * VT_BYTES);
+      mbar_expect_tx(bar_v + 8 * hb, (ch == 0 ? T::BYTES : 0) + nt * T::BYTES);
+      mbar_expect_tx(bar_p + 8 * hb, nt * VT_BYTES);
     }
     __syncwarp();
-    if (lane == 0 && !a_loaded) tma_load_2d(sA, &tmdO, bar_v, 0, bh * L + r * BS);
-    if (lane >= 1 && lane <= nt) tma_load_2d(sB + (lane - 1) * T::BYTES, &tmV, bar_v, 0, bh * L + col_of(t0 + lane - 1) * BS);
+    if (lane == 0 && ch == 0) tma_load_2d(sA, &tmdO, bar_v + 8 * hb, pos.x0, pos.row0 + R.r * BS);
+    if (lane >= 1 && lane <= nt)
+      tma_load_2d(sB + (b0 + lane - 1) * T::BYTES, &tmV, bar_v + 8 * hb, pos.x0, pos.row0 + R.col(t0 + lane - 1, col_idx) * BS);
     if (lane >= 9 && lane < 9 + nt)
-      tma_load_2d(sP + (lane - 9) * VT_BYTES, &tmP, bar_p, 0, (int)(((size_t)bh * nnzb + rp + t0 + lane - 9) * BS));
+      tma_load_2d(sP + (b0 + lane - 9) * VT_BYTES, &tmP, bar_p + 8 * hb, 0, (int)(((size_t)bh * nnzb + R.rp + t0 + lane - 9) * BS));
   };
+  auto first_loads = [&](const RowRec& R, int bh) {
+    if (R.nblk > 0) issue_loads(R, bh, 0);
+    if (!R.single() && R.nchunks() > 1) issue_loads(R, bh, 1);
+  };
+
+  int u = blockIdx.x;
+  RowRec R;
+  int bh = 0;
+  if (u < total) { const int rank = u / BH; R = RowRec(row_info[rank]); bh = u - rank * BH; }
 
   if (q == 0) {
     if (lane == 0) {
       s_abort = *reinterpret_cast<volatile int*>(status);
-      mbar_init(bar_v, 1);
-      mbar_init(bar_p, 1);
+      for (int i = 0; i < 6; ++i) mbar_init(bar_v + 8 * i, 1);      // bar_v[2], bar_p[2], bar_k[2]
       mbar_init(bar_s, 1);
-      mbar_init(bar_k, 1);
       mbar_init(bar_o, 1);
       fence_barrier_init();
     }
     __syncwarp();
-    // long rows ask for their first tiles before the (larger) TMEM allocation, short rows after it:
-    // each order measured faster for its case
-    if (s_abort == 0 && nblk > 0 && !single) issue_loads(0);
+    if (s_abort == 0 && u < total) first_loads(R, bh);
   }
   __syncthreads();
   if (s_abort != 0) return;
   if (q == 0) {
     tmem_alloc(slot, ncols);
     tmem_relinquish();
-    if (nblk > 0 && single) issue_loads(0);
   }
-  a_loaded = true;
-  float delta;
-  {
-    const size_t off = ((size_t)bh * L + r * BS + row) * D + hf * (D / 2);
-    const uint4* a4 = reinterpret_cast<const uint4*>(dOg + off);
-    const uint4* b4 = reinterpret_cast<const uint4*>(Og + off);
-    float acc = 0.f;
-#pragma unroll
-    for (int u = 0; u < D / 16; ++u) {
-      const uint4 a = a4[u], b = b4[u];
-      acc += bf16_lo(a.x) * bf16_lo(b.x) + bf16_hi(a.x) * bf16_hi(b.x) + bf16_lo(a.y) * bf16_lo(b.y) +
-             bf16_hi(a.y) * bf16_hi(b.y) + bf16_lo(a.z) * bf16_lo(b.z) + bf16_hi(a.z) * bf16_hi(b.z) +
-             bf16_lo(a.w) * bf16_lo(b.w) + bf16_hi(a.w) * bf16_hi(b.w);
-    }
-    delta = acc + __shfl_xor_sync(0xffffffffu, acc, 16);
-  }
-  const float nds = -delta * scale;
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -296,135 +128,182 @@ __global__ void __launch_bounds__(128) k_bwd_row(const __grid_constant__ CUtenso
   const uint32_t t_lane = tmem + ((uint32_t)(q * 32) << 16);
   constexpr uint32_t IDESC_P = make_idesc_bf16(64, 64, 0, 0);
   constexpr uint32_t IDESC_Q = make_idesc_bf16(64, D, 0, 1);
-  uint32_t ph_v = 0, ph_p = 0, ph_s = 0, ph_k = 0, ph_o = 0;
+  // parities run on across units.  pv, pk: one bit per half, thread 0 only; pp (one bit per half), ps, po: every thread
+  uint32_t pv = 0, pk = 0, pp = 0, ps = 0, po = 0;
   bool ok = true;
 
-  for (int ch = 0; ch < nchunks && ok; ++ch) {
-    const int t0 = ch * NCH, nt = min(NCH, nblk - t0);
-    if (ch > 0 && q == 0) {
-      if (lane == 0) bulk_wait_read_all();                     // previous dS tiles have left shared memory
-      __syncwarp();
-      issue_loads(ch);
-    }
-    if (!__syncthreads_and(mbar_wait(bar_v, ph_v))) { if (tid == 0) report(status, ERR_LOAD_WAIT); ok = false; break; }
-    ph_v ^= 1;
-    if (tid == 0) {
+  for (; u < total && ok; u += gridDim.x) {
+    const int un = u + (int)gridDim.x;
+    const bool has_next = un < total;
+    RowRec Rn;
+    int bhn = 0;
+    if (has_next) { const int rank = un / BH; Rn = RowRec(row_info[rank]); bhn = un - rank * BH; }
+
+    const int rp = R.rp, nblk = R.nblk, r = R.r;
+    const bool single = R.single();
+    const OpPos pos = op_pos(bh, L, heads, D);
+
+    // tid 0: dP MMAs of chunk ch (its dO / V tiles were requested earlier), pair p of the chunk in columns col0 + 64 p
+    auto issue_dp = [&](int ch, uint32_t col0) -> bool {
+      const int CH = single ? NCH : 2;
+      const int t0 = ch * CH, nt = min(CH, nblk - t0);
+      const int hb = single ? 0 : (ch & 1), b0 = 2 * hb;
+      if (!mbar_wait(bar_v + 8 * hb, (pv >> hb) & 1)) { report(status, ERR_LOAD_WAIT); return false; }
+      pv ^= 1u << hb;
       tc_fence_after();
       for (int t = 0; t < nt; ++t) {
-        const uint32_t d_addr = tmem + ((uint32_t)((t & 1) * 16) << 16) + (t >> 1) * 64;
+        const uint32_t d_addr = tmem + ((uint32_t)((t & 1) * 16) << 16) + col0 + (uint32_t)(t >> 1) * 64u;
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk)
-          mma_bf16(d_addr, T::kmajor(sA, kk), T::kmajor(sB + t * T::BYTES, kk), IDESC_P, kk > 0);
+          mma_bf16(d_addr, T::kmajor(sA, kk), T::kmajor(sB + (b0 + t) * T::BYTES, kk), IDESC_P, kk > 0);
       }
       mma_commit(bar_s);
-    }
-    const bool w1 = mbar_wait(bar_s, ph_s);
-    if (q == 0) {                                              // V consumed: bring K into the same buffers
-      const bool all_ok = __all_sync(0xffffffffu, w1);
-      if (all_ok) {
-        if (lane == 0) mbar_expect_tx(bar_k, nt * T::BYTES);
-        __syncwarp();
-        if (lane < nt) tma_load_2d(sB + lane * T::BYTES, &tmK, bar_k, 0, bh * L + col_of(t0 + lane) * BS);
-      }
-    }
-    const bool w2 = mbar_wait(bar_p, ph_p);
-    if (!__syncthreads_and(w1 && w2)) { if (tid == 0) report(status, ERR_MMA_WAIT); ok = false; break; }
-    ph_s ^= 1; ph_p ^= 1;
-    tc_fence_after();
-    for (int p = 0; p < 2; ++p) {
-      const int t = 2 * p + hf;
-      const bool mine = t < nt;
-      const uint32_t tile = sP + t * VT_BYTES;
+      return true;
+    };
+    // warp 0, all lanes: the dP MMAs have consumed the V tiles of this chunk: bring K into the same buffers
+    auto issue_k = [&](int hb, int t0, int nt) {
+      if (lane == 0) mbar_expect_tx(bar_k + 8 * hb, nt * T::BYTES);
+      __syncwarp();
+      if (lane < nt)
+        tma_load_2d(sB + (2 * hb + lane) * T::BYTES, &tmK, bar_k + 8 * hb, pos.x0, pos.row0 + R.col(t0 + lane, col_idx) * BS);
+    };
+    // dS = P (dP scale - delta scale), in place over the P tiles b0 + t; pair p of the chunk sits in columns colbase + 64 p
+    auto ds_math = [&](uint32_t colbase, int b0, int nt, int npairs, float nds) {
+      for (int p = 0; p < npairs; ++p) {
+        const int t = 2 * p + hf;
+        const bool mine = t < nt;
+        const uint32_t tile = sP + (b0 + t) * VT_BYTES;
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        uint32_t v[32];
-        tmem_ld32(t_lane + p * 64 + half * 32, v);
-        tmem_ld_wait();
-        if (mine) {
+        for (int half = 0; half < 2; ++half) {
+          uint32_t v[32];
+          tmem_ld32(t_lane + colbase + p * 64 + half * 32, v);
+          tmem_ld_wait();
+          if (mine) {
 #pragma unroll
-          for (int cc = 0; cc < 4; ++cc) {
-            const int c = half * 4 + cc;
-            const uint32_t addr = tile + row * 128 + ((c ^ (row & 7)) << 4);
-            uint32_t w[4];
-            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]) : "r"(addr) : "memory");
+            for (int cc = 0; cc < 4; ++cc) {
+              const int c = half * 4 + cc;
+              const uint32_t addr = tile + row * 128 + ((c ^ (row & 7)) << 4);
+              uint32_t w[4];
+              asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]) : "r"(addr) : "memory");
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-              const float p0 = bf16_lo(w[u]), p1 = bf16_hi(w[u]);
-              const float g0 = __uint_as_float(v[cc * 8 + 2 * u]), g1 = __uint_as_float(v[cc * 8 + 2 * u + 1]);
-              w[u] = pack_bf16(p0 * fmaf(g0, scale, nds), p1 * fmaf(g1, scale, nds));
+              for (int e = 0; e < 4; ++e) {
+                const float p0 = bf16_lo(w[e]), p1 = bf16_hi(w[e]);
+                const float g0 = __uint_as_float(v[cc * 8 + 2 * e]), g1 = __uint_as_float(v[cc * 8 + 2 * e + 1]);
+                w[e] = pack_bf16(p0 * fmaf(g0, scale, nds), p1 * fmaf(g1, scale, nds));
+              }
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
             }
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
           }
         }
       }
-    }
-    fence_proxy_async();
-    tc_fence_before();
-    __syncthreads();
-    if (tid == 0) {
+    };
+    // tid 0: store the dS tiles of a chunk and issue dQ += dS K (every tile into the one accumulator at lane offset 0)
+    auto issue_dq = [&](int hb, int t0, int nt, bool first_chunk) -> bool {
+      const int b0 = 2 * hb;
       for (int t = 0; t < nt; ++t)
-        tma_store_2d(&tmdS, sP + t * VT_BYTES, 0, (int)(((size_t)bh * nnzb + rp + t0 + t) * BS));
+        tma_store_2d(&tmdS, sP + (b0 + t) * VT_BYTES, 0, (int)(((size_t)bh * nnzb + rp + t0 + t) * BS));
       bulk_commit();
-      if (mbar_wait(bar_k, ph_k)) {
-        tc_fence_after();
-        for (int t = 0; t < nt; ++t) {
-          const uint32_t d_addr = tmem + ((uint32_t)((t & 1) * 16) << 16) + dq_col;
-          const uint32_t first = (ch == 0 && t < 2) ? 0u : 1u;
+      if (!mbar_wait(bar_k + 8 * hb, (pk >> hb) & 1)) { report(status, ERR_LOAD_WAIT); return false; }
+      pk ^= 1u << hb;
+      tc_fence_after();
+      for (int t = 0; t < nt; ++t) {
+        const uint32_t first = (first_chunk && t == 0) ? 0u : 1u;
 #pragma unroll
-          for (int kk = 0; kk < BS / 16; ++kk)
-            mma_bf16(d_addr, ValTile::kmajor(sP + t * VT_BYTES, kk), T::mnmajor(sB + t * T::BYTES, kk), IDESC_Q,
-                     (kk > 0) ? 1u : first);
-        }
-        mma_commit(bar_o);
-      } else {
-        report(status, ERR_LOAD_WAIT);
+        for (int kk = 0; kk < BS / 16; ++kk)
+          mma_bf16(tmem, ValTile::kmajor(sP + (b0 + t) * VT_BYTES, kk), T::mnmajor(sB + (b0 + t) * T::BYTES, kk), IDESC_Q,
+                   (kk > 0) ? 1u : first);
       }
-    }
-    ph_k ^= 1;
-    if (!__syncthreads_and(mbar_wait(bar_o, ph_o))) { if (tid == 0) report(status, ERR_MMA2_WAIT); ok = false; break; }
-    ph_o ^= 1;
-    tc_fence_after();
-  }
+      return true;
+    };
 
-  if (ok) {
-    const bool odd_valid = nblk >= 2;
-    __nv_bfloat16* dst = dQ + ((size_t)bh * L + r * BS + row) * D + hf * (D / 2);
+    if (nblk > 0) {
+      if (tid == 0) issue_dp(0, single ? 0u : 64u);
+      // delta_i = sum_n dO_in O_in: the two owners of a row take one half of the head dimension each
+      float delta;
+      {
+        const size_t off = (size_t)(pos.row0 + r * BS + row) * pos.ld + pos.x0 + hf * (D / 2);
+        const uint4* a4 = reinterpret_cast<const uint4*>(dOg + off);
+        const uint4* b4 = reinterpret_cast<const uint4*>(Og + off);
+        float acc = 0.f;
 #pragma unroll
-    for (int h = 0; h < D / 32; ++h) {
-      uint32_t v[32];
-      if (nblk > 0) {
-        tmem_ld32(t_lane + dq_col + h * 32, v);
-        tmem_ld_wait();
+        for (int e = 0; e < D / 16; ++e) {
+          const uint4 a = a4[e], b = b4[e];
+          acc += bf16_lo(a.x) * bf16_lo(b.x) + bf16_hi(a.x) * bf16_hi(b.x) + bf16_lo(a.y) * bf16_lo(b.y) +
+                 bf16_hi(a.y) * bf16_hi(b.y) + bf16_lo(a.z) * bf16_lo(b.z) + bf16_hi(a.z) * bf16_hi(b.z) +
+                 bf16_lo(a.w) * bf16_lo(b.w) + bf16_hi(a.w) * bf16_hi(b.w);
+        }
+        delta = acc + __shfl_xor_sync(0xffffffffu, acc, 16);
       }
-      float acc[32];
+      const float nds = -delta * scale;
+      const int n = single ? 1 : R.nchunks();
+      for (int c = 0; c < n && ok; ++c) {
+        const int CH = single ? NCH : 2;
+        const int hb = single ? 0 : (c & 1), t0 = c * CH, nt = min(CH, nblk - t0);
+        // dP(c) has arrived; in a long row that also means dQ(c-1) is complete
+        if (!__syncthreads_and(mbar_wait(bar_s, ps))) { if (tid == 0) report(status, ERR_MMA_WAIT); ok = false; break; }
+        ps ^= 1u;
+        tc_fence_after();
+        if (q == 0) {
+          issue_k(hb, t0, nt);
+          if (c >= 1 && c + 1 < n) {                               // the other half is free: it takes chunk c+1
+            if (lane == 0) bulk_wait_read_all();                   // once the dS stores of chunk c-1 have read it
+            __syncwarp();
+            issue_loads(R, bh, c + 1);
+          }
+        }
+        if (!__syncthreads_and(mbar_wait(bar_p + 8 * hb, (pp >> hb) & 1))) { if (tid == 0) report(status, ERR_LOAD_WAIT); ok = false; break; }
+        pp ^= 1u << hb;
+        ds_math(single ? 0u : 64u, 2 * hb, nt, single ? 2 : 1, nds);
+        fence_proxy_async();
+        tc_fence_before();
+        __syncthreads();
+        if (tid == 0 && issue_dq(hb, t0, nt, c == 0)) {
+          if (c + 1 < n) issue_dp(c + 1, 64u);
+          else mma_commit(bar_o);
+        }
+      }
+      if (ok) {
+        if (!__syncthreads_and(mbar_wait(bar_o, po))) { if (tid == 0) report(status, ERR_MMA2_WAIT); ok = false; }
+        po ^= 1u;
+      }
+      tc_fence_after();
+    }
+    if (ok && q == 0 && has_next) {                                // every buffer of this unit is free
+      if (lane == 0) bulk_wait_read_all();
+      __syncwarp();
+      first_loads(Rn, bhn);
+    }
+    if (ok) {
+      // the accumulator rows sit in lanes 0-15 of every quadrant: those lanes write the whole row
+      __nv_bfloat16* dst = dQ + (size_t)(pos.row0 + r * BS + row) * pos.ld + pos.x0;
 #pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        const float mine_v = (nblk > 0 && (hf == 0 || odd_valid)) ? __uint_as_float(v[j]) : 0.f;
-        acc[j] = mine_v + __shfl_xor_sync(0xffffffffu, mine_v, 16);
-      }
-      if (D == 64) {
-        if (hf == h) {
+      for (int h = 0; h < D / 32; ++h) {
+        uint32_t v[32];
+        if (nblk > 0) {
+          tmem_ld32(t_lane + h * 32, v);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = 0u;
+        }
+        if (hf == 0) {
 #pragma unroll
           for (int j = 0; j < 32; j += 8) {
-            uint4 pk;
-            pk.x = pack_bf16(acc[j], acc[j + 1]); pk.y = pack_bf16(acc[j + 2], acc[j + 3]);
-            pk.z = pack_bf16(acc[j + 4], acc[j + 5]); pk.w = pack_bf16(acc[j + 6], acc[j + 7]);
-            *reinterpret_cast<uint4*>(dst + j) = pk;
+            uint4 pk4;
+            pk4.x = pack_bf16(__uint_as_float(v[j]), __uint_as_float(v[j + 1]));
+            pk4.y = pack_bf16(__uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+            pk4.z = pack_bf16(__uint_as_float(v[j + 4]), __uint_as_float(v[j + 5]));
+            pk4.w = pack_bf16(__uint_as_float(v[j + 6]), __uint_as_float(v[j + 7]));
+            *reinterpret_cast<uint4*>(dst + h * 32 + j) = pk4;
           }
-        }
-      } else {
-#pragma unroll
-        for (int j = 0; j < 16; j += 8) {
-          float val[8];
-#pragma unroll
-          for (int u = 0; u < 8; ++u) val[u] = hf ? acc[16 + j + u] : acc[j + u];
-          uint4 pk;
-          pk.x = pack_bf16(val[0], val[1]); pk.y = pack_bf16(val[2], val[3]);
-          pk.z = pack_bf16(val[4], val[5]); pk.w = pack_bf16(val[6], val[7]);
-          *reinterpret_cast<uint4*>(dst + j) = pk;
         }
       }
     }
+    tc_fence_before();
+    __syncthreads();                                               // the next unit's dP MMAs overwrite these columns
+    tc_fence_after();
+    R = Rn;
+    bh = bhn;
   }
   if (tid == 0) bulk_wait_read_all();
   tc_fence_before();
@@ -433,65 +312,49 @@ __global__ void __launch_bounds__(128) k_bwd_row(const __grid_constant__ CUtenso
 }
 
 // =====================================================================================
-// Block SpMM.  128 threads, one CTA per (line, bh); NST value/operand tile pairs per chunk.
-//   DUAL == false: line = block row r.   out0[r*64.., :] = sum_k  vals0(r, c_k)   * B0[c_k*64.., :]
-//   DUAL == true : line = block column c.
-//                  out0[c*64.., :] = sum_r vals0(r, c)^T * B0[r*64.., :]      (dK = dS^T Q)
-//                  out1[c*64.., :] = sum_r vals1(r, c)^T * B1[r*64.., :]      (dV = P^T dO)
-template <int D, bool DUAL, int NST>
-__global__ void __launch_bounds__(128) k_spmm(const __grid_constant__ CUtensorMap tmV0,
-                                              const __grid_constant__ CUtensorMap tmV1,
-                                              const __grid_constant__ CUtensorMap tmB0,
-                                              const __grid_constant__ CUtensorMap tmB1,
-                                              __nv_bfloat16* __restrict__ out0, __nv_bfloat16* __restrict__ out1,
-                                              const int* __restrict__ line_ptr, const int* __restrict__ idx,
-                                              const int* __restrict__ pos, const int* __restrict__ order, int L,
-                                              int nnzb, int* status) {
+// Backward, column side.  Unit = (block column c, bh):
+//     dK[c*64.., :] = sum_r dS(r, c)^T Q[r*64.., :]        dV[c*64.., :] = sum_r P(r, c)^T dO[r*64.., :]
+// The value tiles are read as MN-major A operands, so no transposed copies exist anywhere.
+// Warp 0 feeds a ring of COL_NST stages (one entry of a column each: dS, Q, P, dO tiles) and issues the
+// MMAs; the ring runs on across the units of the CTA, so the first tiles of the next column load while
+// the current one finishes.  The two accumulators of a unit share 64 TMEM columns (dK in lanes 0-15 of
+// every quadrant, dV in lanes 16-31) and units alternate between two such buffers: warps 1-4 (TMEM
+// quadrant = warp & 3) turn buffer j & 1 into output rows while warp 0 already accumulates the next unit
+// into the other one.
+template <int D>
+__global__ void __launch_bounds__(COL_THREADS) k_bwd_col(const __grid_constant__ CUtensorMap tmdS,
+                                                         const __grid_constant__ CUtensorMap tmP,
+                                                         const __grid_constant__ CUtensorMap tmQ,
+                                                         const __grid_constant__ CUtensorMap tmdO,
+                                                         __nv_bfloat16* __restrict__ dK, __nv_bfloat16* __restrict__ dV,
+                                                         const int* __restrict__ col_ptr, const int* __restrict__ row_idx,
+                                                         const int* __restrict__ csc_pos, const int* __restrict__ order,
+                                                         int L, int nnzb, int BH, int nb, int heads, int* status) {
   using T = OpTile<D>;
-  constexpr int NP = DUAL ? 2 : 1;                                // products per entry
-  constexpr int STAGE_BYTES = NP * (VT_BYTES + T::BYTES);
+  constexpr int NST = COL_NST;
+  constexpr int STAGE_BYTES = 2 * (VT_BYTES + T::BYTES);
   extern __shared__ uint8_t smem_raw[];
-  const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  // ring of NST stages, one entry of the line each: full[s] (tiles landed), empty[s] (MMAs that read them done)
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t sbase = (raw + 1023u) & ~1023u;
+  // full[s]: tiles of stage s landed; empty[s]: the MMAs that read stage s are done;
+  // done[b]: accumulator buffer b holds a finished unit; free[b]: its rows have been read out (4 warps arrive)
   const uint32_t bar_full = sbase + NST * STAGE_BYTES;
   const uint32_t bar_empty = bar_full + 8 * NST;
   const uint32_t bar_done = bar_empty + 8 * NST;
-  const uint32_t slot = bar_done + 8;
-  uint32_t* slot_ptr = reinterpret_cast<uint32_t*>(smem_raw + (slot - smem_u32(smem_raw)));
+  const uint32_t bar_free = bar_done + 16;
+  const uint32_t slot = bar_free + 16;
+  uint32_t* slot_ptr = reinterpret_cast<uint32_t*>(smem_raw + (slot - raw));
+  __shared__ int s_abort;
 
-  // One (b,h) matrix after the other (the value tiles of a matrix were written together, and a grid that
-  // interleaves the matrices measured slower); inside a matrix the longest lines first when an order is given.
-  const int bh = blockIdx.y, line = order ? order[blockIdx.x] : (int)blockIdx.x;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  constexpr uint32_t TMEM_COLS = (NP * D) < 32 ? 32 : (NP * D);   // 32, 64 or 128: powers of two
-  __shared__ int s_abort;                                         // an earlier CTA gave up: do not pile on
-  const int beg = line_ptr[line], end = line_ptr[line + 1];
-  const int n = end - beg;
+  const int total = nb * BH, G = (int)gridDim.x;
+  constexpr uint32_t TMEM_COLS = 128u;                              // two buffers of 64 columns
 
-  // warp 0, all lanes: request entry e into stage st (one copy per lane)
-  auto fill = [&](int st, int e) {
-    const uint32_t sa = sbase + st * STAGE_BYTES;
-    if (lane == 0) mbar_expect_tx(bar_full + 8 * st, STAGE_BYTES);
-    __syncwarp();
-    if (lane < 2 * NP) {
-      const int other = idx[e];                                    // block column (CSR) or block row (CSC)
-      const int blk = DUAL ? pos[e] : e;                           // CSR block id of the value tile
-      const int vrow = (int)(((size_t)bh * nnzb + blk) * BS);
-      const int orow = bh * L + other * BS;
-      if (lane == 0) tma_load_2d(sa, &tmV0, bar_full + 8 * st, 0, vrow);
-      if (lane == 1) tma_load_2d(sa + VT_BYTES, &tmB0, bar_full + 8 * st, 0, orow);
-      if (DUAL && lane == 2) tma_load_2d(sa + VT_BYTES + T::BYTES, &tmV1, bar_full + 8 * st, 0, vrow);
-      if (DUAL && lane == 3) tma_load_2d(sa + 2 * VT_BYTES + T::BYTES, &tmB1, bar_full + 8 * st, 0, orow);
-    }
-  };
-
-  if (warp == 0) {
-    if (lane == 0) {
-      s_abort = *reinterpret_cast<volatile int*>(status);
-      for (int st = 0; st < NST; ++st) { mbar_init(bar_full + 8 * st, 1); mbar_init(bar_empty + 8 * st, 1); }
-      mbar_init(bar_done, 1);
-      fence_barrier_init();
-    }
+  if (warp == 0 && lane == 0) {
+    s_abort = *reinterpret_cast<volatile int*>(status);
+    for (int st = 0; st < NST; ++st) { mbar_init(bar_full + 8 * st, 1); mbar_init(bar_empty + 8 * st, 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(bar_done + 8 * b, 1); mbar_init(bar_free + 8 * b, 4); }
+    fence_barrier_init();
   }
   __syncthreads();
   if (s_abort != 0) return;
@@ -503,81 +366,137 @@ __global__ void __launch_bounds__(128) k_spmm(const __grid_constant__ CUtensorMa
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *slot_ptr;
-  constexpr uint32_t IDESC = make_idesc_bf16(64, D, DUAL ? 1 : 0, 1);
-  bool ok = true;
+  constexpr uint32_t IDESC = make_idesc_bf16(64, D, 1, 1);
+
+  // unit u -> (bh, block column); columns of one (b,h) matrix together, the longest first
+  auto unit_line = [&](int uu, int& bh, int& line, int& beg, int& end) {
+    bh = uu / nb;
+    line = order[uu - bh * nb];
+    beg = col_ptr[line];
+    end = col_ptr[line + 1];
+  };
 
   if (warp == 0) {
-    // (requesting the first tiles before the TMEM allocation measured slower for this kernel)
-    for (int t = 0; t < NST && t < n; ++t) fill(t, beg + t);
-    for (int i = 0; i < n; ++i) {
-      const int st = i % NST;
-      const uint32_t ph = (uint32_t)(i / NST) & 1u;
-      if (!__all_sync(0xffffffffu, mbar_wait(bar_full + 8 * st, ph))) { if (lane == 0) report(status, ERR_LOAD_WAIT); ok = false; break; }
-      if (lane == 0) {
-        tc_fence_after();
-        const uint32_t sa = sbase + st * STAGE_BYTES;
-        const uint32_t first = i == 0 ? 0u : 1u;
-#pragma unroll
-        for (int kk = 0; kk < BS / 16; ++kk) {
-          const uint64_t a0 = DUAL ? ValTile::mnmajor(sa, kk) : ValTile::kmajor(sa, kk);
-          mma_bf16(tmem, a0, T::mnmajor(sa + VT_BYTES, kk), IDESC, (kk > 0) ? 1u : first);
-        }
-        if (DUAL) {
-#pragma unroll
-          for (int kk = 0; kk < BS / 16; ++kk)
-            mma_bf16(tmem + D, ValTile::mnmajor(sa + VT_BYTES + T::BYTES, kk),
-                     T::mnmajor(sa + 2 * VT_BYTES + T::BYTES, kk), IDESC, (kk > 0) ? 1u : first);
-        }
-        if (i + 1 == n) mma_commit(bar_done);
-        else mma_commit(bar_empty + 8 * st);
+    // ------------------------------------------------------------ loads + MMA issue
+    // fill cursor: the next entry to request (runs ahead of the MMAs, across units)
+    int fu = blockIdx.x, fbh = 0, fline = 0, fe = 0, fend = 0;
+    auto fill_seek = [&]() {                                         // move to the next unit that has entries
+      while (fu < total) {
+        unit_line(fu, fbh, fline, fe, fend);
+        if (fe < fend) return;
+        fu += G;
       }
+    };
+    fill_seek();
+    int nfill = 0, nuse = 0;                                         // entries requested / consumed by this CTA
+    auto fill_one = [&]() -> bool {                                  // all lanes; false on a time-out
+      const int st = nfill % NST;
+      if (nfill >= NST) {                                            // the MMAs of the entry NST back must be done
+        if (!__all_sync(0xffffffffu, mbar_wait(bar_empty + 8 * st, (uint32_t)(nfill / NST - 1) & 1u))) return false;
+      }
+      const uint32_t sa = sbase + st * STAGE_BYTES;
+      if (lane == 0) mbar_expect_tx(bar_full + 8 * st, STAGE_BYTES);
       __syncwarp();
-      if (i + NST < n) {                                           // this stage takes entry i + NST once its MMAs are done
-        if (!__all_sync(0xffffffffu, mbar_wait(bar_empty + 8 * st, ph))) { if (lane == 0) report(status, ERR_MMA_WAIT); ok = false; break; }
-        fill(st, beg + i + NST);
+      if (lane < 4) {
+        const OpPos pos = op_pos(fbh, L, heads, D);
+        const int vrow = (int)(((size_t)fbh * nnzb + csc_pos[fe]) * BS);     // CSR block id of the value tile
+        const int orow = pos.row0 + row_idx[fe] * BS;
+        if (lane == 0) tma_load_2d(sa, &tmdS, bar_full + 8 * st, 0, vrow);
+        if (lane == 1) tma_load_2d(sa + VT_BYTES, &tmQ, bar_full + 8 * st, pos.x0, orow);
+        if (lane == 2) tma_load_2d(sa + VT_BYTES + T::BYTES, &tmP, bar_full + 8 * st, 0, vrow);
+        if (lane == 3) tma_load_2d(sa + 2 * VT_BYTES + T::BYTES, &tmdO, bar_full + 8 * st, pos.x0, orow);
       }
-    }
-  }
-  {
-    // only warp 0 polls the barrier of the last MMAs; the other warps sleep in the CTA barrier
-    bool w = true;
-    if (warp == 0) {
-      w = (n > 0 && ok) ? mbar_wait(bar_done, 0) : (n == 0);
-      tc_fence_before();
-    }
-    if (!__syncthreads_and(w)) { if (tid == 0 && ok) report(status, ERR_MMA_WAIT); ok = false; } else ok = true;
-    tc_fence_after();
-  }
-
-  // epilogue: TMEM -> bf16 rows of the output(s)
-  const bool active = lane < 16;
-  const int row = warp * 16 + (lane & 15);
-  const uint32_t tlane = tmem + ((uint32_t)(warp * 32) << 16);
-  if (ok) {
+      ++nfill;
+      if (++fe >= fend) { fu += G; fill_seek(); }
+      return true;
+    };
+    bool ok = true;
+    int uses0 = 0, uses1 = 0;                                        // units with entries that went to buffer 0 / 1
+    int j = 0;
+    for (int uu = blockIdx.x; uu < total && ok; uu += G, ++j) {
+      int bh, line, beg, end;
+      unit_line(uu, bh, line, beg, end);
+      const int n = end - beg;
+      if (n == 0) continue;
+      const int buf = j & 1;
+      const int uses = buf ? uses1 : uses0;
+      if (uses >= 1) {                                               // the rows of the unit before last have been read out
+        if (!__all_sync(0xffffffffu, mbar_wait(bar_free + 8 * buf, (uint32_t)(uses - 1) & 1u))) { ok = false; break; }
+        tc_fence_after();
+      }
+      const uint32_t acc = tmem + (uint32_t)buf * 64u;
+      for (int i = 0; i < n && ok; ++i) {
+        while (ok && nfill < nuse + NST && fu < total) ok = fill_one();
+        if (!ok) break;
+        const int st = nuse % NST;
+        if (!__all_sync(0xffffffffu, mbar_wait(bar_full + 8 * st, (uint32_t)(nuse / NST) & 1u))) { ok = false; break; }
+        if (lane == 0) {
+          tc_fence_after();
+          const uint32_t sa = sbase + st * STAGE_BYTES;
+          const uint32_t first = i == 0 ? 0u : 1u;
 #pragma unroll
-    for (int pi = 0; pi < NP; ++pi) {
-      __nv_bfloat16* dst = (pi == 0 ? out0 : out1) + ((size_t)bh * L + (size_t)line * BS + row) * D;
+          for (int kk = 0; kk < BS / 16; ++kk)                       // dK += dS^T Q  (lanes 0-15 of every quadrant)
+            mma_bf16(acc, ValTile::mnmajor(sa, kk), T::mnmajor(sa + VT_BYTES, kk), IDESC, (kk > 0) ? 1u : first);
+#pragma unroll
+          for (int kk = 0; kk < BS / 16; ++kk)                       // dV += P^T dO  (lanes 16-31)
+            mma_bf16(acc + (16u << 16), ValTile::mnmajor(sa + VT_BYTES + T::BYTES, kk),
+                     T::mnmajor(sa + 2 * VT_BYTES + T::BYTES, kk), IDESC, (kk > 0) ? 1u : first);
+          mma_commit(bar_empty + 8 * st);
+          if (i + 1 == n) mma_commit(bar_done + 8 * buf);
+        }
+        __syncwarp();
+        ++nuse;
+      }
+      if (buf) ++uses1; else ++uses0;
+    }
+    if (!ok && lane == 0) report(status, ERR_LOAD_WAIT);
+  } else {
+    // ------------------------------------------------------------ output rows: TMEM -> bf16 -> global
+    const int qd = warp & 3;                                         // TMEM quadrant of this warp
+    const int row = qd * 16 + (lane & 15);
+    __nv_bfloat16* out = lane < 16 ? dK : dV;
+    bool ok = true;
+    int uses0 = 0, uses1 = 0;
+    int j = 0;
+    for (int uu = blockIdx.x; uu < total && ok; uu += G, ++j) {
+      int bh, line, beg, end;
+      unit_line(uu, bh, line, beg, end);
+      const int n = end - beg;
+      const int buf = j & 1;
+      const OpPos pos = op_pos(bh, L, heads, D);
+      __nv_bfloat16* dst = out + (size_t)(pos.row0 + line * BS + row) * pos.ld + pos.x0;
+      if (n > 0) {
+        const int uses = buf ? uses1 : uses0;
+        if (!__all_sync(0xffffffffu, mbar_wait(bar_done + 8 * buf, (uint32_t)uses & 1u))) { ok = false; break; }
+        tc_fence_after();
+      }
+      const uint32_t tl = tmem + ((uint32_t)(qd * 32) << 16) + (uint32_t)buf * 64u;
 #pragma unroll
       for (int h = 0; h < D / 32; ++h) {
         uint32_t v[32];
-        if (end > beg) {
-          tmem_ld32(tlane + pi * D + h * 32, v);
+        if (n > 0) {
+          tmem_ld32(tl + h * 32, v);
           tmem_ld_wait();
         } else {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = 0u;
+          for (int e = 0; e < 32; ++e) v[e] = 0u;
         }
-        if (active) {
-          uint4* d4 = reinterpret_cast<uint4*>(dst + h * 32);
+        uint4* d4 = reinterpret_cast<uint4*>(dst + h * 32);
 #pragma unroll
-          for (int q = 0; q < 4; ++q)
-            d4[q] = make_uint4(pack_bf16(__uint_as_float(v[8 * q]), __uint_as_float(v[8 * q + 1])),
-                               pack_bf16(__uint_as_float(v[8 * q + 2]), __uint_as_float(v[8 * q + 3])),
-                               pack_bf16(__uint_as_float(v[8 * q + 4]), __uint_as_float(v[8 * q + 5])),
-                               pack_bf16(__uint_as_float(v[8 * q + 6]), __uint_as_float(v[8 * q + 7])));
-        }
+        for (int e = 0; e < 4; ++e)
+          d4[e] = make_uint4(pack_bf16(__uint_as_float(v[8 * e]), __uint_as_float(v[8 * e + 1])),
+                             pack_bf16(__uint_as_float(v[8 * e + 2]), __uint_as_float(v[8 * e + 3])),
+                             pack_bf16(__uint_as_float(v[8 * e + 4]), __uint_as_float(v[8 * e + 5])),
+                             pack_bf16(__uint_as_float(v[8 * e + 6]), __uint_as_float(v[8 * e + 7])));
+      }
+      if (n > 0) {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_free + 8 * buf);
+        if (buf) ++uses1; else ++uses0;
       }
     }
+    if (!ok && lane == 0) report(status, ERR_MMA_WAIT);
   }
   tc_fence_before();
   __syncthreads();
@@ -677,19 +596,21 @@ __global__ void k_wait_selftest(int* status, long long limit_cycles) {
   if (!ok && threadIdx.x == 0) report(status, ERR_LOAD_WAIT);
 }
 
-constexpr int NST_N = 4, NST_T = 2;
+template <int D> constexpr size_t smem_row() { return 1024 + (size_t)5 * OpTile<D>::BYTES + 4 * VT_BYTES + 128; }
+template <int D> constexpr size_t smem_col() { return 1024 + (size_t)COL_NST * 2 * (VT_BYTES + OpTile<D>::BYTES) + 128; }
 
-template <int D> constexpr size_t smem_dp_ds() { return 1024 + (size_t)5 * OpTile<D>::BYTES + 4 * VT_BYTES + 64; }
-template <int D> constexpr size_t smem_spmm(int nst, int np) { return 1024 + (size_t)nst * np * (VT_BYTES + OpTile<D>::BYTES) + 128; }
-
+// Shared-memory opt-in of the two backward kernels, and how many CTAs of each one SM holds at once
+// (the persistent grids; both kernels take 128 of the 512 tensor-memory columns).
 template <int D>
-int set_attrs() {
-  SPION_CUDA_TRY(cudaFuncSetAttribute(k_dp_ds<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dp_ds<D>()));
-  SPION_CUDA_TRY(cudaFuncSetAttribute(k_bwd_row<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dp_ds<D>()));
-  SPION_CUDA_TRY(cudaFuncSetAttribute(k_spmm<D, false, NST_N>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      (int)smem_spmm<D>(NST_N, 1)));
-  SPION_CUDA_TRY(cudaFuncSetAttribute(k_spmm<D, true, NST_T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      (int)smem_spmm<D>(NST_T, 2)));
+int set_attrs(TcState* s) {
+  SPION_CUDA_TRY(cudaFuncSetAttribute(k_bwd_row<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_row<D>()));
+  SPION_CUDA_TRY(cudaFuncSetAttribute(k_bwd_col<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_col<D>()));
+  int n = 0;
+  SPION_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, k_bwd_row<D>, ROW_THREADS, smem_row<D>()));
+  s->row_ctas = n > 4 ? 4 : n;
+  SPION_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, k_bwd_col<D>, COL_THREADS, smem_col<D>()));
+  s->col_ctas = n > 4 ? 4 : n;
+  if (s->row_ctas < 1 || s->col_ctas < 1) return SPION_ERR_CUDA;
   return SPION_OK;
 }
 
@@ -718,37 +639,24 @@ int run_backward(spion_ctx* c, TcState* s, const void* Q, const void* K, const v
     P = s->p64_ws;
     dS = s->ds64_ws;
   }
-  const uint64_t rows = (uint64_t)c->BH * c->L, vrows = (uint64_t)c->BH * vw.nnzb * BS;
-  const dim3 grid(vw.nb, c->BH);
+  const uint64_t vrows = (uint64_t)c->BH * vw.nnzb * BS;
   prof_mark(c, -1);
   CUtensorMap mds, mp, mq, mk, mdo, mv;
-  if ((rc = make_map(s, &mds, dS, vrows, BS, BS)) || (rc = make_map(s, &mp, P, vrows, BS, BS)) ||
-      (rc = make_map(s, &mq, Q, rows, D, BS)) || (rc = make_map(s, &mk, K, rows, D, BS)) ||
-      (rc = make_map(s, &mdo, dO, rows, D, BS)) || (rc = make_map(s, &mv, V, rows, D, BS)))
+  if ((rc = make_map(s, &mds, dS, vrows, BS, BS, BS)) || (rc = make_map(s, &mp, P, vrows, BS, BS, BS)) ||
+      (rc = make_operand_map(c, s, &mq, Q, D)) || (rc = make_operand_map(c, s, &mk, K, D)) ||
+      (rc = make_operand_map(c, s, &mdo, dO, D)) || (rc = make_operand_map(c, s, &mv, V, D)))
     return rc;
-  if (!(s->stages & 64)) {
-    k_bwd_row<D><<<grid, 128, smem_dp_ds<D>(), c->stream>>>(mdo, mv, mk, mp, mds, (const __nv_bfloat16*)dO,
-                                                            (const __nv_bfloat16*)O, (__nv_bfloat16*)dQ, vw.row_info,
-                                                            vw.col_idx, c->L, vw.nnzb, c->scale, c->status_dev);
-    SPION_LAUNCH_CHECK();
-    c->launches += 1;
-    prof_mark(c, SPION_STAGE_BWD_ROW);
-  } else {
-    k_dp_ds<D><<<grid, 128, smem_dp_ds<D>(), c->stream>>>(mdo, mv, mp, mds, (const __nv_bfloat16*)dO,
-                                                          (const __nv_bfloat16*)O, vw.row_info, vw.col_idx, c->L,
-                                                          vw.nnzb, c->scale, c->status_dev);
-    SPION_LAUNCH_CHECK();
-    prof_mark(c, SPION_STAGE_FUSED_DP_DS);
-    k_spmm<D, false, NST_N><<<dim3(vw.nb, c->BH), 128, smem_spmm<D>(NST_N, 1), c->stream>>>(
-        mds, mds, mk, mk, (__nv_bfloat16*)dQ, nullptr, vw.row_ptr, vw.col_idx, nullptr, nullptr, c->L, vw.nnzb,
-        c->status_dev);
-    SPION_LAUNCH_CHECK();
-    c->launches += 2;
-    prof_mark(c, SPION_STAGE_SPMM_DQ);
-  }
-  k_spmm<D, true, NST_T><<<dim3(vw.nb, c->BH), 128, smem_spmm<D>(NST_T, 2), c->stream>>>(
-      mds, mp, mq, mdo, (__nv_bfloat16*)dK, (__nv_bfloat16*)dV, vw.col_ptr, vw.row_idx, vw.csc_pos,
-      s->col_order, c->L, vw.nnzb, c->status_dev);
+  const long long total = (long long)c->BH * vw.nb;
+  const long long row_cap = (long long)s->sms * s->row_ctas, col_cap = (long long)s->sms * s->col_ctas;
+  k_bwd_row<D><<<(int)(total < row_cap ? total : row_cap), ROW_THREADS, smem_row<D>(), c->stream>>>(
+      mdo, mv, mk, mp, mds, (const __nv_bfloat16*)dO, (const __nv_bfloat16*)O, (__nv_bfloat16*)dQ, vw.row_info,
+      vw.col_idx, c->L, vw.nnzb, c->BH, vw.nb, c->heads, c->scale, c->status_dev);
+  SPION_LAUNCH_CHECK();
+  c->launches += 1;
+  prof_mark(c, SPION_STAGE_BWD_ROW);
+  k_bwd_col<D><<<(int)(total < col_cap ? total : col_cap), COL_THREADS, smem_col<D>(), c->stream>>>(
+      mds, mp, mq, mdo, (__nv_bfloat16*)dK, (__nv_bfloat16*)dV, vw.col_ptr, vw.row_idx, vw.csc_pos, s->col_order, c->L,
+      vw.nnzb, c->BH, vw.nb, c->heads, c->status_dev);
   SPION_LAUNCH_CHECK();
   c->launches += 1;
   prof_mark(c, SPION_STAGE_SPMM_DKDV);
@@ -823,10 +731,12 @@ int tc_engine_prepare(spion_ctx* c) {
       return SPION_ERR_CUDA;
     }
     s->encode = (EncodeTiledFn)fn;
-    const char* env = getenv("SPION_TC_STAGES");
-    if (env) s->stages = atoi(env);
-    int rc = (c->d == 64) ? set_attrs<64>() : set_attrs<32>();
-    if (!rc) rc = fused_set_attrs(c->d);
+    if (cudaDeviceGetAttribute(&s->sms, cudaDevAttrMultiProcessorCount, c->device) != cudaSuccess || s->sms < 1) {
+      delete s;
+      return SPION_ERR_CUDA;
+    }
+    int rc = (c->d == 64) ? set_attrs<64>(s) : set_attrs<32>(s);
+    if (!rc) rc = fused_set_attrs(s, c->d);
     if (!rc && cudaMalloc(&s->lse_ws, (size_t)c->BH * c->L * sizeof(float)) != cudaSuccess) rc = SPION_ERR_ALLOC;
     if (rc) { delete s; return rc; }
     s->super = c->bs == 32;
@@ -837,6 +747,8 @@ int tc_engine_prepare(spion_ctx* c) {
     if (rc) return rc;
   }
   const TcView vw = tc_view(c, s);
+  // value-tile rows are 32-bit TMA coordinates: (bh * nnzb + block) * 64 must stay below 2^31
+  if ((unsigned long long)c->BH * (unsigned long long)vw.nnzb * BS >= 0x7fffffffULL) return SPION_ERR_SHAPE;
   if (!s->row_info && cudaMalloc(&s->row_info, (size_t)SPION_MAX_NB * sizeof(int4)) != cudaSuccess) return SPION_ERR_ALLOC;
   k_row_info<<<1, 512, 0, c->stream>>>(vw.row_ptr, vw.col_idx, vw.nb, s->row_info);
   SPION_LAUNCH_CHECK();

@@ -54,6 +54,36 @@ struct ValTile {
 };
 
 
+// Where the [L x D] operand matrix of (b,h) pair `bh` starts inside the 2-D tensor the maps describe.
+//   heads == 0: operands are [BH, L, D]      -> rows bh*L ..,      columns 0 .. D,        row pitch D
+//   heads == H: operands are [B, L, H, D]    -> rows (bh/H)*L ..,  columns (bh%H)*D ..,   row pitch H*D
+// (the second form is what a linear projection writes before any head split; models/attention.py:131-139)
+struct OpPos { int row0, x0, ld; };
+__device__ __forceinline__ OpPos op_pos(int bh, int L, int heads, int D) {
+  if (heads == 0) return OpPos{bh * L, 0, D};
+  const int b = bh / heads;
+  return OpPos{b * L, (bh - b * heads) * D, heads * D};
+}
+
+constexpr int ROW_NCH = 4;              // tiles of a block row that the row kernels handle as one chunk
+
+// One record of the sorted row list: {row_ptr, blocks | row << 16, col0 | col1 << 16, col2 | col3 << 16}.
+struct RowRec {
+  int rp, nblk, r, c01, c23;
+  __device__ RowRec() : rp(0), nblk(0), r(0), c01(0), c23(0) {}
+  __device__ explicit RowRec(int4 ri) : rp(ri.x), nblk(ri.y & 0xffff), r(ri.y >> 16), c01(ri.z), c23(ri.w) {}
+  __device__ int col(int t, const int* __restrict__ col_idx) const {          // block column of the row's t-th block
+    return t < 4 ? (((t & 2) ? c23 : c01) >> ((t & 1) * 16)) & 0xffff : col_idx[rp + t];
+  }
+  __device__ bool single() const { return nblk <= ROW_NCH; }
+  __device__ int chunk() const { return single() ? ROW_NCH : 2; }             // tiles per chunk
+  __device__ int nchunks() const { return (nblk + chunk() - 1) / chunk(); }
+  // Load jobs.  A short row has one (Q, K and V tiles of the row).  A long row has 2*nchunks: the K pairs of
+  // pass A, then the K and V pairs of pass B; job g uses buffers [2*(g&1), 2*(g&1)+1] and the barriers of
+  // that half, so job g+2 is requested as soon as job g has released its half and two jobs are in flight.
+  __device__ int njobs() const { return nblk == 0 ? 0 : (single() ? 1 : 2 * nchunks()); }
+};
+
 // ------------------------------------------------------------------ host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -61,7 +91,8 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
 
 struct TcState {
   EncodeTiledFn encode = nullptr;
-  int stages = 0;               // debugging switches (SPION_TC_STAGES): bit 6 = split row kernels
+  int sms = 0;                  // multiprocessors of the context's device
+  int fwd_ctas = 0, row_ctas = 0, col_ctas = 0;   // resident CTAs per SM of the three persistent kernels
   float* lse_ws = nullptr;      // [BH*L] log-sum-exp workspace for the calls that do not expose it
   int* col_order = nullptr;     // block columns from the longest to the shortest
   int4* row_info = nullptr;     // per block row: {row_ptr, blocks, col0 | col1 << 16, col2 | col3 << 16}: one load instead of two dependent ones
@@ -88,12 +119,15 @@ inline TcView tc_view(const spion_ctx* c, const TcState* s) {
   return TcView{c->row_ptr, c->col_idx, c->col_ptr, c->row_idx, c->csc_pos, nullptr, s->row_info, c->nb, c->nnzb};
 }
 
-inline int make_map(TcState* s, CUtensorMap* m, const void* base, uint64_t rows, uint32_t cols, uint32_t box_rows) {
+// 2-D bf16 tensor of `rows` x `cols` (row-major, contiguous rows) read or written in boxes of
+// box_rows x box_cols; box_cols * 2 bytes is 128 (SWIZZLE_128B) or 64 (SWIZZLE_64B).
+inline int make_map(TcState* s, CUtensorMap* m, const void* base, uint64_t rows, uint32_t cols, uint32_t box_cols,
+                    uint32_t box_rows) {
   const cuuint64_t dims[2] = {cols, rows};
   const cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
-  const cuuint32_t box[2] = {cols, box_rows};
+  const cuuint32_t box[2] = {box_cols, box_rows};
   const cuuint32_t estr[2] = {1, 1};
-  const CUtensorMapSwizzle sw = (cols * 2 == 128) ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+  const CUtensorMapSwizzle sw = (box_cols * 2 == 128) ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
   CUresult r = s->encode(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
                          CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -106,8 +140,15 @@ inline int make_map(TcState* s, CUtensorMap* m, const void* base, uint64_t rows,
 }
 
 
+// Map over one dense operand (Q, K, V, dO): [BH*L, D] rows, or [B*L, H*D] rows with a [64 x D] box at
+// column h*D when the context's operands are in the merged-head form.
+inline int make_operand_map(const spion_ctx* c, TcState* s, CUtensorMap* m, const void* base, int D) {
+  if (c->heads == 0) return make_map(s, m, base, (uint64_t)c->BH * c->L, (uint32_t)D, (uint32_t)D, BS);
+  return make_map(s, m, base, (uint64_t)(c->BH / c->heads) * c->L, (uint32_t)(c->heads * D), (uint32_t)D, BS);
+}
+
 // tc_fused.cu
-int fused_set_attrs(int d);
+int fused_set_attrs(TcState* s, int d);
 int fused_forward(spion_ctx* c, TcState* s, const void* Q, const void* K, const void* V, const float* keypad, void* O,
                   float* lse, void* P64_optional);
 

@@ -6,7 +6,10 @@ Same call shape as the reference's sparse modules -- ``forward(query, key, value
 * fp32 *or* bf16 elements (the reference forces fp32, models/attention.py:88-92);
 * no transposed copies of K (forward) and V (backward) (models/attention_blockcuda.py:48,80);
 * block CSR/CSC fixed once per layer (``set_mask``), not rebuilt per call (:26-43);
-* P is kept as ``[BH, nnzb, bs, bs]`` tiles, which is what TMA and the tensor cores want.
+* P is kept as ``[BH, nnzb, bs, bs]`` tiles, which is what TMA and the tensor cores want;
+* on the tensor-core engine, head-split *views* of the ``[B, L, H*d]`` projections (what
+  ``split_heads`` returns, models/attention.py:131-139) are read in place and the output is written
+  in the same form, so neither the head split nor ``combine_heads`` copies anything.
 
 ``attn`` is returned in that tile layout (use ``to_reference_order`` to compare with the
 reference's element-CSR order).
@@ -50,6 +53,7 @@ class BlockSparseAttention(nn.Module):
         self.fused = can_fuse if fused is None else bool(fused)
         self.nnzb = -1
         self._mask_key = None
+        self._mask_ref = None
         self._fn = _make_function(self)
 
     def __del__(self):
@@ -68,7 +72,10 @@ class BlockSparseAttention(nn.Module):
         self.nnzb = int(lib.spion_pattern_nnzb(self.handle))
         from .pattern import pattern_from_mask
         self._pattern = pattern_from_mask(m8, self.bs)          # block CSR for the helpers above
-        self._mask_key = (mat.data_ptr(), mat._version)
+        # The key names the tensor by address and version; the tensor itself is kept alive so that the
+        # address cannot be handed to another mask while the key is in use.
+        self._mask_key = (mat.data_ptr(), mat._version, tuple(mat.shape), str(mat.device))
+        self._mask_ref = mat
         return self.nnzb
 
     @property
@@ -107,11 +114,40 @@ class BlockSparseAttention(nn.Module):
         return torch.cat(out, dim=1)
 
     # ------------------------------------------------------------------ call
+    def _check_operands(self, query, key, value, mask):
+        """The kernels take sizes from the context, not from the tensors: refuse anything else loudly
+        (a short last batch would otherwise read and write past the buffers)."""
+        want = (self.B, self.H, self.L, self.d)
+        for name, t in (("query", query), ("key", key), ("value", value)):
+            if tuple(t.shape) != want:
+                raise _lib.SpionError(f"{name} has shape {tuple(t.shape)}, this module was built for {want} "
+                                      "(batch_size, num_head, max_seq_len, head_dim of its config)")
+            if t.device != self.device:
+                raise _lib.SpionError(f"{name} is on {t.device}, the module's context is on {self.device}")
+        if self.keypad:
+            if mask is None or tuple(mask.shape) != (self.B, self.L):
+                raise _lib.SpionError(f"key-padding mask must have shape {(self.B, self.L)}")
+
+    def operand_form(self, t) -> int:
+        """0: contiguous [B, H, L, d]; H: the head-split view of a contiguous [B, L, H, d] tensor; -1: neither."""
+        if t.is_contiguous():
+            return 0
+        if tuple(t.stride()) == (self.L * self.H * self.d, self.d, self.H * self.d, 1):
+            return self.H
+        return -1
+
+    def empty_operand(self, heads: int, device):
+        """Uninitialised [B, H, L, d] tensor in the given form (see operand_form)."""
+        if heads:
+            return torch.empty(self.B, self.L, self.H, self.d, dtype=self.dtype, device=device).transpose(1, 2)
+        return torch.empty(self.B, self.H, self.L, self.d, dtype=self.dtype, device=device)
+
     def forward(self, query, key, value, mask=None, mat=None):
-        if mat is not None and (mat.data_ptr(), mat._version) != self._mask_key:
+        if mat is not None and (mat.data_ptr(), mat._version, tuple(mat.shape), str(mat.device)) != self._mask_key:
             self.set_mask(mat)
         if self.nnzb < 0:
             raise _lib.SpionError("no block mask set (call set_mask or pass mat)")
+        self._check_operands(query, key, value, mask)
         pen = None
         if self.keypad:
             pen = (1e6 * (1 - mask.to(torch.float32)))[:, None, :].expand(self.B, self.H, self.L).contiguous()
@@ -141,17 +177,21 @@ def _make_function(mod: BlockSparseAttention):
     class FusedBlockAttnFunction(torch.autograd.Function):
         @staticmethod
         def forward(ctx, query, key, value, pen):
-            q = query.to(mod.dtype).contiguous()
-            k = key.to(mod.dtype).contiguous()
-            v = value.to(mod.dtype).contiguous()
+            q, k, v = query.to(mod.dtype), key.to(mod.dtype), value.to(mod.dtype)
+            # head-split views of [B, L, H*d] projections are read where they lie; anything else is packed
+            heads = mod.H if all(mod.operand_form(t) == mod.H for t in (q, k, v)) else 0
+            if not heads:
+                q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
             dev = q.device
-            O = torch.empty_like(q)
+            O = mod.empty_operand(heads, dev)
             lse = torch.empty(mod.BH * mod.L, dtype=torch.float32, device=dev)
             P = torch.empty(mod.BH * mod.nnz, dtype=mod.dtype, device=dev)     # read again by the backward
             check(lib.spion_set_stream(mod.handle, _lib.current_stream_ptr()))
+            check(lib.spion_set_head_layout(mod.handle, heads), "spion_set_head_layout")
             check(lib.spion_attn_forward_fused(mod.handle, ptr(q), ptr(k), ptr(v), ptr(pen), ptr(O), ptr(lse), ptr(P)),
                   "spion_attn_forward_fused")
             ctx.save_for_backward(q, k, v, O, P)
+            ctx.heads = heads
             ctx.mark_non_differentiable(P)
             return O, P
 
@@ -159,9 +199,15 @@ def _make_function(mod: BlockSparseAttention):
         def backward(ctx, grad_output, grad_p):
             q, k, v, O, P = ctx.saved_tensors
             dev = q.device
-            go = grad_output.to(mod.dtype).contiguous()
-            dq, dk, dv = torch.empty_like(q), torch.empty_like(q), torch.empty_like(q)
+            heads = ctx.heads
+            go = grad_output.to(mod.dtype)
+            if heads and mod.operand_form(go) != heads:
+                go = go.transpose(1, 2).contiguous().transpose(1, 2)
+            elif not heads:
+                go = go.contiguous()
+            dq, dk, dv = (mod.empty_operand(heads, dev) for _ in range(3))
             check(lib.spion_set_stream(mod.handle, _lib.current_stream_ptr()))
+            check(lib.spion_set_head_layout(mod.handle, heads), "spion_set_head_layout")
             dS = torch.empty(mod.BH * mod.nnz, dtype=mod.dtype, device=dev)
             check(lib.spion_attn_backward_ex(mod.handle, ptr(q), ptr(k), ptr(v), ptr(P), ptr(O), ptr(go), ptr(dS),
                                              None, None, ptr(dq), ptr(dk), ptr(dv)), "spion_attn_backward_ex")
@@ -182,6 +228,7 @@ def _make_function(mod: BlockSparseAttention):
             O = torch.empty_like(q)
             scratch = torch.empty(n, dtype=torch.float32, device=dev) if mod.needs_scratch else None
             check(lib.spion_set_stream(mod.handle, _lib.current_stream_ptr()))
+            check(lib.spion_set_head_layout(mod.handle, 0), "spion_set_head_layout")
             check(lib.spion_attn_forward_ex(mod.handle, ptr(q), ptr(k), ptr(v), ptr(pen), ptr(P), ptr(O), ptr(scratch)),
                   "spion_attn_forward_ex")
             ctx.save_for_backward(q, k, v, P, O)

@@ -141,3 +141,27 @@ def test_discover_layers_reference_form():
     for l in range(2):
         o, _, _ = opat.discover_block_mask(maps[l].cpu().numpy(), 32, 0.8)
         assert np.array_equal(mat_lst[0][l].cpu().numpy(), o.astype(np.float32))
+
+
+LARGE = np.load(os.path.join(GOLD, "pattern_reference_large.npz"))
+
+
+@pytest.mark.parametrize("case", sorted({k.split("/")[0] for k in LARGE.files}))
+def test_discovery_at_the_largest_block_counts(case):
+    """nb = 256 and nb = 512 (L = 16384 at block 64 / 32): the masks the reference's own walkers produced,
+    reproduced by the kernels bit for bit, with the CSR / CSC and the element CSR that belong to them."""
+    import hashlib
+    pattern = _pattern_mod()
+    A, L, bs, F, ck = _map(LARGE[case + "/meta"])
+    assert hashlib.sha256(np.ascontiguousarray(A.numpy()).tobytes()).digest() == LARGE[case + "/sha"].tobytes()
+    nb = L // bs
+    gold = np.unpackbits(LARGE[case + "/mat"])[:nb * nb].reshape(nb, nb)
+    q = float(LARGE[case + "/q"])
+    p = pattern.discover_pattern(A.cuda(), bs, q, conv="diag" if ck == 0 else "box", F=F)
+    assert np.array_equal(p.mat.cpu().numpy(), gold)
+    assert abs(float(p.thresh.item()) - float(LARGE[case + "/thresh"])) <= 2e-5 * abs(float(p.thresh.item()))
+    _check_structure(p, gold)
+    sm, off, col, nnz = p.element_csr(repeat=1)
+    assert nnz == int(LARGE[case + "/nnz"])
+    got = np.concatenate([sm.cpu().numpy(), off.cpu().numpy(), col.cpu().numpy()])
+    assert hashlib.sha256(got.tobytes()).digest() == LARGE[case + "/csr_sha"].tobytes()

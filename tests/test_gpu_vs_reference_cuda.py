@@ -104,58 +104,3 @@ def test_sparse_keypad_matches_reference_cuda():
         outs.append((attn, out))
     assert float((outs[0][0] - outs[1][0]).abs().max()) <= 1e-5
     assert float((outs[0][1] - outs[1][1]).abs().max()) <= 1e-4
-
-
-def test_report_time_against_reference_cuda():
-    """Report only: ms per fwd+bwd of the reference's cuSPARSE pipeline and of this library behind the same entry
-    points, on benchmark config 1 (B=8, H=2, L=1024, d=32, block 32, fp32, ~15 % density).  The figures go to
-    gpurun_out/reference_cuda_timing.json; the test only requires that both ran."""
-    import json
-    from spion_b200.attention import Attention
-    ref = _ref_lib("block_attn.so", 4, 9, 14)
-    B, H, L, d, bs, dens = 8, 2, 1024, 32, 32, 0.15
-    BH = B * H
-    Q, K, V, dO = [t.cuda() for t in synthetic.qkv(3, B, H, L, d)]
-    mat = synthetic.band_random_mask(77, L // bs, dens)
-    sm, off, col, nnz = ocsr.element_csr(mat, bs, BH)
-    sm, off, col = [torch.as_tensor(x).cuda() for x in (sm, off, col)]
-    Kt = K.permute(0, 1, 3, 2).contiguous()
-    Vt = V.permute(0, 1, 3, 2).contiguous()
-    dOc = dO.contiguous()
-    attn = torch.empty(BH * nnz, device="cuda"); out = torch.empty(BH * L * d, device="cuda")
-    dP = torch.zeros(BH * nnz, device="cuda"); dS = torch.empty(BH * nnz, device="cuda")
-    dQ, dK, dV = [torch.empty(BH * L * d, device="cuda") for _ in range(3)]
-
-    def step(lib, handle):
-        lib.attn_forward(handle, p(Q), p(Kt), p(V), p(attn), p(out), p(off), p(col), p(sm), nnz)
-        dP.zero_()                                               # the reference's caller zero-fills it every call
-        lib.attn_backward(handle, p(Q), p(K), p(Vt), p(attn), p(dOc), p(dP), p(dS), p(dQ), p(dK), p(dV),
-                          p(off), p(col), p(sm), nnz)
-
-    times = {}
-    mine = Attention._blockcuda_compile_module()
-    for name, lib in (("reference_cuda", ref), ("spion_b200", mine)):
-        h = lib.init(d, L, BH, bs)
-        for _ in range(3):
-            step(lib, h)
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(10):
-            step(lib, h)
-        e1.record()
-        torch.cuda.synchronize()
-        times[name] = e0.elapsed_time(e1) / 10
-        if lib is mine:
-            lib.destroy(h)
-    assert times["reference_cuda"] > 0 and times["spion_b200"] > 0
-    report = {"config": {"B": B, "H": H, "L": L, "d": d, "block": bs, "density": float(mat.mean()), "dtype": "fp32"},
-              "ms_per_fwd_bwd": times, "speedup": times["reference_cuda"] / times["spion_b200"]}
-    print(json.dumps(report))
-    out_dir = os.path.join(os.path.dirname(REF_DIR), os.pardir, "gpurun_out")
-    try:
-        os.makedirs(out_dir, exist_ok=True)
-        with open(os.path.join(out_dir, "reference_cuda_timing.json"), "w") as f:
-            json.dump(report, f)
-    except OSError:
-        pass

@@ -58,3 +58,24 @@ def test_value_layout_helpers():
     t = oatt.block_values_from_dense(P.numpy(), mat, bs)
     assert t.shape == (1, int(mat.sum()), bs, bs)
     assert t[0, 1, 0, 0] == 2 * bs and t[0, 2, 0, 0] == bs * L + bs
+
+
+def test_blockwise_fp64_oracle_matches_dense_masked_closed_form():
+    """The block-row oracle used for the large GPU parity cases, against the dense-masked closed form in
+    fp64 (with and without key padding, block 32 and 64, an empty-looking row of one block)."""
+    for seed, (B, H, L, d, bs, dens, kpm) in enumerate([(1, 2, 256, 32, 32, 0.3, False), (2, 1, 256, 64, 64, 0.5, True),
+                                                        (1, 1, 512, 64, 32, 0.1, False)]):
+        Q, K, V, dO = synthetic.qkv(40 + seed, B, H, L, d)
+        mat = synthetic.band_random_mask(seed, L // bs, dens)
+        kp = synthetic.key_padding(seed, B, L) if kpm else None
+        O, P, gQ, gK, gV = oatt.sparse_attention(Q, K, V, mat, bs, kp, dO, dtype=torch.float64)
+        tiles = oatt.block_values_from_dense(P.numpy(), mat, bs)
+        for b in range(B):
+            for h in range(H):
+                o, pt, dq, dk, dv = oatt.sparse_attention_blockwise(Q[b, h].numpy(), K[b, h].numpy(), V[b, h].numpy(), mat, bs,
+                                                                     None if kp is None else kp[b].numpy(), dO[b, h].numpy())
+                assert np.abs(o - O[b, h].numpy()).max() < 1e-12
+                assert np.abs(pt - tiles[b * H + h]).max() < 1e-13
+                assert np.abs(dq - gQ[b, h].numpy()).max() < 1e-12
+                assert np.abs(dk - gK[b, h].numpy()).max() < 1e-12
+                assert np.abs(dv - gV[b, h].numpy()).max() < 1e-12
