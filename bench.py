@@ -152,6 +152,9 @@ def stage_bytes(stage, BH, L, d, nnz, esz, psz, p_stored=False):
         # fused kernels: operands once, no S/P/dP/dS (P written only when the staged backward needs it)
         "fused_fwd": 4 * ld + 4 * BH * L + (psz * v if p_stored else 0),
         "bwd_row": 5 * ld + 2 * psz * v,
+        # recompute backward: Q, K, V, dO, O in, dQ out (+ lse in, delta out) / Q, K, V, dO in, dK, dV out (+ lse, delta in)
+        "bwd_row_rc": 6 * ld + 8 * BH * L,
+        "bwd_col_rc": 6 * ld + 8 * BH * L,
     }[stage]
 
 
@@ -160,6 +163,10 @@ def stage_flops(stage, BH, d, nnz):
         return 2.0 * nnz * d * BH
     if stage in ("spmm_dkdv", "fused_fwd", "bwd_row"):
         return 4.0 * nnz * d * BH
+    if stage == "bwd_row_rc":
+        return 6.0 * nnz * d * BH
+    if stage == "bwd_col_rc":
+        return 8.0 * nnz * d * BH
     return 0.0
 
 
@@ -472,12 +479,19 @@ def run_sweep_table(args, rank, world, local_rank):
                 mat = synthetic.band_random_mask(2024 + bs, L // bs, dens)
                 nnzb = mod.set_mask(torch.as_tensor(mat).to(dev))
                 n = B * H * nnzb * bs * bs
-                P = torch.empty(n, dtype=torch.bfloat16, device=dev); dS = torch.empty_like(P)
+                stored = args.mode == "stored"
+                P = dS = None
+                if stored:
+                    P = torch.empty(n, dtype=torch.bfloat16, device=dev); dS = torch.empty_like(P)
 
                 def step():
                     check(lib.spion_attn_forward_fused(mod.handle, ptr(Q), ptr(K), ptr(V), None, ptr(O), ptr(lse), ptr(P)))
-                    check(lib.spion_attn_backward_ex(mod.handle, ptr(Q), ptr(K), ptr(V), ptr(P), ptr(O), ptr(dO),
-                                                     ptr(dS), None, None, ptr(dQ), ptr(dK), ptr(dV)))
+                    if stored:
+                        check(lib.spion_attn_backward_ex(mod.handle, ptr(Q), ptr(K), ptr(V), ptr(P), ptr(O), ptr(dO),
+                                                         ptr(dS), None, None, ptr(dQ), ptr(dK), ptr(dV)))
+                    else:
+                        check(lib.spion_attn_backward_fused(mod.handle, ptr(Q), ptr(K), ptr(V), ptr(O), ptr(dO), ptr(lse),
+                                                            None, ptr(dQ), ptr(dK), ptr(dV)))
                 for _ in range(3):
                     step()
                 mod.check_device_status()
@@ -502,6 +516,7 @@ def run_sweep_table(args, rank, world, local_rank):
                           "ms_per_step": head["ms_per_step"], "higher_is_better": True, "scaling": "weak",
                           "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
                           "config": {"workload": "sweep_table", "B": B, "H": H, "d_head": d,
+                                     "mode": "stored P / dS" if args.mode == "stored" else "recompute backward",
                                      "timing": "inputs resident in HBM; working set of every cell larger than L2 "
                                                "except L=1024"},
                           "sweep": rows}))
@@ -517,8 +532,10 @@ def main():
                     choices=sorted(WORKLOADS) + sorted(TRAIN_WORKLOADS) + sorted(REFCUDA_WORKLOADS) +
                     ["pattern_L4096_bs64", "pattern_L1024_bs32", "sweep_table"])
     ap.add_argument("--engine", default="auto", choices=["auto", "simt", "tcgen05", "staged"])
-    ap.add_argument("--mode", default="auto", choices=["auto", "fused", "staged"],
-                    help="fused: S/P/dP/dS stay on chip (tcgen05 engine); staged: one kernel per stage")
+    ap.add_argument("--mode", default="auto", choices=["auto", "fused", "stored", "staged"],
+                    help="fused: S, P, dP, dS stay on chip, the backward rebuilds its tiles (tcgen05 engine); "
+                         "stored: fused forward that stores P, backward kernels that read P and write dS; "
+                         "staged: one kernel per stage")
     ap.add_argument("--repeats", type=int, default=5, help="how often the timed loop of --steps steps is repeated")
     ap.add_argument("--no-graph", action="store_true", help="training workloads: launch the step eagerly")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -567,9 +584,10 @@ def main():
     engine = {"auto": _lib.ENGINE_AUTO, "simt": _lib.ENGINE_SIMT, "tcgen05": _lib.ENGINE_TCGEN05,
               "staged": _lib.ENGINE_SIMT_STAGED}[args.engine]
     mod = BlockSparseAttention(cfg, dtype=tdt, engine=engine, device=dev,
-                               fused=None if args.mode == "auto" else (args.mode == "fused"))
+                               fused=None if args.mode == "auto" else (args.mode in ("fused", "stored")),
+                               return_probs=False, recompute=args.mode != "stored")
     fused_fwd = mod.fused
-    fused_bwd = False            # the backward kernels read the stored P tiles
+    fused_bwd = mod.recompute    # neither P nor dS in HBM
     mat = synthetic.band_random_mask(2024, nb, dens)          # same mask on every rank (one layer)
     nnzb = mod.set_mask(torch.as_tensor(mat).to(dev))
     flops, fused_bytes, nnz = algorithmic(B, H, L, d, bs, nnzb, esz)
@@ -578,7 +596,9 @@ def main():
     hQ, hK, hV, hdO = [t.to(tdt).pin_memory() for t in synthetic.qkv(99 + rank, B, H, L, d)]
     Q, K, V, dO = [t.to(dev) for t in (hQ, hK, hV, hdO)]
     n = BH * nnz
-    P = torch.empty(n, dtype=tdt, device=dev); dS = torch.empty(n, dtype=tdt, device=dev)
+    P = dS = None
+    if not mod.recompute:
+        P = torch.empty(n, dtype=tdt, device=dev); dS = torch.empty(n, dtype=tdt, device=dev)
     O = torch.empty_like(Q); dQ = torch.empty_like(Q); dK = torch.empty_like(Q); dV = torch.empty_like(Q)
     scr = torch.empty(n, dtype=torch.float32, device=dev) if mod.needs_scratch else None
     check(lib.spion_set_stream(mod.handle, _lib.current_stream_ptr()))
@@ -586,6 +606,11 @@ def main():
     lse = torch.empty(BH * L, dtype=torch.float32, device=dev)
 
     def step_device():
+        if fused_bwd:
+            check(lib.spion_attn_forward_fused(mod.handle, ptr(Q), ptr(K), ptr(V), None, ptr(O), ptr(lse), None))
+            check(lib.spion_attn_backward_fused(mod.handle, ptr(Q), ptr(K), ptr(V), ptr(O), ptr(dO), ptr(lse), None,
+                                                ptr(dQ), ptr(dK), ptr(dV)))
+            return
         if fused_fwd:
             check(lib.spion_attn_forward_fused(mod.handle, ptr(Q), ptr(K), ptr(V), None, ptr(O), ptr(lse), ptr(P)))
         else:
@@ -789,9 +814,10 @@ def main():
             "dtype": "bf16" if dt == "bf16" else "f32", "data": "synthetic",
             "config": {"workload": args.workload, "B_per_gpu": B, "H": H, "L": L, "d_head": d, "block": bs,
                        "density": nnzb / float(nb * nb), "nnzb": nnzb, "engine": args.engine,
-                       "mode": "fused forward (P stored) + row / column backward kernels" if fused_fwd else "one kernel per stage",
-                       "l2_policy": "inputs larger than L2 (Q,K,V,dO = %.0f MB, P+dS = %.0f MB per step)"
-                                    % (4 * hQ.numel() * esz / 1e6, 2 * n * esz / 1e6)},
+                       "mode": ("fused forward + recompute backward (no P / dS in HBM)" if fused_bwd else
+                                "fused forward (P stored) + row / column backward kernels" if fused_fwd else "one kernel per stage"),
+                       "l2_policy": "inputs and outputs larger than L2 (Q,K,V,dO + O,dQ,dK,dV = %.0f MB%s per step)"
+                                    % (8 * hQ.numel() * esz / 1e6, "" if fused_bwd else ", P+dS = %.0f MB" % (2 * n * esz / 1e6))},
             "roofline": roofline, "kernels": kern,
             "step_bound": {"ms": step_bound_ms, "frac": step_bound_ms / ms_step,
                            "note": "max(12*nnz*d*BH flop / bf16 peak, 12*L*d*e*BH bytes / HBM peak): fully fused bound"},

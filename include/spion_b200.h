@@ -113,7 +113,9 @@ enum {
   SPION_STAGE_SPMM_DKDV = 10,  /* fused kernels: dK and dV in one kernel           */
   SPION_STAGE_FUSED_FWD = 11,  /* fused kernels: S, softmax, P V in one kernel     */
   SPION_STAGE_BWD_ROW = 12,    /* fused kernels: dP, dS and dQ per block row (P read, dS written) */
-  SPION_STAGE_COUNT = 13
+  SPION_STAGE_BWD_ROW_RC = 13, /* recompute backward, row side: S, dP, dS on chip, dQ and delta written */
+  SPION_STAGE_BWD_COL_RC = 14, /* recompute backward, column side: S, dP, P, dS on chip, dK and dV written */
+  SPION_STAGE_COUNT = 15
 };
 int spion_profile(spion_ctx* ctx, int enable);
 int spion_profile_get(spion_ctx* ctx, int stage, double* total_ms, long long* launches);
@@ -257,6 +259,22 @@ int spion_needs_scratch(const spion_ctx* ctx);
 int spion_supports_fused(const spion_ctx* ctx);   /* 1 if the fused call can run this context */
 int spion_attn_forward_fused(spion_ctx* ctx, const void* Q, const void* K, const void* V,
                              const float* keypad, void* O, float* lse, void* P_optional);
+
+/* Fused native backward (tcgen05 engine only; UNSUPPORTED otherwise): the counterpart of
+ * spion_attn_forward_fused called with P_optional == NULL.  Neither P nor dS exists in global memory:
+ * both kernels rebuild their tiles from Q, K, V, dO and the forward's log-sum-exp (replaces
+ * models/block_attn.cu:489-545 and the two nnz-sized scratch arrays of models/attention_blockcuda.py:84-85).
+ *   O, dO [as Q]   lse [BH*L] as written by spion_attn_forward_fused   keypad as passed to the forward
+ *   dQ, dK, dV (out).  The context keeps one [BH*L] fp32 array (delta) between its two kernels. */
+int spion_attn_backward_fused(spion_ctx* ctx, const void* Q, const void* K, const void* V,
+                              const void* O, const void* dO, const float* lse, const float* keypad,
+                              void* dQ, void* dK, void* dV);
+
+/* Head / batch mean of the probabilities of the current pattern (models/model_transformer.py:137) from
+ * Q, K and the forward's log-sum-exp, without a stored P (tcgen05 engine only): A [L, L] fp32, zero
+ * outside the selected blocks.  With the full mask this is the warm-up phase's attention map. */
+int spion_mean_map_recompute(spion_ctx* ctx, const void* Q, const void* K, const float* lse,
+                             const float* keypad, float* A);
 
 /* Stand-alone sparse row softmax on block tiles (the kernels of models/block_attn.cu:33-130):
  * forward S (fp32 tiles) -> P (context dtype), backward (dP fp32, P) -> dS (context dtype). */

@@ -17,7 +17,7 @@ CONV_DIAG, CONV_BOX = 0, 1
 SELECT_PATHS, SELECT_TOPK = 0, 1
 KIND_DENSE, KIND_DENSE_KPM, KIND_BLOCK, KIND_BLOCK_KPM = 0, 1, 2, 3
 ENGINE_AUTO, ENGINE_SIMT, ENGINE_TCGEN05, ENGINE_SIMT_STAGED = 0, 1, 2, 3
-STAGE_COUNT = 13
+STAGE_COUNT = 15
 
 # name -> (restype, argtypes); every symbol include/spion_b200.h declares
 SIGNATURES = {
@@ -52,6 +52,8 @@ SIGNATURES = {
     "spion_attn_backward_ex": (c_int, [c_void_p] * 13),
     "spion_supports_fused": (c_int, [c_void_p]),
     "spion_attn_forward_fused": (c_int, [c_void_p] * 8),
+    "spion_attn_backward_fused": (c_int, [c_void_p] * 11),
+    "spion_mean_map_recompute": (c_int, [c_void_p] * 6),
     "spion_softmax_forward_ex": (c_int, [c_void_p] * 4),
     "spion_softmax_backward_ex": (c_int, [c_void_p] * 4),
     "spion_static_scratch_capacity": (ctypes.c_size_t, []),

@@ -102,8 +102,10 @@ class Attention(nn.Module):
         model_dev = next(self.parameters()).device
         if self.native:
             from .native import BlockSparseAttention
+            # the layer above ignores the probabilities of the sparse phase (models/model_transformer.py:137 reads
+            # them in the dense phase only): none are stored
             self.block_attn = BlockSparseAttention(config, dtype=self.native_dtype, keypad=self.with_keypad,
-                                                   device=model_dev)
+                                                   device=model_dev, return_probs=False)
             return
         if self.with_keypad:
             block_attn_cpp = Attention._blockcuda_mask_compile_module()

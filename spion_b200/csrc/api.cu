@@ -218,7 +218,7 @@ extern "C" int spion_profile_reset(spion_ctx* c) {
 extern "C" const char* spion_stage_name(int stage) {
   static const char* names[SPION_STAGE_COUNT] = {
       "structure", "sddmm_s", "softmax_fwd", "spmm_o", "sddmm_dp", "softmax_bwd", "spmm_dq", "spmm_dk", "spmm_dv",
-      "fused_dp_ds", "spmm_dkdv", "fused_fwd", "bwd_row"};
+      "fused_dp_ds", "spmm_dkdv", "fused_fwd", "bwd_row", "bwd_row_rc", "bwd_col_rc"};
   return (stage >= 0 && stage < SPION_STAGE_COUNT) ? names[stage] : "?";
 }
 
@@ -496,6 +496,25 @@ extern "C" int spion_attn_forward_fused(spion_ctx* c, const void* Q, const void*
   if (!use_tc(c)) return SPION_ERR_UNSUPPORTED;
   DeviceGuard guard(c->device);
   return tc_engine_forward_fused(c, Q, K, V, keypad, O, lse, P_optional);
+}
+
+extern "C" int spion_attn_backward_fused(spion_ctx* c, const void* Q, const void* K, const void* V, const void* O,
+                                         const void* dO, const float* lse, const float* keypad, void* dQ, void* dK,
+                                         void* dV) {
+  if (!c || !Q || !K || !V || !O || !dO || !lse || !dQ || !dK || !dV) return SPION_ERR_ARG;
+  if (is_dense(c) || c->nnzb < 0) return SPION_ERR_STATE;
+  if (!use_tc(c)) return SPION_ERR_UNSUPPORTED;
+  DeviceGuard guard(c->device);
+  return tc_engine_backward_fused(c, Q, K, V, O, dO, lse, keypad, dQ, dK, dV);
+}
+
+extern "C" int spion_mean_map_recompute(spion_ctx* c, const void* Q, const void* K, const float* lse,
+                                        const float* keypad, float* A) {
+  if (!c || !Q || !K || !lse || !A) return SPION_ERR_ARG;
+  if (is_dense(c) || c->nnzb < 0) return SPION_ERR_STATE;
+  if (!use_tc(c)) return SPION_ERR_UNSUPPORTED;
+  DeviceGuard guard(c->device);
+  return tc_engine_mean_map(c, Q, K, lse, keypad, A);
 }
 
 extern "C" int spion_softmax_forward_ex(spion_ctx* c, const float* S, const float* keypad, void* P) {

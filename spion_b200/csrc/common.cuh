@@ -169,4 +169,7 @@ int tc_engine_backward(spion_ctx* c, const void* Q, const void* K, const void* V
                        const void* dO, void* dS, float* dP_scratch, void* dQ, void* dK, void* dV);
 int tc_engine_forward_fused(spion_ctx* c, const void* Q, const void* K, const void* V, const float* keypad, void* O,
                             float* lse, void* P_optional);
+int tc_engine_backward_fused(spion_ctx* c, const void* Q, const void* K, const void* V, const void* O, const void* dO,
+                             const float* lse, const float* keypad, void* dQ, void* dK, void* dV);
+int tc_engine_mean_map(spion_ctx* c, const void* Q, const void* K, const float* lse, const float* keypad, float* A);
 int tc_engine_wait_selftest(spion_ctx* c, long long limit_cycles);

@@ -602,15 +602,12 @@ template <int D> constexpr size_t smem_col() { return 1024 + (size_t)COL_NST * 2
 // Shared-memory opt-in of the two backward kernels, and how many CTAs of each one SM holds at once
 // (the persistent grids; both kernels take 128 of the 512 tensor-memory columns).
 template <int D>
-int set_attrs(TcState* s) {
+int set_attrs(TcState* s, int device) {
   SPION_CUDA_TRY(cudaFuncSetAttribute(k_bwd_row<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_row<D>()));
   SPION_CUDA_TRY(cudaFuncSetAttribute(k_bwd_col<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_col<D>()));
-  int n = 0;
-  SPION_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, k_bwd_row<D>, ROW_THREADS, smem_row<D>()));
-  s->row_ctas = n > 4 ? 4 : n;
-  SPION_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, k_bwd_col<D>, COL_THREADS, smem_col<D>()));
-  s->col_ctas = n > 4 ? 4 : n;
-  if (s->row_ctas < 1 || s->col_ctas < 1) return SPION_ERR_CUDA;
+  int rc;
+  if ((rc = resident_ctas(k_bwd_row<D>, device, ROW_THREADS, smem_row<D>(), 128, &s->row_ctas))) return rc;
+  if ((rc = resident_ctas(k_bwd_col<D>, device, COL_THREADS, smem_col<D>(), 128, &s->col_ctas))) return rc;
   return SPION_OK;
 }
 
@@ -735,8 +732,10 @@ int tc_engine_prepare(spion_ctx* c) {
       delete s;
       return SPION_ERR_CUDA;
     }
-    int rc = (c->d == 64) ? set_attrs<64>(s) : set_attrs<32>(s);
-    if (!rc) rc = fused_set_attrs(s, c->d);
+    int rc = (c->d == 64) ? set_attrs<64>(s, c->device) : set_attrs<32>(s, c->device);
+    if (!rc) rc = fused_set_attrs(s, c->d, c->device);
+    if (!rc) rc = recompute_set_attrs(s, c->d, c->device);
+    if (!rc && cudaMalloc(&s->delta_ws, (size_t)c->BH * c->L * sizeof(float)) != cudaSuccess) rc = SPION_ERR_ALLOC;
     if (!rc && cudaMalloc(&s->lse_ws, (size_t)c->BH * c->L * sizeof(float)) != cudaSuccess) rc = SPION_ERR_ALLOC;
     if (rc) { delete s; return rc; }
     s->super = c->bs == 32;
@@ -764,6 +763,7 @@ void tc_engine_release(spion_ctx* c) {
   TcState* s = (TcState*)c->tc;
   free_super(s);
   cudaFree(s->lse_ws);
+  cudaFree(s->delta_ws);
   cudaFree(s->row_info);
   cudaFree(s->col_order);
   delete s;
@@ -803,6 +803,19 @@ int tc_engine_forward_fused(spion_ctx* c, const void* Q, const void* K, const vo
   return forward_any(c, Q, K, V, keypad, O, lse, P_optional);
 }
 
+
+int tc_engine_backward_fused(spion_ctx* c, const void* Q, const void* K, const void* V, const void* O, const void* dO,
+                             const float* lse, const float* keypad, void* dQ, void* dK, void* dV) {
+  if (!c->tc) return SPION_ERR_STATE;
+  if (c->nnzb == 0) return SPION_ERR_SHAPE;
+  return recompute_backward(c, (TcState*)c->tc, Q, K, V, O, dO, lse, keypad, dQ, dK, dV);
+}
+
+int tc_engine_mean_map(spion_ctx* c, const void* Q, const void* K, const float* lse, const float* keypad, float* A) {
+  if (!c->tc) return SPION_ERR_STATE;
+  if (c->nnzb == 0) return SPION_ERR_SHAPE;
+  return recompute_mean_map(c, (TcState*)c->tc, Q, K, lse, keypad, A);
+}
 
 int tc_engine_wait_selftest(spion_ctx* c, long long limit_cycles) {
   k_wait_selftest<<<1, 128, 0, c->stream>>>(c->status_dev, limit_cycles);

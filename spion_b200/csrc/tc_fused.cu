@@ -514,26 +514,25 @@ __global__ void __launch_bounds__(FWD_THREADS, 3) k_fwd_fused(const __grid_const
 namespace tc {
 
 // Opt in to the shared memory the kernels need and learn how many CTAs of them one SM holds (the
-// persistent grid is that many per SM; tensor memory allows 512 / 128 = 4).
+// persistent grid is that many per SM).
 template <int D>
-static int fwd_attrs(TcState* s) {
+static int fwd_attrs(TcState* s, int device) {
   const int bytes = (int)fwd_smem_bytes<D>();
-  int occ = 4, n = 0;
+  int occ = 1 << 30, n = 0, rc;
 #define SPION_FWD_ATTR(SP, SB)                                                                                      \
   SPION_CUDA_TRY(cudaFuncSetAttribute(k_fwd_fused<D, SP, SB>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes)); \
-  SPION_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, k_fwd_fused<D, SP, SB>, FWD_THREADS, bytes));    \
+  if ((rc = resident_ctas(k_fwd_fused<D, SP, SB>, device, FWD_THREADS, (size_t)bytes, 128, &n))) return rc;         \
   occ = n < occ ? n : occ;
   SPION_FWD_ATTR(false, false)
   SPION_FWD_ATTR(true, false)
   SPION_FWD_ATTR(false, true)
   SPION_FWD_ATTR(true, true)
 #undef SPION_FWD_ATTR
-  if (occ < 1) return SPION_ERR_CUDA;
   s->fwd_ctas = occ;
   return SPION_OK;
 }
 
-int fused_set_attrs(TcState* s, int d) { return d == 64 ? fwd_attrs<64>(s) : fwd_attrs<32>(s); }
+int fused_set_attrs(TcState* s, int d, int device) { return d == 64 ? fwd_attrs<64>(s, device) : fwd_attrs<32>(s, device); }
 
 template <int D>
 static int fwd_launch(spion_ctx* c, TcState* s, const void* Q, const void* K, const void* V, const float* keypad,

@@ -92,7 +92,9 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
 struct TcState {
   EncodeTiledFn encode = nullptr;
   int sms = 0;                  // multiprocessors of the context's device
-  int fwd_ctas = 0, row_ctas = 0, col_ctas = 0;   // resident CTAs per SM of the three persistent kernels
+  int fwd_ctas = 0, row_ctas = 0, col_ctas = 0;   // resident CTAs per SM of the persistent kernels
+  int rc_row_ctas = 0, rc_col_ctas = 0;           // ... of the two recompute backward kernels
+  float* delta_ws = nullptr;    // [BH*L] delta_i = sum_n dO_in O_in, written by the row kernel, read by the column kernel
   float* lse_ws = nullptr;      // [BH*L] log-sum-exp workspace for the calls that do not expose it
   int* col_order = nullptr;     // block columns from the longest to the shortest
   int4* row_info = nullptr;     // per block row: {row_ptr, blocks, col0 | col1 << 16, col2 | col3 << 16}: one load instead of two dependent ones
@@ -140,6 +142,29 @@ inline int make_map(TcState* s, CUtensorMap* m, const void* base, uint64_t rows,
 }
 
 
+// How many CTAs of a persistent kernel one SM holds at once: the limits are shared memory (dynamic +
+// static + the per-CTA reservation), registers (allocated per warp in units of 256) and tensor memory
+// (512 columns).  Computed from the device's limits and the kernel's own attributes.
+template <typename K>
+inline int resident_ctas(K kernel, int device, int threads, size_t dyn_smem, int tmem_cols, int* out) {
+  cudaFuncAttributes fa;
+  if (cudaFuncGetAttributes(&fa, kernel) != cudaSuccess) return SPION_ERR_CUDA;
+  int smem_sm = 0, smem_resv = 0, regs_sm = 0;
+  if (cudaDeviceGetAttribute(&smem_sm, cudaDevAttrMaxSharedMemoryPerMultiprocessor, device) != cudaSuccess ||
+      cudaDeviceGetAttribute(&smem_resv, cudaDevAttrReservedSharedMemoryPerBlock, device) != cudaSuccess ||
+      cudaDeviceGetAttribute(&regs_sm, cudaDevAttrMaxRegistersPerMultiprocessor, device) != cudaSuccess)
+    return SPION_ERR_CUDA;
+  const size_t per_cta = dyn_smem + fa.sharedSizeBytes + (size_t)smem_resv;
+  const int warps = (threads + 31) / 32;
+  const int regs_warp = ((fa.numRegs * 32 + 255) / 256) * 256;
+  int n = (int)((size_t)smem_sm / per_cta);
+  if (regs_warp > 0 && regs_sm / (regs_warp * warps) < n) n = regs_sm / (regs_warp * warps);
+  if (tmem_cols > 0 && 512 / tmem_cols < n) n = 512 / tmem_cols;
+  if (n < 1) return SPION_ERR_CUDA;
+  *out = n;
+  return SPION_OK;
+}
+
 // Map over one dense operand (Q, K, V, dO): [BH*L, D] rows, or [B*L, H*D] rows with a [64 x D] box at
 // column h*D when the context's operands are in the merged-head form.
 inline int make_operand_map(const spion_ctx* c, TcState* s, CUtensorMap* m, const void* base, int D) {
@@ -147,8 +172,15 @@ inline int make_operand_map(const spion_ctx* c, TcState* s, CUtensorMap* m, cons
   return make_map(s, m, base, (uint64_t)(c->BH / c->heads) * c->L, (uint32_t)(c->heads * D), (uint32_t)D, BS);
 }
 
+// tc_recompute.cu
+int recompute_set_attrs(TcState* s, int d, int device);
+int recompute_backward(spion_ctx* c, TcState* s, const void* Q, const void* K, const void* V, const void* O,
+                       const void* dO, const float* lse, const float* keypad, void* dQ, void* dK, void* dV);
+int recompute_mean_map(spion_ctx* c, TcState* s, const void* Q, const void* K, const float* lse, const float* keypad,
+                       float* A);
+
 // tc_fused.cu
-int fused_set_attrs(TcState* s, int d);
+int fused_set_attrs(TcState* s, int d, int device);
 int fused_forward(spion_ctx* c, TcState* s, const void* Q, const void* K, const void* V, const float* keypad, void* O,
                   float* lse, void* P64_optional);
 

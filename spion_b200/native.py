@@ -25,9 +25,18 @@ from ._lib import check, lib, ptr
 _DTYPES = {torch.float32: _lib.F32, torch.bfloat16: _lib.BF16}
 
 
+class ProbsHandle:
+    """What a fused forward that stores no probabilities hands back in place of them: the operands and the
+    per-row log-sum-exp from which any part of P can be rebuilt (``mean_attention_map`` does, for the
+    warm-up phase).  Valid until the module's next forward."""
+
+    def __init__(self, q, k, lse, pen, heads):
+        self.q, self.k, self.lse, self.pen, self.heads = q, k, lse, pen, heads
+
+
 class BlockSparseAttention(nn.Module):
     def __init__(self, config, dtype=torch.float32, keypad: bool = False, engine: int = _lib.ENGINE_AUTO,
-                 device=None, fused=None):
+                 device=None, fused=None, return_probs: bool = True, recompute: bool = True):
         super().__init__()
         self.d = config["head_dim"]
         self.H = config["num_head"]
@@ -51,6 +60,13 @@ class BlockSparseAttention(nn.Module):
         if fused and not can_fuse:
             raise _lib.SpionError("fused kernels need the tcgen05 engine (bf16, block 64, head_dim 32/64)")
         self.fused = can_fuse if fused is None else bool(fused)
+        # return_probs=False (fused kernels only): the forward writes O and the log-sum-exp, nothing of size
+        # nnz, and ``forward`` returns a ProbsHandle instead of the [BH, nnzb, bs, bs] tiles
+        self.return_probs = bool(return_probs) or not self.fused
+        # recompute=True (fused kernels): the backward rebuilds P and dS on chip from the log-sum-exp;
+        # False: it reads the stored P tiles and writes dS tiles (spion_attn_backward_ex)
+        self.recompute = bool(recompute) and self.fused
+        self.last = None
         self.nnzb = -1
         self._mask_key = None
         self._mask_ref = None
@@ -82,10 +98,20 @@ class BlockSparseAttention(nn.Module):
     def nnz(self) -> int:
         return self.nnzb * self.bs * self.bs
 
-    def mean_attention_map(self, P_tiles: torch.Tensor) -> torch.Tensor:
-        """A = mean over (b,h) of the probabilities this module returned ([BH, nnzb, bs, bs] tiles) as an
-        [L, L] fp32 map (zero outside the mask): what the encoder hands to pattern discovery
-        (models/model_transformer.py:137), without a dense [B, H, L, L] tensor."""
+    def mean_attention_map(self, P_tiles) -> torch.Tensor:
+        """A = mean over (b,h) of the probabilities of the last forward as an [L, L] fp32 map (zero outside the
+        mask): what the encoder hands to pattern discovery (models/model_transformer.py:137), without a dense
+        [B, H, L, L] tensor.  ``P_tiles`` is what ``forward`` returned beside the output: the
+        [BH, nnzb, bs, bs] tiles, or a ProbsHandle, in which case the map is rebuilt from Q, K and the
+        log-sum-exp and no probability was ever stored."""
+        if isinstance(P_tiles, ProbsHandle):
+            h = P_tiles
+            A = torch.empty(self.L, self.L, dtype=torch.float32, device=h.q.device)
+            check(lib.spion_set_stream(self.handle, _lib.current_stream_ptr()))
+            check(lib.spion_set_head_layout(self.handle, h.heads), "spion_set_head_layout")
+            check(lib.spion_mean_map_recompute(self.handle, ptr(h.q), ptr(h.k), ptr(h.lse), ptr(h.pen), ptr(A)),
+                  "spion_mean_map_recompute")
+            return A
         pat = self._pattern
         A = torch.empty(self.L, self.L, dtype=torch.float32, device=P_tiles.device)
         check(lib.spion_mean_map_tiles(ptr(P_tiles), _DTYPES[self.dtype], ptr(pat.blk_row), ptr(pat.col_idx), self.bs,
@@ -151,18 +177,22 @@ class BlockSparseAttention(nn.Module):
         pen = None
         if self.keypad:
             pen = (1e6 * (1 - mask.to(torch.float32)))[:, None, :].expand(self.B, self.H, self.L).contiguous()
-        return self._fn.apply(query, key, value, pen)
+        out, P = self._fn.apply(query, key, value, pen)
+        if not self.return_probs:
+            return out, self.last
+        return out, P
 
 
 class DenseViaBlocks(nn.Module):
     """Warm-up (dense) attention through the same block kernels with the full mask: the dense phase of
     the reference (models/attention_cuda.py) without fp32 up-casts, transposed copies or a
     [B, H, L, L] tensor in the reference's S^T layout.  ``forward(query, key, value, mask)`` ->
-    ``(out, P_tiles)``; ``mean_attention_map(P_tiles)`` gives the [L, L] map for pattern discovery."""
+    ``(out, probs)``; ``mean_attention_map(probs)`` gives the [L, L] map for pattern discovery.  On the
+    tensor-core engine ``probs`` is a ProbsHandle: no probability is written in the whole dense phase."""
 
-    def __init__(self, config, dtype=torch.float32, keypad: bool = False, device=None):
+    def __init__(self, config, dtype=torch.float32, keypad: bool = False, device=None, return_probs: bool = False):
         super().__init__()
-        self.block = BlockSparseAttention(config, dtype=dtype, keypad=keypad, device=device)
+        self.block = BlockSparseAttention(config, dtype=dtype, keypad=keypad, device=device, return_probs=return_probs)
         nb = config["max_seq_len"] // config["block_size"]
         self.block.set_mask(torch.ones(nb, nb, dtype=torch.uint8, device=self.block.device))
 
@@ -185,19 +215,26 @@ def _make_function(mod: BlockSparseAttention):
             dev = q.device
             O = mod.empty_operand(heads, dev)
             lse = torch.empty(mod.BH * mod.L, dtype=torch.float32, device=dev)
-            P = torch.empty(mod.BH * mod.nnz, dtype=mod.dtype, device=dev)     # read again by the backward
+            # the probabilities are stored only for callers that want them back; the backward rebuilds its tiles
+            want_p = mod.return_probs or not mod.recompute
+            P = torch.empty(mod.BH * mod.nnz, dtype=mod.dtype, device=dev) if want_p else None
             check(lib.spion_set_stream(mod.handle, _lib.current_stream_ptr()))
             check(lib.spion_set_head_layout(mod.handle, heads), "spion_set_head_layout")
             check(lib.spion_attn_forward_fused(mod.handle, ptr(q), ptr(k), ptr(v), ptr(pen), ptr(O), ptr(lse), ptr(P)),
                   "spion_attn_forward_fused")
-            ctx.save_for_backward(q, k, v, O, P)
+            ctx.save_for_backward(q, k, v, O, lse)
+            ctx.pen = pen
             ctx.heads = heads
+            ctx.P = None if mod.recompute else P
+            mod.last = ProbsHandle(q.detach(), k.detach(), lse, pen, heads)
+            if P is None:
+                P = torch.empty(0, dtype=mod.dtype, device=dev)
             ctx.mark_non_differentiable(P)
             return O, P
 
         @staticmethod
         def backward(ctx, grad_output, grad_p):
-            q, k, v, O, P = ctx.saved_tensors
+            q, k, v, O, lse = ctx.saved_tensors
             dev = q.device
             heads = ctx.heads
             go = grad_output.to(mod.dtype)
@@ -208,9 +245,13 @@ def _make_function(mod: BlockSparseAttention):
             dq, dk, dv = (mod.empty_operand(heads, dev) for _ in range(3))
             check(lib.spion_set_stream(mod.handle, _lib.current_stream_ptr()))
             check(lib.spion_set_head_layout(mod.handle, heads), "spion_set_head_layout")
-            dS = torch.empty(mod.BH * mod.nnz, dtype=mod.dtype, device=dev)
-            check(lib.spion_attn_backward_ex(mod.handle, ptr(q), ptr(k), ptr(v), ptr(P), ptr(O), ptr(go), ptr(dS),
-                                             None, None, ptr(dq), ptr(dk), ptr(dv)), "spion_attn_backward_ex")
+            if ctx.P is None:
+                check(lib.spion_attn_backward_fused(mod.handle, ptr(q), ptr(k), ptr(v), ptr(O), ptr(go), ptr(lse),
+                                                    ptr(ctx.pen), ptr(dq), ptr(dk), ptr(dv)), "spion_attn_backward_fused")
+            else:
+                dS = torch.empty(mod.BH * mod.nnz, dtype=mod.dtype, device=dev)
+                check(lib.spion_attn_backward_ex(mod.handle, ptr(q), ptr(k), ptr(v), ptr(ctx.P), ptr(O), ptr(go), ptr(dS),
+                                                 None, None, ptr(dq), ptr(dk), ptr(dv)), "spion_attn_backward_ex")
             return dq, dk, dv, None
 
     if mod.fused:

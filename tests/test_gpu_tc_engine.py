@@ -23,12 +23,19 @@ def rel(a, b):
 
 
 def check(B, H, L, d, bs, mat, keypad=None, seed=5):
+    """Both backward paths of the engine: tiles rebuilt on chip from the log-sum-exp (the default), and the
+    kernels that read stored P tiles and write dS tiles (spion_attn_backward_ex)."""
+    for recompute in (True, False):
+        check_one(B, H, L, d, bs, mat, keypad, seed, recompute)
+
+
+def check_one(B, H, L, d, bs, mat, keypad, seed, recompute):
     from spion_b200 import _lib
     from spion_b200.native import BlockSparseAttention
     Q, K, V, dO = [t.to(torch.bfloat16) for t in synthetic.qkv(seed, B, H, L, d)]
     mod = BlockSparseAttention(cfg(B, H, L, d, bs), dtype=torch.bfloat16, keypad=keypad is not None,
-                               engine=_lib.ENGINE_TCGEN05)
-    assert mod.fused
+                               engine=_lib.ENGINE_TCGEN05, recompute=recompute)
+    assert mod.fused and mod.recompute == recompute
     q = Q.cuda().requires_grad_(True); k = K.cuda().requires_grad_(True); v = V.cuda().requires_grad_(True)
     out, P = mod(q, k, v, None if keypad is None else keypad.cuda(), torch.as_tensor(mat).cuda())
     out.backward(dO.cuda())
@@ -109,3 +116,37 @@ def test_mean_map_from_tiles_and_dense_via_blocks(dtype):
     assert float((As * (1 - M)).abs().max()) == 0.0
     _, Pm = oatt.sparse_attention(Q.float(), K.float(), V.float(), mat, bs)
     assert float((As - Pm.mean(0).mean(0)).abs().max()) <= tol
+
+
+@pytest.mark.parametrize("d,bs", [(64, 64), (32, 64), (64, 32)])
+def test_mean_map_rebuilt_from_lse(d, bs):
+    """The warm-up map A = mean_bh P from Q, K and the log-sum-exp (no stored probabilities): full mask, with
+    key padding, with merged-head operands, and on a sparse 32-wide mask (zero outside the selected blocks)."""
+    from spion_b200.native import BlockSparseAttention, DenseViaBlocks, ProbsHandle
+    B, H, L = 3, 1, 256                                             # odd number of (b,h) matrices
+    Q, K, V = [t.to(torch.bfloat16) for t in synthetic.qkv(13, B, H, L, d, n=3)]
+    kp = synthetic.key_padding(6, B, L)
+    for keypad in (None, kp):
+        mod = DenseViaBlocks(cfg(B, H, L, d, bs), dtype=torch.bfloat16, keypad=keypad is not None)
+        out, probs = mod(Q.cuda(), K.cuda(), V.cuda(), None if keypad is None else keypad.cuda())
+        assert isinstance(probs, ProbsHandle)
+        A = mod.mean_attention_map(probs)
+        mod.block.check_device_status()
+        O, Pd = oatt.sparse_attention(Q.float(), K.float(), V.float(), np.ones((L // bs, L // bs), np.uint8), bs, keypad)
+        want = Pd.mean(0).mean(0)
+        assert float((A.cpu() - want).abs().max()) <= 2e-2 * float(want.max())
+        assert rel(out, O) <= REL
+    # sparse mask, merged-head operands, two heads
+    B, H = 2, 2
+    Q, K, V = [t.to(torch.bfloat16) for t in synthetic.qkv(14, B, H, L, d, n=3)]
+    mat = synthetic.band_random_mask(3, L // bs, 0.4)
+    sp = BlockSparseAttention(cfg(B, H, L, d, bs), dtype=torch.bfloat16, return_probs=False)
+    merged = [t.cuda().transpose(1, 2).contiguous().transpose(1, 2) for t in (Q, K, V)]
+    out, probs = sp(*merged, None, torch.as_tensor(mat).cuda())
+    assert isinstance(probs, ProbsHandle) and probs.heads == H
+    A = sp.mean_attention_map(probs).cpu()
+    sp.check_device_status()
+    _, Pm = oatt.sparse_attention(Q.float(), K.float(), V.float(), mat, bs)
+    want = Pm.mean(0).mean(0)
+    assert float((A * (1 - oatt.expand_mask(mat, bs))).abs().max()) == 0.0
+    assert float((A - want).abs().max()) <= 2e-2 * float(want.max())
