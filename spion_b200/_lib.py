@@ -10,7 +10,8 @@ import os
 from ctypes import c_double, c_int, c_longlong, c_void_p
 
 LIB_DIR = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib")
-LIB_PATH = os.path.join(LIB_DIR, "libspion_b200.so")
+# SPION_B200_LIBRARY names another build of the same library (e.g. one compiled with developer macros)
+LIB_PATH = os.environ.get("SPION_B200_LIBRARY") or os.path.join(LIB_DIR, "libspion_b200.so")
 
 F32, BF16 = 0, 1
 CONV_DIAG, CONV_BOX = 0, 1

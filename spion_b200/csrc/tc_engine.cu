@@ -30,6 +30,10 @@
 
 using namespace tc;
 
+#ifdef SPION_TRACE
+SPION_TRACE_SETTER(spion_debug_trace_engine)
+#endif
+
 namespace {
 
 constexpr int ROW_THREADS = 128;

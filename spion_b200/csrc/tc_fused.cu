@@ -17,9 +17,13 @@
 
 using namespace tc;
 
+#ifdef SPION_TRACE
+SPION_TRACE_SETTER(spion_debug_trace_fused)
+#endif
+
 namespace {
 
-constexpr int FWD_THREADS = 128;
+constexpr int FWD_THREADS = 160;           // warps 0-3: one TMEM quadrant each (math); warp 4: TMA loads, MMA issue, tile stores
 constexpr int FWD_NCH = ROW_NCH;           // tiles of a row that fits in one chunk
 // TMEM (128 columns): S pairs at [0,64) and [64,128); O overwrites [0,64) once P has been extracted.
 
@@ -36,6 +40,18 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
+// 32 consecutive values (16 packed words) of row i, columns [32 g, 32 g + 32), into the same image.
+__device__ __forceinline__ void store_half_row_swizzled(uint32_t tile, int i, int g, const uint32_t (&w)[16]) {
+#pragma unroll
+  for (int cc = 0; cc < 4; ++cc) {
+    const int c = g * 4 + cc;
+    const uint32_t addr = tile + i * 128 + ((c ^ (i & 7)) << 4);
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[4 * cc]), "r"(w[4 * cc + 1]),
+                 "r"(w[4 * cc + 2]), "r"(w[4 * cc + 3])
+                 : "memory");
+  }
+}
+
 __device__ __forceinline__ void store_row_swizzled(uint32_t tile, int i, const uint32_t (&w)[32]) {
 #pragma unroll
   for (int c = 0; c < 8; ++c) {
@@ -46,11 +62,13 @@ __device__ __forceinline__ void store_row_swizzled(uint32_t tile, int i, const u
   }
 }
 
-// Persistent CTAs (4 warps, one per TMEM quadrant; the grid is the number of CTAs the device holds at
-// once): CTA i works on units i, i + grid, i + 2 grid, ... of the list (sorted block row, bh), bh
-// fastest.  Barriers are initialised and tensor memory is allocated once per CTA; the operand tiles of
-// the next unit are requested as soon as the last MMA of the current one has retired, so they arrive
-// while the current unit's output rows are written.
+// Persistent CTAs (the grid is the number of CTAs the device holds at once): CTA i works on units i,
+// i + grid, i + 2 grid, ... of the list (sorted block row, bh), bh fastest.  Four math warps (one per TMEM
+// quadrant) do the softmax arithmetic and write the output rows; a fifth, the control warp, issues every
+// TMA load, MMA and tile store, so the math warps never spend issue slots or wait on a copy engine.
+// Barriers are initialised and tensor memory is allocated once per CTA; the operand tiles of the next
+// unit are requested as soon as the last MMA of the current one has retired, so they arrive while the
+// current unit's output rows are written.
 // A row of the block is owned by two threads of one warp (lane l: even tiles, lane l+16: odd tiles), so
 // the row statistics need only one warp shuffle.  Rows with at most 4 blocks are done in one chunk (S in
 // all 128 columns, O then overwrites the first 64); longer rows stream chunks of 2 tiles through columns
@@ -86,14 +104,16 @@ __global__ void __launch_bounds__(FWD_THREADS, 3) k_fwd_fused(const __grid_const
   uint32_t* slot_ptr = reinterpret_cast<uint32_t*>(smem_raw + (slot - raw));
   __shared__ int s_abort;
 
-  const int tid = threadIdx.x, q = tid >> 5, lane = tid & 31;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const bool ctl = warp == 4;                                  // control warp: no arithmetic, no TMEM reads
+  const int q = warp & 3;                                      // TMEM quadrant of a math warp
   const int hf = lane >> 4;                                    // 0: even tiles, 1: odd tiles
   const int row = q * 16 + (lane & 15);                        // row of the block this thread owns
   const int total = nrows * BH;
   constexpr uint32_t ncols = 128u;
   constexpr uint32_t o_col = 0u;
 
-  // Called by all lanes of warp 0: lane 0 announces the bytes, then one lane per tile issues its copy
+  // Called by all lanes of the control warp: lane 0 announces the bytes, then one lane per tile issues its copy
   // (a single thread needs about 0.1 us per copy; a row has up to nine).
   auto issue_job = [&](const RowRec& R, int bh, int g) {
     const bool single = R.single();
@@ -121,7 +141,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 3) k_fwd_fused(const __grid_const
   int bh = 0;
   if (u < total) { const int rank = u / BH; R = RowRec(row_info[rank]); bh = u - rank * BH; }
 
-  if (q == 0) {
+  if (ctl) {
     if (lane == 0) {
       s_abort = *reinterpret_cast<volatile int*>(status);
       mbar_init(bar_k0, 1);
@@ -140,7 +160,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 3) k_fwd_fused(const __grid_const
   }
   __syncthreads();
   if (s_abort != 0) return;
-  if (q == 0) {
+  if (ctl) {
     tmem_alloc(slot, ncols);
     tmem_relinquish();
   }
@@ -158,7 +178,9 @@ __global__ void __launch_bounds__(FWD_THREADS, 3) k_fwd_fused(const __grid_const
   uint32_t pk = 0, pv = 0, ps = 0, po = 0;
   bool ok = true;
 
-  for (; u < total && ok; u += gridDim.x) {
+  int ord = 0;
+  for (; u < total && ok; u += gridDim.x, ++ord) {
+    SPION_STAMP(ord, 0);
     // the unit after this one (its operands are requested before this unit's output is written)
     const int un = u + (int)gridDim.x;
     const bool has_next = un < total;
@@ -185,7 +207,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 3) k_fwd_fused(const __grid_const
 
     // All buffers of this unit are free (its last MMA has retired): ask for the next unit's first tiles.
     auto prefetch_next = [&]() {
-      if (q == 0 && has_next) {
+      if (ctl && has_next) {
         if (STORE_P) {                                           // the tile stores must have read their tiles
           if (lane == 0) bulk_wait_read_all();
           __syncwarp();
@@ -195,7 +217,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 3) k_fwd_fused(const __grid_const
       }
     };
 
-    // tid 0: wait for the K tiles of job g (already requested) and issue the S MMAs of its chunk into
+    // control lane: wait for the K tiles of job g (already requested) and issue the S MMAs of its chunk into
     // accumulator columns col(t); the commit arrives on bar
     auto issue_s = [&](int g, uint32_t pair_stride, uint32_t col0, uint32_t bar) -> bool {
       const int ch = (single || g < nchunks) ? g : g - nchunks;
@@ -204,11 +226,13 @@ __global__ void __launch_bounds__(FWD_THREADS, 3) k_fwd_fused(const __grid_const
       if (!mbar_wait(hb ? bar_k1 : bar_k0, (pk >> hb) & 1)) { report(status, ERR_LOAD_WAIT); return false; }
       pk ^= 1u << hb;
       tc_fence_after();
-      for (int t = 0; t < nt; ++t) {
+      const uint64_t dq0 = T::kmajor(sQ, 0);
+      uint64_t dk0 = T::kmajor(sK + b0 * T::BYTES, 0);
+      for (int t = 0; t < nt; ++t, dk0 = desc_advance(dk0, T::BYTES)) {
         const uint32_t d_addr = tmem + ((uint32_t)((t & 1) * 16) << 16) + col0 + (uint32_t)(t >> 1) * pair_stride;
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk)
-          mma_bf16(d_addr, T::kmajor(sQ, kk), T::kmajor(sK + (b0 + t) * T::BYTES, kk), IDESC_S, kk > 0);
+          mma_bf16(d_addr, desc_advance(dq0, kk * T::K_STEP), desc_advance(dk0, kk * T::K_STEP), IDESC_S, kk > 0);
       }
       mma_commit(bar);
       return true;
@@ -234,8 +258,15 @@ __global__ void __launch_bounds__(FWD_THREADS, 3) k_fwd_fused(const __grid_const
             tmem_ld_wait();
             if (mine && quarter_ok(rp + t0 + t, half)) {
               if (!kp) {                                            // the scale is positive: compare raw scores
+                float ma = mraw, mb = -INFINITY, mc = -INFINITY, md = -INFINITY;   // four chains instead of one
 #pragma unroll
-                for (int j = 0; j < 32; j += 2) mraw = fmaxf(mraw, fmaxf(__uint_as_float(v[j]), __uint_as_float(v[j + 1])));
+                for (int j = 0; j < 32; j += 8) {
+                  ma = fmaxf(ma, fmaxf(__uint_as_float(v[j]), __uint_as_float(v[j + 1])));
+                  mb = fmaxf(mb, fmaxf(__uint_as_float(v[j + 2]), __uint_as_float(v[j + 3])));
+                  mc = fmaxf(mc, fmaxf(__uint_as_float(v[j + 4]), __uint_as_float(v[j + 5])));
+                  md = fmaxf(md, fmaxf(__uint_as_float(v[j + 6]), __uint_as_float(v[j + 7])));
+                }
+                mraw = fmaxf(fmaxf(ma, mb), fmaxf(mc, md));
               } else {
 #pragma unroll
                 for (int j = 0; j < 32; ++j)
@@ -286,43 +317,48 @@ __global__ void __launch_bounds__(FWD_THREADS, 3) k_fwd_fused(const __grid_const
         const int t = 2 * p + hf;
         const bool mine = t < nt;
         const int c = mine ? col_of(t0 + t) : 0;
-        uint32_t w[32];
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
-          uint32_t v[32];
+          uint32_t v[32], w[16];
           tmem_ld32(t_lane + colbase + p * 64 + half * 32, v);
           tmem_ld_wait();
           if (mine && quarter_ok(rp + t0 + t, half)) {
+            float la = 0.f, lb = 0.f, lc = 0.f, ld = 0.f;               // four independent running sums
 #pragma unroll
             for (int j = 0; j < 32; j += 2) {
               float h0 = m2, h1 = m2;
               if (kp) { h0 = fmaf(kp[c * BS + half * 32 + j], LOG2E, m2); h1 = fmaf(kp[c * BS + half * 32 + j + 1], LOG2E, m2); }
               const float e0 = ex2(fmaf(__uint_as_float(v[j]), sc2, -h0)), e1 = ex2(fmaf(__uint_as_float(v[j + 1]), sc2, -h1));
-              l_part += e0 + e1;
-              w[half * 16 + (j >> 1)] = pack_bf16(e0, e1);
+              if ((j & 6) == 0) la += e0 + e1;
+              else if ((j & 6) == 2) lb += e0 + e1;
+              else if ((j & 6) == 4) lc += e0 + e1;
+              else ld += e0 + e1;
+              w[j >> 1] = pack_bf16(e0, e1);
             }
+            l_part += (la + lb) + (lc + ld);
           } else {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) w[half * 16 + j] = 0u;
+            for (int j = 0; j < 16; ++j) w[j] = 0u;
           }
+          if (mine) store_half_row_swizzled(sP + (b0 + t) * VT_BYTES, row, half, w);
         }
-        if (mine) store_row_swizzled(sP + (b0 + t) * VT_BYTES, row, w);
       }
     };
 
-    // tid 0: O += P V for the tiles of one chunk (after its V tiles have arrived), then the P tile stores.
+    // control lane: O += P V for the tiles of one chunk (after its V tiles have arrived), then the P tile stores.
     // Every tile of the row accumulates into the one [64 x D] accumulator at lane offset 0.
     auto issue_pv = [&](int hb, int t0, int nt, bool first_chunk) -> bool {
       const int b0 = 2 * hb;
       if (!mbar_wait(hb ? bar_v1 : bar_v0, (pv >> hb) & 1)) { report(status, ERR_LOAD_WAIT); return false; }
       pv ^= 1u << hb;
       tc_fence_after();
-      for (int t = 0; t < nt; ++t) {
+      uint64_t dp0 = ValTile::kmajor(sP + b0 * VT_BYTES, 0), dv0 = T::mnmajor(sV + b0 * T::BYTES, 0);
+      for (int t = 0; t < nt; ++t, dp0 = desc_advance(dp0, VT_BYTES), dv0 = desc_advance(dv0, T::BYTES)) {
         const uint32_t first = (first_chunk && t == 0) ? 0u : 1u;
 #pragma unroll
         for (int kk = 0; kk < BS / 16; ++kk)
-          mma_bf16(tmem + o_col, ValTile::kmajor(sP + (b0 + t) * VT_BYTES, kk), T::mnmajor(sV + (b0 + t) * T::BYTES, kk),
-                   IDESC_O, (kk > 0) ? 1u : first);
+          mma_bf16(tmem + o_col, desc_advance(dp0, kk * ValTile::K_STEP), desc_advance(dv0, kk * T::MN_STEP), IDESC_O,
+                   (kk > 0) ? 1u : first);
       }
       if (STORE_P) {                                                // these tiles are final: store them now
         for (int t = 0; t < nt; ++t)
@@ -345,14 +381,19 @@ __global__ void __launch_bounds__(FWD_THREADS, 3) k_fwd_fused(const __grid_const
 
     if (single && nblk > 0) {
       // ---------------------------------------------------------------- rows of at most 4 blocks
-      if (tid == 0) issue_s(0, 64u, 0u, bar_s);
+      if (ctl && lane == 0) issue_s(0, 64u, 0u, bar_s);
       if (!__syncthreads_and(mbar_wait(bar_s, ps))) { if (tid == 0) report(status, ERR_MMA_WAIT); ok = false; }
       ps ^= 1u;
       tc_fence_after();
+      SPION_STAMP(ord, 1);
       if (ok) {
-        stats_math(0u, 0, nblk, 2);
-        finish_stats();
-        if (STORE_P) {
+        if (!ctl) {
+          stats_math(0u, 0, nblk, 2);
+          finish_stats();
+        }
+        SPION_STAMP(ord, 2);
+        if (ctl) {
+        } else if (STORE_P) {
           // keep both tiles' exponentials packed in registers, normalise once the denominator is known
           uint32_t wp[2][32];
 #pragma unroll
@@ -398,10 +439,12 @@ __global__ void __launch_bounds__(FWD_THREADS, 3) k_fwd_fused(const __grid_const
         } else {
           prob_math(0u, 0, 0, nblk, 2);
         }
+        SPION_STAMP(ord, 3);
         fence_proxy_async();                                        // P rows -> visible to the MMA proxy
         tc_fence_before();
         __syncthreads();
-        if (tid == 0 && issue_pv(0, 0, nblk, true)) mma_commit(bar_o);
+        SPION_STAMP(ord, 4);
+        if (ctl && lane == 0 && issue_pv(0, 0, nblk, true)) mma_commit(bar_o);
         if (!__syncthreads_and(mbar_wait(bar_o, po))) { if (tid == 0) report(status, ERR_MMA2_WAIT); ok = false; }
         po ^= 1u;
         tc_fence_after();
@@ -411,10 +454,10 @@ __global__ void __launch_bounds__(FWD_THREADS, 3) k_fwd_fused(const __grid_const
       // Pass A (statistics): the pair of chunk c sits in columns 64 (c & 1); the MMAs of chunk c+1 are
       // issued before the arithmetic on chunk c.  bar_s serves the even chunks, bar_o the odd ones.
       const int n = nchunks;
-      if (tid == 0) issue_s(0, 0u, 0u, bar_s);
+      if (ctl && lane == 0) issue_s(0, 0u, 0u, bar_s);
       for (int c = 0; c < n && ok; ++c) {
         const int b = c & 1;
-        if (tid == 0 && c + 1 < n) issue_s(c + 1, 0u, (uint32_t)(b ^ 1) * 64u, b ? bar_s : bar_o);
+        if (ctl && lane == 0 && c + 1 < n) issue_s(c + 1, 0u, (uint32_t)(b ^ 1) * 64u, b ? bar_s : bar_o);
         if (!__syncthreads_and(mbar_wait(b ? bar_o : bar_s, b ? po : ps))) {
           if (tid == 0) report(status, ERR_MMA_WAIT);
           ok = false;
@@ -422,31 +465,31 @@ __global__ void __launch_bounds__(FWD_THREADS, 3) k_fwd_fused(const __grid_const
         }
         if (b) po ^= 1u; else ps ^= 1u;
         tc_fence_after();
-        if (q == 0 && c + 2 < njobs) issue_job(R, bh, c + 2);       // the S MMAs have consumed this half's K tiles
-        stats_math((uint32_t)b * 64u, 2 * c, min(2, nblk - 2 * c), 1);
+        if (ctl && c + 2 < njobs) issue_job(R, bh, c + 2);         // the S MMAs have consumed this half's K tiles
+        if (!ctl) stats_math((uint32_t)b * 64u, 2 * c, min(2, nblk - 2 * c), 1);
         tc_fence_before();
         __syncthreads();                                            // chunk c+2 overwrites these columns
       }
-      finish_stats();
+      if (!ctl) finish_stats();
       // Pass B: S of a chunk in columns [64,128), O accumulates in [0,64).  The tensor pipe completes in
       // issue order: once S(c+1) has arrived, O += P V of chunk c is complete too, and its half of the
       // buffers is requested again.
-      if (ok && tid == 0) issue_s(n, 0u, 64u, bar_s);
+      if (ok && ctl && lane == 0) issue_s(n, 0u, 64u, bar_s);
       for (int c = 0; c < n && ok; ++c) {
         const int g = n + c, hb = g & 1, t0 = 2 * c, nt = min(2, nblk - t0);
         if (!__syncthreads_and(mbar_wait(bar_s, ps))) { if (tid == 0) report(status, ERR_MMA_WAIT); ok = false; break; }
         ps ^= 1u;
         tc_fence_after();
-        if (c > 0 && q == 0 && g + 1 < njobs) {                     // chunk c-1 is finished: its half takes job g+1
+        if (c > 0 && ctl && g + 1 < njobs) {                        // chunk c-1 is finished: its half takes job g+1
           if (STORE_P && lane == 0) bulk_wait_read_all();           // once the tile stores have read it
           __syncwarp();
           issue_job(R, bh, g + 1);
         }
-        prob_math(64u, 2 * hb, t0, nt, 1);
+        if (!ctl) prob_math(64u, 2 * hb, t0, nt, 1);
         fence_proxy_async();
         tc_fence_before();
         __syncthreads();
-        if (tid == 0 && issue_pv(hb, t0, nt, c == 0)) {
+        if (ctl && lane == 0 && issue_pv(hb, t0, nt, c == 0)) {
           if (c + 1 < n) issue_s(g + 1, 0u, 64u, bar_s);
           else mma_commit(bar_o);
         }
@@ -456,12 +499,14 @@ __global__ void __launch_bounds__(FWD_THREADS, 3) k_fwd_fused(const __grid_const
         po ^= 1u;
       }
       tc_fence_after();
-    } else {
+    } else if (!ctl) {
       finish_stats();
     }
+    SPION_STAMP(ord, 5);
     if (ok) prefetch_next();
+    SPION_STAMP(ord, 6);
     // ------------------------------------------------------------------ output rows of this unit
-    if (ok) {
+    if (ok && !ctl) {
       float inv = 1.0f, lse2 = lse_fixed;
       if (!STORE_P) {
         const float l = l_part + __shfl_xor_sync(0xffffffffu, l_part, 16) + (float)(L - n_sel) * exp2f(-m2);
@@ -496,17 +541,24 @@ __global__ void __launch_bounds__(FWD_THREADS, 3) k_fwd_fused(const __grid_const
         }
       }
     }
+    SPION_STAMP(ord, 7);
     // the next unit's S MMAs overwrite the accumulator columns read above
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    SPION_STAMP(ord, 8);
+    if (threadIdx.x == 0) SPION_STAMP(ord, 9 + 0 * nblk);
+#ifdef SPION_TRACE
+    if (threadIdx.x == 0 && g_spion_trace && ord < g_spion_trace_units)
+      g_spion_trace[((size_t)blockIdx.x * g_spion_trace_units + ord) * 16 + 15] = (unsigned long long)nblk;
+#endif
     R = Rn;
     bh = bhn;
   }
-  if (STORE_P && tid == 0) bulk_wait_read_all();                  // shared memory must outlive the tile stores
+  if (STORE_P && ctl && lane == 0) bulk_wait_read_all();          // shared memory must outlive the tile stores
   tc_fence_before();
   __syncthreads();
-  if (q == 0) tmem_dealloc(tmem, ncols);
+  if (ctl) tmem_dealloc(tmem, ncols);
 }
 
 }  // namespace

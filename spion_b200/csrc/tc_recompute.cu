@@ -23,6 +23,10 @@
 
 using namespace tc;
 
+#ifdef SPION_TRACE
+SPION_TRACE_SETTER(spion_debug_trace_rc)
+#endif
+
 namespace {
 
 constexpr int RC_THREADS = 256;

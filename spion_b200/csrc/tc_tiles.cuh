@@ -33,6 +33,11 @@ __device__ __forceinline__ uint32_t fma_bf16x2(uint32_t a, uint32_t b, uint32_t 
 __device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
 
+// A descriptor's start-address field counts 16-byte units in its low 14 bits: stepping an operand by
+// `bytes` inside one tile is an add on the low word (the tiles are 1024-byte aligned and at most 8 KB, so
+// the field never carries).
+__device__ __forceinline__ uint64_t desc_advance(uint64_t desc, uint32_t bytes) { return desc + (uint64_t)(bytes >> 4); }
+
 template <int D> struct OpTile {
   static constexpr int ROW_BYTES = D * 2;                        // 128 (D=64) or 64 (D=32)
   static constexpr int BYTES = BS * ROW_BYTES;
@@ -44,6 +49,7 @@ template <int D> struct OpTile {
   __device__ static uint64_t mnmajor(uint32_t saddr, int kk) {
     return make_smem_desc(saddr + kk * 16 * ROW_BYTES, BYTES, SBO, LAYOUT);
   }
+  static constexpr uint32_t K_STEP = 32, MN_STEP = 16 * ROW_BYTES;   // bytes per K step of the two uses
 };
 // bf16 value tile [64 x 64], 128-byte rows, SWIZZLE_128B
 struct ValTile {
@@ -51,8 +57,32 @@ struct ValTile {
   __device__ static uint64_t mnmajor(uint32_t saddr, int kk) {
     return make_smem_desc(saddr + kk * 2048, VT_BYTES, 1024, LAYOUT_SW128);
   }
+  static constexpr uint32_t K_STEP = 32, MN_STEP = 2048;
 };
 
+
+#ifdef SPION_TRACE
+// Developer build only: nanosecond stamps (%globaltimer) of thread 0 at phase boundaries, 16 per unit,
+// for the first units of every CTA.
+static __device__ unsigned long long* g_spion_trace;     // one copy per translation unit (no relocatable device code)
+static __device__ int g_spion_trace_units;
+#define SPION_TRACE_SETTER(name)                                                              \
+  extern "C" int name(void* device_buffer, int units_per_cta) {                               \
+    SPION_CUDA_TRY(cudaMemcpyToSymbol(g_spion_trace, &device_buffer, sizeof(void*)));         \
+    SPION_CUDA_TRY(cudaMemcpyToSymbol(g_spion_trace_units, &units_per_cta, sizeof(int)));     \
+    return SPION_OK;                                                                          \
+  }
+__device__ __forceinline__ void trace_stamp(int unit_ordinal, int k) {
+  if (threadIdx.x == 0 && g_spion_trace && unit_ordinal < g_spion_trace_units) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)::"memory");
+    g_spion_trace[((size_t)blockIdx.x * g_spion_trace_units + unit_ordinal) * 16 + k] = t;
+  }
+}
+#define SPION_STAMP(u, k) trace_stamp(u, k)
+#else
+#define SPION_STAMP(u, k)
+#endif
 
 // Where the [L x D] operand matrix of (b,h) pair `bh` starts inside the 2-D tensor the maps describe.
 //   heads == 0: operands are [BH, L, D]      -> rows bh*L ..,      columns 0 .. D,        row pitch D
