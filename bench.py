@@ -585,11 +585,11 @@ def main():
               "staged": _lib.ENGINE_SIMT_STAGED}[args.engine]
     mod = BlockSparseAttention(cfg, dtype=tdt, engine=engine, device=dev,
                                fused=None if args.mode == "auto" else (args.mode in ("fused", "stored")),
-                               return_probs=False, recompute=args.mode != "stored")
+                               return_probs=False, recompute={"fused": True, "stored": False}.get(args.mode))
     fused_fwd = mod.fused
-    fused_bwd = mod.recompute    # neither P nor dS in HBM
     mat = synthetic.band_random_mask(2024, nb, dens)          # same mask on every rank (one layer)
     nnzb = mod.set_mask(torch.as_tensor(mat).to(dev))
+    fused_bwd = mod.recompute    # neither P nor dS in HBM (chosen per mask when --mode auto)
     flops, fused_bytes, nnz = algorithmic(B, H, L, d, bs, nnzb, esz)
 
     # rank-specific shard of the batch*head work

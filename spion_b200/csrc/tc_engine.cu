@@ -559,10 +559,13 @@ __global__ void __launch_bounds__(256) k_convert_tiles(__nv_bfloat16* __restrict
 // grid walking the records starts its longest rows first.  One CTA; nb <= SPION_MAX_NB.
 //   {row_ptr, blocks | row << 16, col0 | col1 << 16, col2 | col3 << 16}
 __global__ void k_row_info(const int32_t* __restrict__ row_ptr, const int32_t* __restrict__ col_idx, int nb,
-                           int4* __restrict__ info) {
+                           int4* __restrict__ info, int* __restrict__ n_long) {
   __shared__ int s_n[SPION_MAX_NB];
+  if (threadIdx.x == 0) *n_long = 0;
   for (int r = threadIdx.x; r < nb; r += blockDim.x) s_n[r] = row_ptr[r + 1] - row_ptr[r];
   __syncthreads();
+  for (int r = threadIdx.x; r < nb; r += blockDim.x)
+    if (s_n[r] > ROW_NCH) atomicAdd(n_long, 1);                     // rows that need the streamed schedule
   for (int r = threadIdx.x; r < nb; r += blockDim.x) {
     const int rp = row_ptr[r], n = s_n[r];
     int rank = 0;
@@ -739,6 +742,7 @@ int tc_engine_prepare(spion_ctx* c) {
     int rc = (c->d == 64) ? set_attrs<64>(s, c->device) : set_attrs<32>(s, c->device);
     if (!rc) rc = fused_set_attrs(s, c->d, c->device);
     if (!rc) rc = recompute_set_attrs(s, c->d, c->device);
+    if (!rc) rc = pipe_set_attrs(s, c->d, c->device);
     if (!rc && cudaMalloc(&s->delta_ws, (size_t)c->BH * c->L * sizeof(float)) != cudaSuccess) rc = SPION_ERR_ALLOC;
     if (!rc && cudaMalloc(&s->lse_ws, (size_t)c->BH * c->L * sizeof(float)) != cudaSuccess) rc = SPION_ERR_ALLOC;
     if (rc) { delete s; return rc; }
@@ -753,8 +757,11 @@ int tc_engine_prepare(spion_ctx* c) {
   // value-tile rows are 32-bit TMA coordinates: (bh * nnzb + block) * 64 must stay below 2^31
   if ((unsigned long long)c->BH * (unsigned long long)vw.nnzb * BS >= 0x7fffffffULL) return SPION_ERR_SHAPE;
   if (!s->row_info && cudaMalloc(&s->row_info, (size_t)SPION_MAX_NB * sizeof(int4)) != cudaSuccess) return SPION_ERR_ALLOC;
-  k_row_info<<<1, 512, 0, c->stream>>>(vw.row_ptr, vw.col_idx, vw.nb, s->row_info);
+  if (!s->n_long_dev && cudaMalloc(&s->n_long_dev, sizeof(int)) != cudaSuccess) return SPION_ERR_ALLOC;
+  k_row_info<<<1, 512, 0, c->stream>>>(vw.row_ptr, vw.col_idx, vw.nb, s->row_info, s->n_long_dev);
   SPION_LAUNCH_CHECK();
+  SPION_CUDA_TRY(cudaMemcpyAsync(&s->n_long, s->n_long_dev, sizeof(int), cudaMemcpyDeviceToHost, c->stream));
+  SPION_CUDA_TRY(cudaStreamSynchronize(c->stream));                // set_pattern time: once per mask
   if (!s->col_order && cudaMalloc(&s->col_order, (size_t)SPION_MAX_NB * sizeof(int)) != cudaSuccess) return SPION_ERR_ALLOC;
   k_line_order<<<1, 512, 0, c->stream>>>(vw.col_ptr, vw.nb, s->col_order);
   SPION_LAUNCH_CHECK();
@@ -768,6 +775,7 @@ void tc_engine_release(spion_ctx* c) {
   free_super(s);
   cudaFree(s->lse_ws);
   cudaFree(s->delta_ws);
+  cudaFree(s->n_long_dev);
   cudaFree(s->row_info);
   cudaFree(s->col_order);
   delete s;

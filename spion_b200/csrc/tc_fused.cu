@@ -598,18 +598,27 @@ static int fwd_launch(spion_ctx* c, TcState* s, const void* Q, const void* K, co
     return rc;
   if (P64) { if ((rc = make_map(s, &mp, P64, vrows, BS, BS, BS))) return rc; } else mp = mq;
   prof_mark(c, -1);
-  const long long total = (long long)c->BH * vw.nb;
-  const int grid = (int)(total < (long long)s->sms * s->fwd_ctas ? total : (long long)s->sms * s->fwd_ctas);
+  // Masks whose rows all have at most four blocks run on the pipelined kernel for short rows
+  // (tc_fwd_pipe.cu: about 1.7x less time per row, two CTAs per SM).  As soon as some rows are longer,
+  // everything goes through this file's kernel: a second launch for a handful of long rows costs more
+  // than the pipelining gains (measured at 5 % density, L = 4096: 79 us split against 70 us in one launch).
+  const bool all_short = s->n_long == 0;
+  const int rows_here = all_short ? 0 : vw.nb;
+  const long long total = (long long)c->BH * rows_here;
   const float floor_v = keypad ? 0.0f : -100.0f;
+  if (total > 0) {
+    const int grid = (int)(total < (long long)s->sms * s->fwd_ctas ? total : (long long)s->sms * s->fwd_ctas);
 #define SPION_FWD_LAUNCH(SP, SB)                                                                                  \
   k_fwd_fused<D, SP, SB><<<grid, FWD_THREADS, fwd_smem_bytes<D>(), c->stream>>>(                                   \
       mq, mk, mv, mp, (__nv_bfloat16*)O, lse, keypad, vw.row_info, vw.col_idx, vw.submask, c->L, vw.nnzb, c->BH,   \
-      vw.nb, c->heads, c->scale, floor_v, c->status_dev)
-  if (P64) { if (vw.submask) SPION_FWD_LAUNCH(true, true); else SPION_FWD_LAUNCH(true, false); }
-  else { if (vw.submask) SPION_FWD_LAUNCH(false, true); else SPION_FWD_LAUNCH(false, false); }
+      rows_here, c->heads, c->scale, floor_v, c->status_dev)
+    if (P64) { if (vw.submask) SPION_FWD_LAUNCH(true, true); else SPION_FWD_LAUNCH(true, false); }
+    else { if (vw.submask) SPION_FWD_LAUNCH(false, true); else SPION_FWD_LAUNCH(false, false); }
 #undef SPION_FWD_LAUNCH
-  SPION_LAUNCH_CHECK();
-  c->launches += 1;
+    SPION_LAUNCH_CHECK();
+    c->launches += 1;
+  }
+  if (all_short && (rc = pipe_forward(c, s, mq, mk, mv, mp, P64 != nullptr, keypad, O, lse, 0))) return rc;
   prof_mark(c, SPION_STAGE_FUSED_FWD);
   return SPION_OK;
 }

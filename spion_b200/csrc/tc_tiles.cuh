@@ -124,6 +124,9 @@ struct TcState {
   int sms = 0;                  // multiprocessors of the context's device
   int fwd_ctas = 0, row_ctas = 0, col_ctas = 0;   // resident CTAs per SM of the persistent kernels
   int rc_row_ctas = 0, rc_col_ctas = 0;           // ... of the two recompute backward kernels
+  int pipe_ctas = 0;                              // ... of the pipelined forward for short rows
+  int n_long = 0;               // block rows with more than ROW_NCH blocks: the first n_long records of row_info
+  int* n_long_dev = nullptr;
   float* delta_ws = nullptr;    // [BH*L] delta_i = sum_n dO_in O_in, written by the row kernel, read by the column kernel
   float* lse_ws = nullptr;      // [BH*L] log-sum-exp workspace for the calls that do not expose it
   int* col_order = nullptr;     // block columns from the longest to the shortest
@@ -208,6 +211,11 @@ int recompute_backward(spion_ctx* c, TcState* s, const void* Q, const void* K, c
                        const void* dO, const float* lse, const float* keypad, void* dQ, void* dK, void* dV);
 int recompute_mean_map(spion_ctx* c, TcState* s, const void* Q, const void* K, const float* lse, const float* keypad,
                        float* A);
+
+// tc_fwd_pipe.cu: forward of the records [rank0, nb) of row_info (rows of at most ROW_NCH blocks)
+int pipe_set_attrs(TcState* s, int d, int device);
+int pipe_forward(spion_ctx* c, TcState* s, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
+                 const CUtensorMap& mp, bool store_p, const float* keypad, void* O, float* lse, int rank0);
 
 // tc_fused.cu
 int fused_set_attrs(TcState* s, int d, int device);

@@ -36,7 +36,7 @@ class ProbsHandle:
 
 class BlockSparseAttention(nn.Module):
     def __init__(self, config, dtype=torch.float32, keypad: bool = False, engine: int = _lib.ENGINE_AUTO,
-                 device=None, fused=None, return_probs: bool = True, recompute: bool = True):
+                 device=None, fused=None, return_probs: bool = True, recompute=None):
         super().__init__()
         self.d = config["head_dim"]
         self.H = config["num_head"]
@@ -63,9 +63,13 @@ class BlockSparseAttention(nn.Module):
         # return_probs=False (fused kernels only): the forward writes O and the log-sum-exp, nothing of size
         # nnz, and ``forward`` returns a ProbsHandle instead of the [BH, nnzb, bs, bs] tiles
         self.return_probs = bool(return_probs) or not self.fused
-        # recompute=True (fused kernels): the backward rebuilds P and dS on chip from the log-sum-exp;
-        # False: it reads the stored P tiles and writes dS tiles (spion_attn_backward_ex)
-        self.recompute = bool(recompute) and self.fused
+        # recompute=True (fused kernels): the backward rebuilds P and dS on chip from the log-sum-exp and nothing
+        # of size nnz exists in memory; False: the forward stores P, the backward reads it and writes dS
+        # (spion_attn_backward_ex).  None: chosen per mask in set_mask -- recompute for 32-wide blocks (no tile
+        # conversion passes: measured 6 - 25 % faster) and for the full mask of the warm-up phase (equal speed,
+        # 2 * BH * L^2 elements less memory); stored tiles for sparse 64-wide masks (measured 10 - 15 % faster).
+        self._recompute_arg = recompute
+        self.recompute = self.fused and (recompute is None or bool(recompute))
         self.last = None
         self.nnzb = -1
         self._mask_key = None
@@ -86,6 +90,9 @@ class BlockSparseAttention(nn.Module):
         check(lib.spion_set_stream(self.handle, _lib.current_stream_ptr()))
         check(lib.spion_set_pattern(self.handle, ptr(m8)), "spion_set_pattern")
         self.nnzb = int(lib.spion_pattern_nnzb(self.handle))
+        if self.fused and self._recompute_arg is None:
+            nb = self.L // self.bs
+            self.recompute = self.bs == 32 or self.nnzb == nb * nb
         from .pattern import pattern_from_mask
         self._pattern = pattern_from_mask(m8, self.bs)          # block CSR for the helpers above
         # The key names the tensor by address and version; the tensor itself is kept alive so that the
