@@ -268,9 +268,9 @@ def run_training(args, rank, world, local_rank):
     dens = [float(m.mean()) for m in mat_lst[0]]
     del maps
     torch.cuda.empty_cache()
-    # The captured step holds no collective: with more than one rank the step runs eagerly (a capture that
-    # included the gradient all-reduce did not finish on 8 GPUs).
-    use_graph = not args.no_graph and world == 1
+    # A capture never holds a collective: with more than one rank the step is two graphs (forward + backward;
+    # clipping + optimizer) around an eager gradient all-reduce.
+    use_graph = not args.no_graph
     if use_graph:
         tr.capture_sparse_step(ids, y)
     run_step = (lambda a, b: tr.step_graph(a, b)) if use_graph else (lambda a, b: tr.step(a, b)[0])
@@ -283,6 +283,7 @@ def run_training(args, rank, world, local_rank):
         run_step(ids, y)
     e1.record()
     barrier()
+    ms_local = e0.elapsed_time(e1) / args.steps
     t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -303,6 +304,27 @@ def run_training(args, rank, world, local_rank):
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     e2e_ms = float(t.item()) / args.steps
+    # Where the step's time goes on every rank: CUDA events inside a few extra steps -- forward + backward,
+    # the gradient all-reduce (which also absorbs the wait for the slowest rank), clipping + optimizer.
+    parts = None
+    ar_ms = None
+    if world > 1:
+        tr.allreduce_events = []
+        for _ in range(10):
+            run_step(ids, y)
+        torch.cuda.synchronize()
+        evs = tr.allreduce_events
+        tr.allreduce_events = None
+        if use_graph:
+            med = [statistics.median(e[k].elapsed_time(e[k + 1]) for e in evs) for k in range(3)]
+        else:
+            med = [float("nan"), statistics.median(a.elapsed_time(b) for a, b in evs), float("nan")]
+        mine = torch.tensor(med + [ms_local], device=dev, dtype=torch.float64)
+        allr = [torch.zeros_like(mine) for _ in range(world)]
+        dist.all_gather(allr, mine)
+        parts = {"fwd_bwd_ms": [round(float(t[0]), 3) for t in allr], "allreduce_ms": [round(float(t[1]), 3) for t in allr],
+                 "clip_opt_ms": [round(float(t[2]), 3) for t in allr], "step_ms": [round(float(t[3]), 3) for t in allr]}
+        ar_ms = max(float(t[1]) for t in allr)
     launches = sum(int(layer.mha.block_attn.launch_count()) for layer in tr.model.model.layers)
     if rank == 0:
         print(json.dumps({
@@ -313,6 +335,8 @@ def run_training(args, rank, world, local_rank):
             "config": {"workload": args.workload, "task": cfg["task"], "batch_per_gpu": per_rank, "L": L,
                        "block": cfg["block_size"], "threshold": thr, "density_per_layer": dens,
                        "grad_bucket_bytes": tr.bucket.nbytes, "cuda_graph": use_graph, "pattern_discovery_ms": pattern_ms,
+                       "allreduce_ms_per_step": ar_ms, "allreduce_share": (ar_ms / ms_step) if ar_ms else None,
+                       "per_rank": parts,
                        "l2_policy": "activations of one step exceed L2"},
             "e2e": {"value": tokens / (e2e_ms * 1e-3) / 1e6, "unit": "Mtokens/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": int((2 if dual else 1) * per_rank * L * 8 + per_rank * 8), "d2h_bytes_per_step": 4},

@@ -589,6 +589,34 @@ __global__ void k_line_order(const int32_t* __restrict__ line_ptr, int nb, int* 
   }
 }
 
+// Column records for the streaming column kernel, in col_order: one CTA.
+//   rec[x]  = {block column, index of its first pair, pairs, entries}
+//   pair[p] = {block row of the pair's first entry, of its second (-1: none), CSR block ids of the two}
+__global__ void k_col_recs(const int32_t* __restrict__ col_ptr, const int32_t* __restrict__ row_idx,
+                           const int32_t* __restrict__ csc_pos, const int* __restrict__ order, int nb,
+                           int4* __restrict__ rec, int4* __restrict__ pair) {
+  __shared__ int s_first[SPION_MAX_NB + 1];
+  if (threadIdx.x == 0) {
+    int acc = 0;
+    for (int x = 0; x < nb; ++x) {
+      const int c = order[x];
+      s_first[x] = acc;
+      acc += (col_ptr[c + 1] - col_ptr[c] + 1) >> 1;
+    }
+    s_first[nb] = acc;
+  }
+  __syncthreads();
+  for (int x = threadIdx.x; x < nb; x += blockDim.x) {
+    const int c = order[x], beg = col_ptr[c], n = col_ptr[c + 1] - beg, np = (n + 1) >> 1;
+    rec[x] = make_int4(c, s_first[x], np, n);
+    for (int k = 0; k < np; ++k) {
+      const int e0 = beg + 2 * k;
+      const bool two = e0 + 1 < beg + n;
+      pair[s_first[x] + k] = make_int4(row_idx[e0], two ? row_idx[e0 + 1] : -1, csc_pos[e0], two ? csc_pos[e0 + 1] : 0);
+    }
+  }
+}
+
 // Self-test of the bounded wait: one CTA waits on an mbarrier that nothing ever arrives on, with a
 // short limit; it must give up, record ERR_LOAD_WAIT in the status word and return normally.
 __global__ void k_wait_selftest(int* status, long long limit_cycles) {
@@ -765,6 +793,16 @@ int tc_engine_prepare(spion_ctx* c) {
   if (!s->col_order && cudaMalloc(&s->col_order, (size_t)SPION_MAX_NB * sizeof(int)) != cudaSuccess) return SPION_ERR_ALLOC;
   k_line_order<<<1, 512, 0, c->stream>>>(vw.col_ptr, vw.nb, s->col_order);
   SPION_LAUNCH_CHECK();
+  if (!s->col_rec && cudaMalloc(&s->col_rec, (size_t)SPION_MAX_NB * sizeof(int4)) != cudaSuccess) return SPION_ERR_ALLOC;
+  if ((size_t)vw.nnzb > s->col_pair_cap) {                         // at most one pair per entry
+    cudaFree(s->col_pair);
+    s->col_pair = nullptr;
+    s->col_pair_cap = 0;
+    if (cudaMalloc(&s->col_pair, (size_t)vw.nnzb * sizeof(int4)) != cudaSuccess) return SPION_ERR_ALLOC;
+    s->col_pair_cap = (size_t)vw.nnzb;
+  }
+  k_col_recs<<<1, 512, 0, c->stream>>>(vw.col_ptr, vw.row_idx, vw.csc_pos, s->col_order, vw.nb, s->col_rec, s->col_pair);
+  SPION_LAUNCH_CHECK();
   c->launches += 2;
   return SPION_OK;
 }
@@ -778,6 +816,8 @@ void tc_engine_release(spion_ctx* c) {
   cudaFree(s->n_long_dev);
   cudaFree(s->row_info);
   cudaFree(s->col_order);
+  cudaFree(s->col_rec);
+  cudaFree(s->col_pair);
   delete s;
   c->tc = nullptr;
 }

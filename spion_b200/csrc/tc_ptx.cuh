@@ -9,6 +9,9 @@
 #include <stdint.h>
 
 #define SPION_WAIT_CYCLES 4000000000LL
+#ifndef SPION_WAIT_BACKOFF_NS
+#define SPION_WAIT_BACKOFF_NS 40
+#endif
 
 namespace tc {
 
@@ -37,6 +40,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// Non-blocking test: has the phase with this parity completed?
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
 // Bounded wait.  Returns false when the limit is hit (the caller records it and leaves).
 __device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, long long limit_cycles) {
   if (mbar_try_wait(bar, parity)) return true;
@@ -44,6 +59,9 @@ __device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, l
   for (;;) {
     if (mbar_try_wait(bar, parity)) return true;
     if (clock64() - t0 > limit_cycles) return false;
+    // Back off: a warp that polls without pause takes issue slots from the warp it is waiting for (the one
+    // thread that issues the MMAs shares its scheduler with the pollers).
+    __nanosleep(SPION_WAIT_BACKOFF_NS);
   }
 }
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {

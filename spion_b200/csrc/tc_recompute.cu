@@ -7,12 +7,13 @@
 // are functions of Q, K, V, dO, O alone, so both backward kernels rebuild the tiles they need in tensor
 // memory / shared memory instead of reading what the forward pass and the row kernel would have stored:
 //     k_bwd_row_rc   per block row:     S = Q K^T, dP = dO V^T  ->  dS  ->  dQ = dS K;   writes delta
-//     k_bwd_col_rc   per block column:  S, dP of every entry    ->  P, dS  ->  dV += P^T dO, dK += dS^T Q
+//     k_bwd_col_stream (tc_recompute_col.cu)
+//                    per block column:  S, dP of every entry    ->  P, dS  ->  dV += P^T dO, dK += dS^T Q
 // This replaces models/block_attn.cu:489-545 (two cuSPARSE SDDMMs' worth of stored values, the softmax
 // backward kernel and three SpMMs) with 16 L d e bytes of traffic per (b,h) matrix and step instead of
 // 16 L d e + 5 nnz p.
 //
-// Both kernels are persistent (grid = CTAs the device holds at once, units taken with stride grid) and
+// The kernels are persistent (grid = CTAs the device holds at once, units taken with stride grid) and
 // use 8 math warps: warps w and w + 4 share TMEM quadrant w & 3 and split the 64 columns of a tile in
 // two halves, which the backward allows without any exchange (lse and delta are per-row inputs).
 // Thread 0 issues the TMA loads' MMAs; every wait on an mbarrier is bounded.
@@ -339,250 +340,6 @@ __global__ void __launch_bounds__(RC_THREADS, 2) k_bwd_row_rc(const __grid_const
   if (warp == 0) tmem_dealloc(tmem, ncols);
 }
 
-template <int D> constexpr size_t rc_col_smem() {
-  // K | V | Q x2 | dO x2 | P x2 | dS x2 | barriers
-  return 1024 + (size_t)6 * OpTile<D>::BYTES + 4 * VT_BYTES + 128;
-}
-
-// =====================================================================================
-// Column side.  Unit = (block column c, bh):  dK[c] = sum_r dS(r,c)^T Q[r],  dV[c] = sum_r P(r,c)^T dO[r].
-// K[c] and V[c] are loaded once per unit; the entries r of the column are taken two at a time: the S and dP
-// tiles of the pair share TMEM columns [0,64) and [64,128) (first entry in lanes 0-15 of every quadrant,
-// second in lanes 16-31, so all 32 lanes of a warp own a query row), P and dS are written as bf16 tiles
-// [query x key] into shared memory and read back as MN-major A operands (the transposes cost nothing), and
-// both accumulators live in columns [128, 128 + D): dK in lanes 0-15, dV in lanes 16-31.
-template <int D, bool SUB>
-__global__ void __launch_bounds__(RC_THREADS, 2) k_bwd_col_rc(const __grid_constant__ CUtensorMap tmQ,
-                                                              const __grid_constant__ CUtensorMap tmK,
-                                                              const __grid_constant__ CUtensorMap tmV,
-                                                              const __grid_constant__ CUtensorMap tmdO,
-                                                              const float* __restrict__ lse_in,
-                                                              const float* __restrict__ delta_in,
-                                                              const float* __restrict__ keypad,
-                                                              __nv_bfloat16* __restrict__ dK, __nv_bfloat16* __restrict__ dV,
-                                                              const int* __restrict__ col_ptr, const int* __restrict__ row_idx,
-                                                              const int* __restrict__ csc_pos, const int* __restrict__ order,
-                                                              const uint8_t* __restrict__ submask, int L, int BH, int nb,
-                                                              int heads, float scale, int* status) {
-  using T = OpTile<D>;
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t raw = smem_u32(smem_raw);
-  const uint32_t sbase = (raw + 1023u) & ~1023u;
-  const uint32_t sK = sbase;
-  const uint32_t sV = sK + T::BYTES;
-  const uint32_t sQ = sV + T::BYTES;                            // two entry slots
-  const uint32_t sdO = sQ + 2 * T::BYTES;
-  const uint32_t sP = sdO + 2 * T::BYTES;
-  const uint32_t sDS = sP + 2 * VT_BYTES;
-  const uint32_t bars = sDS + 2 * VT_BYTES;
-  // bar_kv: K and V of the unit; bar_in[slot]: Q and dO of an entry; bar_s: S / dP MMAs; bar_acc: dK / dV MMAs of a pair
-  const uint32_t bar_kv = bars, bar_in = bars + 8, bar_s = bars + 24, bar_acc = bars + 32, slot = bars + 40;
-  uint32_t* slot_ptr = reinterpret_cast<uint32_t*>(smem_raw + (slot - raw));
-  __shared__ int s_abort;
-
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int q = warp & 3, g = warp >> 2;                       // TMEM quadrant, column half
-  const int es = lane >> 4;                                    // entry of the pair this lane works on
-  const int row = q * 16 + (lane & 15);                        // query row inside the entry's block (math), output row (epilogue)
-  const int total = nb * BH, G = (int)gridDim.x;
-  constexpr uint32_t ncols = 256u;
-  constexpr uint32_t ACC = 128u;
-
-  struct Unit { int bh, line, beg, end; };
-  auto unit_of = [&](int uu) -> Unit {                           // columns of one (b,h) matrix together, the longest first
-    Unit U;
-    U.bh = uu / nb;
-    U.line = order[uu - U.bh * nb];
-    U.beg = col_ptr[U.line];
-    U.end = col_ptr[U.line + 1];
-    return U;
-  };
-  // warp 0, all lanes
-  auto load_kv = [&](const Unit& U) {
-    const OpPos pos = op_pos(U.bh, L, heads, D);
-    if (lane == 0) mbar_expect_tx(bar_kv, 2 * T::BYTES);
-    __syncwarp();
-    if (lane == 0) tma_load_2d(sK, &tmK, bar_kv, pos.x0, pos.row0 + U.line * BS);
-    if (lane == 1) tma_load_2d(sV, &tmV, bar_kv, pos.x0, pos.row0 + U.line * BS);
-  };
-  auto load_pair = [&](const Unit& U, int e0) {                 // entries e0 (slot 0) and e0 + 1 (slot 1) if they exist
-    const OpPos pos = op_pos(U.bh, L, heads, D);
-    const int cnt = min(2, U.end - e0);
-    if (lane < cnt) mbar_expect_tx(bar_in + 8 * lane, 2 * T::BYTES);
-    __syncwarp();
-    if (lane < 2 * cnt) {
-      const int sl = lane >> 1;
-      const int orow = pos.row0 + row_idx[e0 + sl] * BS;
-      if (lane & 1) tma_load_2d(sdO + sl * T::BYTES, &tmdO, bar_in + 8 * sl, pos.x0, orow);
-      else tma_load_2d(sQ + sl * T::BYTES, &tmQ, bar_in + 8 * sl, pos.x0, orow);
-    }
-  };
-  auto first_loads = [&](const Unit& U) {
-    if (U.end > U.beg) { load_kv(U); load_pair(U, U.beg); }
-  };
-
-  int u = blockIdx.x;
-  Unit U{0, 0, 0, 0};
-  if (u < total) U = unit_of(u);
-
-  if (warp == 0) {
-    if (lane == 0) {
-      s_abort = *reinterpret_cast<volatile int*>(status);
-      mbar_init(bar_kv, 1);
-      mbar_init(bar_in, 1);
-      mbar_init(bar_in + 8, 1);
-      mbar_init(bar_s, 1);
-      mbar_init(bar_acc, 1);
-      fence_barrier_init();
-    }
-    __syncwarp();
-    if (s_abort == 0 && u < total) first_loads(U);
-  }
-  __syncthreads();
-  if (s_abort != 0) return;
-  if (warp == 0) {
-    tmem_alloc(slot, ncols);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = *slot_ptr;
-  const uint32_t t_lane = tmem + ((uint32_t)(q * 32) << 16);
-  constexpr uint32_t IDESC_S = make_idesc_bf16(64, 64, 0, 0);
-  constexpr uint32_t IDESC_T = make_idesc_bf16(64, D, 1, 1);
-  const float sc2 = scale * LOG2E;
-  uint32_t pkv = 0, pin = 0, ps = 0, pacc = 0;                  // pkv, pin (one bit per slot): thread 0 only
-  bool ok = true;
-
-  for (; u < total && ok; u += G) {
-    const int un = u + G;
-    const bool has_next = un < total;
-    Unit Un{0, 0, 0, 0};
-    if (has_next) Un = unit_of(un);
-    const int n = U.end - U.beg;
-    const int npairs = (n + 1) >> 1;
-    const OpPos pos = op_pos(U.bh, L, heads, D);
-    const float* kp = keypad ? keypad + (size_t)U.bh * L + U.line * BS + g * 32 : nullptr;   // the keys of this block column
-
-    for (int k = 0; k < npairs && ok; ++k) {
-      const int e0 = U.beg + 2 * k;
-      const int cnt = min(2, U.end - e0);
-      if (tid == 0) {
-        bool got = true;
-        if (k == 0) { got = mbar_wait(bar_kv, pkv); pkv ^= 1u; }
-        for (int sl = 0; sl < cnt && got; ++sl) { got = mbar_wait(bar_in + 8 * sl, (pin >> sl) & 1); pin ^= 1u << sl; }
-        if (got) {
-          tc_fence_after();
-          for (int sl = 0; sl < cnt; ++sl) {
-            const uint32_t lo = (uint32_t)(sl * 16) << 16;
-#pragma unroll
-            for (int kk = 0; kk < D / 16; ++kk)                  // S = Q_r K_c^T
-              mma_bf16(tmem + lo, T::kmajor(sQ + sl * T::BYTES, kk), T::kmajor(sK, kk), IDESC_S, kk > 0);
-#pragma unroll
-            for (int kk = 0; kk < D / 16; ++kk)                  // dP = dO_r V_c^T
-              mma_bf16(tmem + lo + 64u, T::kmajor(sdO + sl * T::BYTES, kk), T::kmajor(sV, kk), IDESC_S, kk > 0);
-          }
-          mma_commit(bar_s);
-        } else {
-          report(status, ERR_LOAD_WAIT);
-        }
-      }
-      // per-row inputs of this lane's entry
-      const bool mine = es < cnt;
-      float lse = 0.f, nds = 0.f;
-      bool live = false;
-      if (mine) {
-        const size_t ri = (size_t)U.bh * L + (size_t)row_idx[e0 + es] * BS + row;
-        lse = lse_in[ri];
-        nds = -delta_in[ri] * scale;
-        live = !SUB || ((submask[csc_pos[e0 + es]] >> ((q >> 1) * 2 + g)) & 1);
-      }
-      if (!__syncthreads_and(mbar_wait(bar_s, ps))) { if (tid == 0) report(status, ERR_MMA_WAIT); ok = false; break; }
-      ps ^= 1u;
-      tc_fence_after();
-      {
-        uint32_t sv[32], gv[32], wp[16], wds[16];
-        tmem_ld32(t_lane + g * 32, sv);
-        tmem_ld32(t_lane + 64u + g * 32, gv);
-        tmem_ld_wait();
-        if (mine) {
-          p_ds_32<true>(sv, gv, sc2, scale, lse, nds, kp, live, wp, wds);
-          store_half_row_swizzled(sP + es * VT_BYTES, row, g, wp);
-          store_half_row_swizzled(sDS + es * VT_BYTES, row, g, wds);
-        }
-      }
-      fence_proxy_async();
-      tc_fence_before();
-      __syncthreads();
-      if (tid == 0) {
-        tc_fence_after();
-        for (int sl = 0; sl < cnt; ++sl) {
-          const uint32_t first = (k == 0 && sl == 0) ? 0u : 1u;
-#pragma unroll
-          for (int kk = 0; kk < BS / 16; ++kk)                   // dV += P^T dO   (lanes 16-31)
-            mma_bf16(tmem + ACC + (16u << 16), ValTile::mnmajor(sP + sl * VT_BYTES, kk), T::mnmajor(sdO + sl * T::BYTES, kk),
-                     IDESC_T, (kk > 0) ? 1u : first);
-#pragma unroll
-          for (int kk = 0; kk < BS / 16; ++kk)                   // dK += dS^T Q   (lanes 0-15)
-            mma_bf16(tmem + ACC, ValTile::mnmajor(sDS + sl * VT_BYTES, kk), T::mnmajor(sQ + sl * T::BYTES, kk), IDESC_T,
-                     (kk > 0) ? 1u : first);
-        }
-        mma_commit(bar_acc);
-      }
-      // the entry slots and the P / dS tiles are free once these MMAs have retired
-      if (!__syncthreads_and(mbar_wait(bar_acc, pacc))) { if (tid == 0) report(status, ERR_MMA2_WAIT); ok = false; break; }
-      pacc ^= 1u;
-      tc_fence_after();
-      if (warp == 0) {
-        if (k + 1 < npairs) load_pair(U, e0 + 2);
-        else if (has_next) first_loads(Un);
-      }
-    }
-    if (ok && n == 0 && warp == 0 && has_next) first_loads(Un);
-    if (ok) {
-      // lanes 0-15: dK rows, lanes 16-31: dV rows; the two warps of a quadrant take half of the columns each
-      __nv_bfloat16* dst = (lane < 16 ? dK : dV) + (size_t)(pos.row0 + U.line * BS + row) * pos.ld + pos.x0 + g * (D / 2);
-      if (D == 64) {
-        uint32_t v[32];
-        if (n > 0) { tmem_ld32(t_lane + ACC + g * 32, v); tmem_ld_wait(); }
-        else {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = 0u;
-        }
-#pragma unroll
-        for (int j = 0; j < 32; j += 8)
-          *reinterpret_cast<uint4*>(dst + j) =
-              make_uint4(pack_bf16(__uint_as_float(v[j]), __uint_as_float(v[j + 1])),
-                         pack_bf16(__uint_as_float(v[j + 2]), __uint_as_float(v[j + 3])),
-                         pack_bf16(__uint_as_float(v[j + 4]), __uint_as_float(v[j + 5])),
-                         pack_bf16(__uint_as_float(v[j + 6]), __uint_as_float(v[j + 7])));
-      } else {
-        uint32_t v[16];
-        if (n > 0) { tmem_ld16(t_lane + ACC + g * 16, v); tmem_ld_wait(); }
-        else {
-#pragma unroll
-          for (int j = 0; j < 16; ++j) v[j] = 0u;
-        }
-#pragma unroll
-        for (int j = 0; j < 16; j += 8)
-          *reinterpret_cast<uint4*>(dst + j) =
-              make_uint4(pack_bf16(__uint_as_float(v[j]), __uint_as_float(v[j + 1])),
-                         pack_bf16(__uint_as_float(v[j + 2]), __uint_as_float(v[j + 3])),
-                         pack_bf16(__uint_as_float(v[j + 4]), __uint_as_float(v[j + 5])),
-                         pack_bf16(__uint_as_float(v[j + 6]), __uint_as_float(v[j + 7])));
-      }
-    }
-    tc_fence_before();
-    __syncthreads();                                               // the next unit's MMAs overwrite the accumulators
-    tc_fence_after();
-    U = Un;
-  }
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 0) tmem_dealloc(tmem, ncols);
-}
-
 constexpr size_t MM_SMEM(int tile_bytes) { return 1024 + (size_t)2 * 2 * 2 * tile_bytes + 128; }
 
 // =====================================================================================
@@ -738,23 +495,24 @@ namespace tc {
 template <int D>
 static int rc_attrs(TcState* s, int device) {
   int n = 0, rc;
-  s->rc_row_ctas = s->rc_col_ctas = 1 << 30;
+  s->rc_row_ctas = 1 << 30;
 #define SPION_RC_ATTR(SB)                                                                                                   \
   SPION_CUDA_TRY(cudaFuncSetAttribute(k_bwd_row_rc<D, SB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)rc_row_smem<D>())); \
-  SPION_CUDA_TRY(cudaFuncSetAttribute(k_bwd_col_rc<D, SB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)rc_col_smem<D>())); \
   SPION_CUDA_TRY(cudaFuncSetAttribute(k_mean_map_rc<D, SB>, cudaFuncAttributeMaxDynamicSharedMemorySize,                    \
                                       (int)MM_SMEM(OpTile<D>::BYTES)));                                                     \
   if ((rc = resident_ctas(k_bwd_row_rc<D, SB>, device, RC_THREADS, rc_row_smem<D>(), 256, &n))) return rc;                  \
   s->rc_row_ctas = n < s->rc_row_ctas ? n : s->rc_row_ctas;                                                                 \
-  if ((rc = resident_ctas(k_bwd_col_rc<D, SB>, device, RC_THREADS, rc_col_smem<D>(), 256, &n))) return rc;                  \
-  s->rc_col_ctas = n < s->rc_col_ctas ? n : s->rc_col_ctas;
+
   SPION_RC_ATTR(false)
   SPION_RC_ATTR(true)
 #undef SPION_RC_ATTR
   return SPION_OK;
 }
 
-int recompute_set_attrs(TcState* s, int d, int device) { return d == 64 ? rc_attrs<64>(s, device) : rc_attrs<32>(s, device); }
+int recompute_set_attrs(TcState* s, int d, int device) {
+  int rc = d == 64 ? rc_attrs<64>(s, device) : rc_attrs<32>(s, device);
+  return rc ? rc : col_stream_set_attrs(d);
+}
 
 template <int D>
 static int rc_backward(spion_ctx* c, TcState* s, const void* Q, const void* K, const void* V, const void* O, const void* dO,
@@ -767,21 +525,18 @@ static int rc_backward(spion_ctx* c, TcState* s, const void* Q, const void* K, c
     return rc;
   prof_mark(c, -1);
   const long long total = (long long)c->BH * vw.nb;
-  const long long row_cap = (long long)s->sms * s->rc_row_ctas, col_cap = (long long)s->sms * s->rc_col_ctas;
-  const int grid_row = (int)(total < row_cap ? total : row_cap), grid_col = (int)(total < col_cap ? total : col_cap);
+  const long long row_cap = (long long)s->sms * s->rc_row_ctas;
+  const int grid_row = (int)(total < row_cap ? total : row_cap);
 #define SPION_RC_LAUNCH(SB)                                                                                              \
   k_bwd_row_rc<D, SB><<<grid_row, RC_THREADS, rc_row_smem<D>(), c->stream>>>(                                             \
       mq, mk, mv, mdo, (const __nv_bfloat16*)dO, (const __nv_bfloat16*)O, lse, keypad, s->delta_ws, (__nv_bfloat16*)dQ,   \
       vw.row_info, vw.col_idx, vw.submask, c->L, c->BH, vw.nb, c->heads, c->scale, c->status_dev);                        \
   SPION_LAUNCH_CHECK();                                                                                                  \
-  prof_mark(c, SPION_STAGE_BWD_ROW_RC);                                                                                  \
-  k_bwd_col_rc<D, SB><<<grid_col, RC_THREADS, rc_col_smem<D>(), c->stream>>>(                                             \
-      mq, mk, mv, mdo, lse, s->delta_ws, keypad, (__nv_bfloat16*)dK, (__nv_bfloat16*)dV, vw.col_ptr, vw.row_idx,          \
-      vw.csc_pos, s->col_order, vw.submask, c->L, c->BH, vw.nb, c->heads, c->scale, c->status_dev);                       \
-  SPION_LAUNCH_CHECK();                                                                                                  \
-  prof_mark(c, SPION_STAGE_BWD_COL_RC);
+  prof_mark(c, SPION_STAGE_BWD_ROW_RC);
   if (vw.submask) { SPION_RC_LAUNCH(true) } else { SPION_RC_LAUNCH(false) }
 #undef SPION_RC_LAUNCH
+  if ((rc = col_stream_backward(c, s, mq, mk, mv, mdo, lse, keypad, dK, dV))) return rc;
+  prof_mark(c, SPION_STAGE_BWD_COL_RC);
   c->launches += 2;
   return SPION_OK;
 }

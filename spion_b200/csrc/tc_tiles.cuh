@@ -79,9 +79,18 @@ __device__ __forceinline__ void trace_stamp(int unit_ordinal, int k) {
     g_spion_trace[((size_t)blockIdx.x * g_spion_trace_units + unit_ordinal) * 16 + k] = t;
   }
 }
+__device__ __forceinline__ void trace_stamp_t(int thread, int unit_ordinal, int k) {
+  if ((int)threadIdx.x == thread && g_spion_trace && unit_ordinal < g_spion_trace_units) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)::"memory");
+    g_spion_trace[((size_t)blockIdx.x * g_spion_trace_units + unit_ordinal) * 16 + k] = t;
+  }
+}
 #define SPION_STAMP(u, k) trace_stamp(u, k)
+#define SPION_STAMP_T(t, u, k) trace_stamp_t(t, u, k)
 #else
 #define SPION_STAMP(u, k)
+#define SPION_STAMP_T(t, u, k)
 #endif
 
 // Where the [L x D] operand matrix of (b,h) pair `bh` starts inside the 2-D tensor the maps describe.
@@ -123,13 +132,17 @@ struct TcState {
   EncodeTiledFn encode = nullptr;
   int sms = 0;                  // multiprocessors of the context's device
   int fwd_ctas = 0, row_ctas = 0, col_ctas = 0;   // resident CTAs per SM of the persistent kernels
-  int rc_row_ctas = 0, rc_col_ctas = 0;           // ... of the two recompute backward kernels
+  int rc_row_ctas = 0;                            // ... of the recompute row kernel (the column kernel: one per SM)
   int pipe_ctas = 0;                              // ... of the pipelined forward for short rows
   int n_long = 0;               // block rows with more than ROW_NCH blocks: the first n_long records of row_info
   int* n_long_dev = nullptr;
   float* delta_ws = nullptr;    // [BH*L] delta_i = sum_n dO_in O_in, written by the row kernel, read by the column kernel
   float* lse_ws = nullptr;      // [BH*L] log-sum-exp workspace for the calls that do not expose it
   int* col_order = nullptr;     // block columns from the longest to the shortest
+  // the same columns as records for the streaming column kernel: one load per column / per pair of entries
+  int4* col_rec = nullptr;      // [nb] in col_order: {block column, first pair, pairs, entries}
+  int4* col_pair = nullptr;     // [sum of pairs] {block row of entry 0, of entry 1 (-1: none), CSR block id 0, 1}
+  size_t col_pair_cap = 0;
   int4* row_info = nullptr;     // per block row: {row_ptr, blocks, col0 | col1 << 16, col2 | col3 << 16}: one load instead of two dependent ones
   // 32-wide masks run on 64-wide super-blocks: derived structure + which 32x32 quarters are selected
   bool super = false;
@@ -204,6 +217,11 @@ inline int make_operand_map(const spion_ctx* c, TcState* s, CUtensorMap* m, cons
   if (c->heads == 0) return make_map(s, m, base, (uint64_t)c->BH * c->L, (uint32_t)D, (uint32_t)D, BS);
   return make_map(s, m, base, (uint64_t)(c->BH / c->heads) * c->L, (uint32_t)(c->heads * D), (uint32_t)D, BS);
 }
+
+// tc_recompute_col.cu: streaming column kernel of the recompute backward (reads the context's delta array)
+int col_stream_set_attrs(int d);
+int col_stream_backward(spion_ctx* c, TcState* s, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
+                        const CUtensorMap& mdo, const float* lse, const float* keypad, void* dK, void* dV);
 
 // tc_recompute.cu
 int recompute_set_attrs(TcState* s, int d, int device);

@@ -135,25 +135,34 @@ class Trainer:
         self.mat_lst = None
         self.patterns = None
         self._graph = None
+        self.allreduce_events = None     # set to a list to collect (start, end) CUDA events around the gradient all-reduce
 
     def step(self, ids, label, is_attn=False):
         self.bucket.zero()
         loss, maps = self.model(ids, label, self.mat_lst, is_attn)
         loss.backward()
-        self.bucket.allreduce_mean()
+        if self.allreduce_events is not None:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            self.bucket.allreduce_mean()
+            e1.record()
+            self.allreduce_events.append((e0, e1))
+        else:
+            self.bucket.allreduce_mean()
         torch.nn.utils.clip_grad_value_(self.model.parameters(), 1.0)   # main_conv_ff.py:186
         self.opt.step()
         return loss.detach(), maps
 
     def capture_sparse_step(self, ids, label, warmup: int = 3):
-        """Record one sparse step (forward, backward, optimizer) of a single-rank job as a CUDA graph: the
-        step is a few hundred small launches, so replaying it removes most of the host time.  The library's
-        calls are plain stream-ordered launches with caller-owned buffers, which is what capture needs.
-        With more than one rank the step contains the gradient all-reduce and is not captured."""
+        """Record one sparse step as CUDA graphs: the step is a few hundred small launches, so replaying it
+        removes most of the host time (at 8 samples per GPU the eager step is host-bound).  The library's calls
+        are plain stream-ordered launches with caller-owned buffers, which is what capture needs.
+        One rank: a single graph (forward, backward, clipping, optimizer).  Several ranks: two graphs --
+        forward + backward, and clipping + optimizer -- with the gradient all-reduce issued eagerly between
+        the two replays, so that no collective is ever part of a capture."""
         if self.mat_lst is None:
             raise RuntimeError("capture the step after discover()")
-        if dp.world_size() > 1:
-            raise RuntimeError("the captured step must not contain the gradient all-reduce: run multi-rank steps eagerly")
+        multi = dp.world_size() > 1
         dual = isinstance(ids, (tuple, list))
         self._g_ids = tuple(t.clone() for t in ids) if dual else ids.clone()
         self._g_lab = label.clone()
@@ -166,8 +175,22 @@ class Trainer:
         cur.wait_stream(side)
         torch.cuda.synchronize()
         self._graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self._graph):
-            self._g_loss, _ = self.step(self._g_ids, self._g_lab)
+        self._graph_opt = None
+        if not multi:
+            with torch.cuda.graph(self._graph):
+                self._g_loss, _ = self.step(self._g_ids, self._g_lab)
+            return self._graph
+        # other threads of the process (the collective library's watchdog) may query events while this thread
+        # captures: only this thread's calls belong to the capture
+        with torch.cuda.graph(self._graph, capture_error_mode="thread_local"):
+            self.bucket.zero()
+            loss, _ = self.model(self._g_ids, self._g_lab, self.mat_lst, False)
+            loss.backward()
+            self._g_loss = loss.detach()
+        self._graph_opt = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self._graph_opt, capture_error_mode="thread_local"):
+            torch.nn.utils.clip_grad_value_(self.model.parameters(), 1.0)
+            self.opt.step()
         return self._graph
 
     def step_graph(self, ids, label):
@@ -178,7 +201,23 @@ class Trainer:
         else:
             self._g_ids.copy_(ids, non_blocking=True)
         self._g_lab.copy_(label, non_blocking=True)
+        ev = None
+        if self.allreduce_events is not None:
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+            ev[0].record()
         self._graph.replay()
+        if ev:
+            ev[1].record()
+        if self._graph_opt is not None:
+            self.bucket.allreduce_mean()                      # eager, between the two replays
+            if ev:
+                ev[2].record()
+            self._graph_opt.replay()
+        if ev:
+            if self._graph_opt is None:
+                ev[2].record()
+            ev[3].record()
+            self.allreduce_events.append(tuple(ev))
         return self._g_loss
 
     def discover(self, maps, threshold=None):
