@@ -53,6 +53,7 @@ TRAIN_WORKLOADS = {
     "train_image_L1024": ("image", 256, "fp32", 0.80, "weak"),
     "train_text_L4096": ("text", 32, "bf16", 0.90, "weak"),
     "train_retrieval_L4096": ("retrieval", 64, "bf16", 0.90, "strong"),
+    "train_retrieval_L4096_b8": ("retrieval", 8, "bf16", 0.90, "weak"),     # the per-GPU share of the 8-GPU run, per rank
     "train_tiny": ("text", 2, "bf16", 0.85, "weak"),
 }
 
@@ -60,13 +61,15 @@ TRAIN_WORKLOADS = {
 # dram__bytes_read.sum + dram__bytes_write.sum per launch, from one ncu capture of the same workload and
 # kernels (the summaries are kept under profiles/; NCU_TRAFFIC_SOURCE names the one each entry comes from)
 NCU_TRAFFIC = {
-    "sweep_L4096_bs64_d05": {"fused_fwd": 251.5e6, "bwd_row": 349.0e6, "spmm_dkdv": 333.0e6},
-    "image_L1024_fp32_B256": {"fused_fwd": 581.9e6, "bwd_row": 971.0e6, "spmm_dkdv": 903.6e6},
+    # workload: {stage: bytes}; the forward entry depends on whether P is stored ("fused_fwd+P" / "fused_fwd")
+    "sweep_L4096_bs64_d05": {"fused_fwd+P": 248.9e6, "bwd_row": 420.3e6, "spmm_dkdv": 336.4e6,
+                             "fused_fwd": 134.4e6, "bwd_row_rc": 228.4e6, "bwd_col_rc": 174.9e6},
+    "image_L1024_fp32_B256": {"fused_fwd+P": 581.9e6, "bwd_row": 971.0e6, "spmm_dkdv": 903.6e6},
 }
 
 
 NCU_TRAFFIC_SOURCE = {
-    "sweep_L4096_bs64_d05": "ncu dram bytes per launch, profiles/tcgen05_fused_pipeline_sweep_L4096_bs64_d05.md",
+    "sweep_L4096_bs64_d05": "ncu dram bytes per launch, profiles/tcgen05_kernels_sweep_L4096_bs64_d05.md",
     "image_L1024_fp32_B256": "ncu dram bytes per launch, profiles/simt_fused_fp32_image_L1024_bs32.md",
 }
 
@@ -710,7 +713,8 @@ def main():
     dom_bytes = stage_bytes(dom, BH, L, d, nnz, esz, psz, p_stored=not fused_bwd)
     achieved = dom_bytes / (stages[dom] * 1e-3) / 1e9
     roofline = {"kernel": dom, "bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                "frac": achieved / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC.get(args.workload, {}).get(dom),
+                "frac": achieved / peaks["hbm_gbs"],
+                "traffic": NCU_TRAFFIC.get(args.workload, {}).get(dom + "+P" if (dom == "fused_fwd" and not fused_bwd) else dom),
                 "traffic_source": NCU_TRAFFIC_SOURCE.get(args.workload),
                 "peak_source": peaks["source"],
                 "algorithmic_bytes_per_launch": dom_bytes, "ms_per_launch": stages[dom]}
