@@ -15,7 +15,10 @@ struct DeviceGuard {
   bool ok = true;
   explicit DeviceGuard(int dev) {
     if (cudaGetDevice(&prev) != cudaSuccess) { ok = false; return; }
-    if (dev >= 0 && dev != prev) ok = cudaSetDevice(dev) == cudaSuccess;
+    // Always, not only when the device differs: cudaSetDevice also binds the device's primary context to the
+    // calling thread, which the driver entry point that encodes tensor maps needs (a thread of the autograd
+    // engine that has not launched anything yet has no context bound, cudaGetDevice does not bind one).
+    if (dev >= 0) ok = cudaSetDevice(dev) == cudaSuccess;
   }
   ~DeviceGuard() { if (prev >= 0) cudaSetDevice(prev); }
 };

@@ -771,6 +771,7 @@ int tc_engine_prepare(spion_ctx* c) {
     if (!rc) rc = fused_set_attrs(s, c->d, c->device);
     if (!rc) rc = recompute_set_attrs(s, c->d, c->device);
     if (!rc) rc = pipe_set_attrs(s, c->d, c->device);
+    if (!rc && b32_applies(c)) { rc = b32_set_attrs(s, c->device); s->b32 = rc == SPION_OK; }
     if (!rc && cudaMalloc(&s->delta_ws, (size_t)c->BH * c->L * sizeof(float)) != cudaSuccess) rc = SPION_ERR_ALLOC;
     if (!rc && cudaMalloc(&s->lse_ws, (size_t)c->BH * c->L * sizeof(float)) != cudaSuccess) rc = SPION_ERR_ALLOC;
     if (rc) { delete s; return rc; }
@@ -779,6 +780,10 @@ int tc_engine_prepare(spion_ctx* c) {
   }
   if (s->super) {
     int rc = build_super(c, s);
+    if (rc) return rc;
+  }
+  if (s->b32) {
+    int rc = b32_prepare(c, s);
     if (rc) return rc;
   }
   const TcView vw = tc_view(c, s);
@@ -811,6 +816,7 @@ void tc_engine_release(spion_ctx* c) {
   if (!c->tc) return;
   TcState* s = (TcState*)c->tc;
   free_super(s);
+  b32_release(s);
   cudaFree(s->lse_ws);
   cudaFree(s->delta_ws);
   cudaFree(s->n_long_dev);
@@ -828,6 +834,7 @@ static int forward_any(spion_ctx* c, const void* Q, const void* K, const void* V
   TcState* s = (TcState*)c->tc;
   if (!s) return SPION_ERR_STATE;
   if (c->nnzb == 0) return SPION_ERR_SHAPE;
+  if (s->b32 && !P_user) return b32_forward(c, s, Q, K, V, keypad, O, lse ? lse : s->lse_ws);
   void* P64 = P_user ? (s->super ? s->p64_ws : P_user) : nullptr;
   int rc = fused_forward(c, s, Q, K, V, keypad, O, lse ? lse : s->lse_ws, P64);
   if (rc || !P_user || !s->super) return rc;
@@ -860,7 +867,9 @@ int tc_engine_backward_fused(spion_ctx* c, const void* Q, const void* K, const v
                              const float* lse, const float* keypad, void* dQ, void* dK, void* dV) {
   if (!c->tc) return SPION_ERR_STATE;
   if (c->nnzb == 0) return SPION_ERR_SHAPE;
-  return recompute_backward(c, (TcState*)c->tc, Q, K, V, O, dO, lse, keypad, dQ, dK, dV);
+  TcState* s = (TcState*)c->tc;
+  if (s->b32) return b32_backward(c, s, Q, K, V, O, dO, lse, keypad, dQ, dK, dV);
+  return recompute_backward(c, s, Q, K, V, O, dO, lse, keypad, dQ, dK, dV);
 }
 
 int tc_engine_mean_map(spion_ctx* c, const void* Q, const void* K, const float* lse, const float* keypad, float* A) {

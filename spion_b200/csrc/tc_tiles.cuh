@@ -152,6 +152,11 @@ struct TcState {
           *csc_pos64 = nullptr, *work64 = nullptr, *nnzb64_dev = nullptr;
   void* p64_ws = nullptr; void* ds64_ws = nullptr;     // [BH, nnzb64, 64, 64] bf16 each
   size_t ws_elems = 0;
+  // 32-wide masks with head_dim 64: kernels on the mask's own blocks (tc_b32.cu) for the calls without stored P
+  bool b32 = false;
+  int b32_ctas[3] = {0, 0, 0};  // resident CTAs per SM of the forward / row / column kernel
+  int4* b32_row_rec = nullptr;  // [nb] block rows, longest first: {row_ptr, blocks, block row, 0}
+  int4* b32_col_rec = nullptr;  // [nb] block columns likewise: {col_ptr, entries, block column, 0}
 };
 
 // What the kernels see: the 64-block structure (the mask's own, or the derived super-block one).
@@ -234,6 +239,16 @@ int recompute_mean_map(spion_ctx* c, TcState* s, const void* Q, const void* K, c
 int pipe_set_attrs(TcState* s, int d, int device);
 int pipe_forward(spion_ctx* c, TcState* s, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
                  const CUtensorMap& mp, bool store_p, const float* keypad, void* O, float* lse, int rank0);
+
+// tc_b32.cu: masks of 32-wide blocks on the blocks themselves (bf16, head_dim 64; no stored P)
+bool b32_applies(const spion_ctx* c);
+int b32_set_attrs(TcState* s, int device);
+int b32_prepare(spion_ctx* c, TcState* s);
+void b32_release(TcState* s);
+int b32_forward(spion_ctx* c, TcState* s, const void* Q, const void* K, const void* V, const float* keypad, void* O,
+                float* lse);
+int b32_backward(spion_ctx* c, TcState* s, const void* Q, const void* K, const void* V, const void* O, const void* dO,
+                 const float* lse, const float* keypad, void* dQ, void* dK, void* dV);
 
 // tc_fused.cu
 int fused_set_attrs(TcState* s, int d, int device);
