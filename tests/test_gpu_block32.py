@@ -22,7 +22,7 @@ def cfg(B, H, L, d, bs):
 
 
 def rel(a, b):
-    b = b.float().cpu()
+    b = b.detach().float().cpu()
     return float((a.detach().float().cpu() - b).abs().max() / b.abs().max().clamp_min(1e-30))
 
 
