@@ -500,7 +500,7 @@ def run_sweep_table(args, rank, world, local_rank):
         for bs in (32, 64):
             cfg = {"head_dim": d, "num_head": H, "max_seq_len": L, "batch_size": B, "block_size": bs,
                    "transformer_dim": H * d, "task": "sweep"}
-            mod = BlockSparseAttention(cfg, dtype=torch.bfloat16, device=dev)
+            mod = BlockSparseAttention(cfg, dtype=torch.bfloat16, device=dev, block32=args.block32)
             check(lib.spion_set_stream(mod.handle, _lib.current_stream_ptr()))
             for dens in (0.02, 0.05, 0.10, 0.30):
                 mat = synthetic.band_random_mask(2024 + bs, L // bs, dens)
@@ -563,6 +563,8 @@ def main():
                     help="fused: S, P, dP, dS stay on chip, the backward rebuilds its tiles (tcgen05 engine); "
                          "stored: fused forward that stores P, backward kernels that read P and write dS; "
                          "staged: one kernel per stage")
+    ap.add_argument("--block32", default="auto", choices=["auto", "own", "super"],
+                    help="32-wide masks on the tensor-core engine: kernels on the mask's own blocks, on 64-wide super-blocks, or chosen per mask")
     ap.add_argument("--repeats", type=int, default=5, help="how often the timed loop of --steps steps is repeated")
     ap.add_argument("--no-graph", action="store_true", help="training workloads: launch the step eagerly")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -612,7 +614,8 @@ def main():
               "staged": _lib.ENGINE_SIMT_STAGED}[args.engine]
     mod = BlockSparseAttention(cfg, dtype=tdt, engine=engine, device=dev,
                                fused=None if args.mode == "auto" else (args.mode in ("fused", "stored")),
-                               return_probs=False, recompute={"fused": True, "stored": False}.get(args.mode))
+                               return_probs=False, recompute={"fused": True, "stored": False}.get(args.mode),
+                               block32=args.block32)
     fused_fwd = mod.fused
     mat = synthetic.band_random_mask(2024, nb, dens)          # same mask on every rank (one layer)
     nnzb = mod.set_mask(torch.as_tensor(mat).to(dev))

@@ -84,6 +84,17 @@ int spion_check_device_status(spion_ctx* ctx);
  *   their (b*H + h)-major layouts.  UNSUPPORTED on contexts the tcgen05 engine cannot run. */
 int spion_set_head_layout(spion_ctx* ctx, int heads);
 
+/* Masks of 32 x 32 blocks on the tcgen05 engine (bf16, head_dim 64) have two sets of kernels for the calls that
+ * store no probabilities (spion_attn_forward_fused with P_optional == NULL, spion_attn_backward_fused):
+ *   1: on the mask's own blocks (up to four selected blocks gathered into one 128-row operand; no unselected
+ *      block is ever computed);
+ *   2: on derived 64 x 64 super-blocks whose unselected quarters are masked (also what serves head_dim 32 and
+ *      every call that stores P);
+ *   0 (default): chosen when the mask is set -- 1 when the gathered operands are at least 70 % full on
+ *      average (masks with three or more blocks per block row), else 2.
+ * Takes effect when the next pattern is set.  No counterpart in the reference. */
+int spion_set_block32_path(spion_ctx* ctx, int path);
+
 /* Failure-path self-test that faults nothing: launches one CTA that waits, with the given limit
  * in clock cycles (at most 2e9), on a barrier nobody arrives on.  The kernel gives up, records the
  * time-out in the status word and exits normally; the call then returns what

@@ -31,6 +31,7 @@ SIGNATURES = {
     "spion_needs_scratch": (c_int, [c_void_p]),
     "spion_check_device_status": (c_int, [c_void_p]),
     "spion_set_head_layout": (c_int, [c_void_p, c_int]),
+    "spion_set_block32_path": (c_int, [c_void_p, c_int]),
     "spion_csr_arrays_are_stable": (c_int, [c_void_p, c_int]),
     "spion_selftest_bounded_wait": (c_int, [c_void_p, c_longlong]),
     "spion_launch_count": (c_longlong, [c_void_p]),

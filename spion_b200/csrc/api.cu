@@ -78,6 +78,7 @@ extern "C" spion_ctx* spion_create(int kind, int head_dim, int seq_len, int num_
   c->launches = 0;
   c->tc = nullptr;
   c->heads = 0;
+  c->block32_path = 0;
   c->csr_stable = 0; c->csr_key[0] = c->csr_key[1] = c->csr_key[2] = nullptr; c->csr_nnz = -1;
   c->prof_on = 0; c->prof_n = 0;
   for (int i = 0; i < SPION_PROF_MAX_MARKS; ++i) { c->prof_ev[i] = nullptr; c->prof_stage[i] = -1; }
@@ -149,6 +150,12 @@ extern "C" int spion_set_head_layout(spion_ctx* c, int heads) {
     if (c->BH % heads != 0) return SPION_ERR_SHAPE;
   }
   c->heads = heads;
+  return SPION_OK;
+}
+
+extern "C" int spion_set_block32_path(spion_ctx* c, int path) {
+  if (!c || path < 0 || path > 2) return SPION_ERR_ARG;
+  c->block32_path = path;
   return SPION_OK;
 }
 

@@ -73,6 +73,7 @@ __device__ __forceinline__ void tile_address(const ValueLayout& vl, const Patter
 struct spion_ctx {
   int kind, d, L, BH, bs, nb, dtype, device, engine;
   int heads;                // 0: operands [BH, L, d]; H > 0: operands [B, L, H, d] (tensor-core engine only)
+  int block32_path;         // 32-wide masks on the tensor-core engine: 0 chosen per mask, 1 the mask's own blocks, 2 super-blocks
   float scale;
   cudaStream_t stream;
   // structure workspace (device), capacity nb*nb blocks

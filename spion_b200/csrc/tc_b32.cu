@@ -659,8 +659,9 @@ namespace {
 // id0 | id1 << 16, id2 | id3 << 16} (the ids of the line's first four blocks), from the longest to the shortest
 // line (ties: ascending index).  One CTA.
 __global__ void k_b32_recs(const int32_t* __restrict__ line_ptr, const int32_t* __restrict__ ids, int nb,
-                           int4* __restrict__ rec) {
+                           int4* __restrict__ rec, int* __restrict__ jobs_out) {
   __shared__ int s_n[SPION_MAX_NB];
+  if (jobs_out && threadIdx.x == 0) *jobs_out = 0;
   for (int i = threadIdx.x; i < nb; i += blockDim.x) s_n[i] = line_ptr[i + 1] - line_ptr[i];
   __syncthreads();
   for (int i = threadIdx.x; i < nb; i += blockDim.x) {
@@ -670,6 +671,12 @@ __global__ void k_b32_recs(const int32_t* __restrict__ line_ptr, const int32_t* 
     int c[4] = {0, 0, 0, 0};
     for (int t = 0; t < 4 && t < n; ++t) c[t] = ids[p + t];
     rec[rank] = make_int4(p, n | (i << 16), c[0] | (c[1] << 16), c[2] | (c[3] << 16));
+  }
+  if (jobs_out) {                                  // gathered jobs of all lines: sum of ceil(blocks / 4)
+    __syncthreads();
+    int mine = 0;
+    for (int i = threadIdx.x; i < nb; i += blockDim.x) mine += (s_n[i] + GN - 1) / GN;
+    atomicAdd(jobs_out, mine);
   }
 }
 
@@ -695,10 +702,7 @@ int b32_grid(const spion_ctx* c, const TcState* s) {
 
 namespace tc {
 
-bool b32_applies(const spion_ctx* c) {
-  static const bool off = [] { const char* e = getenv("SPION_BLOCK32_SUPERBLOCKS"); return e && e[0] == '1'; }();
-  return !off && c->bs == B32 && c->d == HD;
-}
+bool b32_applies(const spion_ctx* c) { return c->bs == B32 && c->d == HD; }
 
 int b32_set_attrs(TcState* s, int device) {
   int rc;
@@ -707,22 +711,34 @@ int b32_set_attrs(TcState* s, int device) {
   return SPION_OK;
 }
 
-// once per mask: the sorted row and column records of the mask's own 32-wide structure
+// Once per mask: the sorted row and column records of the mask's own 32-wide structure, and whether these
+// kernels or the super-block kernels serve the mask.  A job works on a 128-row operand gathered from up to
+// four blocks; with fewer than about three blocks per job (masks that are little more than their diagonal
+// band) the unused rows and the per-unit overhead cost more than the quarters the super-blocks waste
+// (measured on the L x density grid of the kernel sweep: the paths break even at 2.8 - 3.0 blocks per job).
 int b32_prepare(spion_ctx* c, TcState* s) {
   if (!s->b32_row_rec && cudaMalloc(&s->b32_row_rec, (size_t)SPION_MAX_NB * sizeof(int4)) != cudaSuccess) return SPION_ERR_ALLOC;
   if (!s->b32_col_rec && cudaMalloc(&s->b32_col_rec, (size_t)SPION_MAX_NB * sizeof(int4)) != cudaSuccess) return SPION_ERR_ALLOC;
-  k_b32_recs<<<1, 512, 0, c->stream>>>(c->row_ptr, c->col_idx, c->nb, s->b32_row_rec);
+  if (!s->b32_jobs_dev && cudaMalloc(&s->b32_jobs_dev, sizeof(int)) != cudaSuccess) return SPION_ERR_ALLOC;
+  k_b32_recs<<<1, 512, 0, c->stream>>>(c->row_ptr, c->col_idx, c->nb, s->b32_row_rec, s->b32_jobs_dev);
   SPION_LAUNCH_CHECK();
-  k_b32_recs<<<1, 512, 0, c->stream>>>(c->col_ptr, c->row_idx, c->nb, s->b32_col_rec);
+  k_b32_recs<<<1, 512, 0, c->stream>>>(c->col_ptr, c->row_idx, c->nb, s->b32_col_rec, nullptr);
   SPION_LAUNCH_CHECK();
   c->launches += 2;
+  int jobs = 0;
+  SPION_CUDA_TRY(cudaMemcpyAsync(&jobs, s->b32_jobs_dev, sizeof(int), cudaMemcpyDeviceToHost, c->stream));
+  SPION_CUDA_TRY(cudaStreamSynchronize(c->stream));                // pattern time: once per mask
+  s->b32_fill = jobs > 0 ? (float)c->nnzb / (float)jobs : 0.0f;
+  s->b32_use = c->block32_path == 1 || (c->block32_path == 0 && s->b32_fill >= 2.8f);
   return SPION_OK;
 }
 
 void b32_release(TcState* s) {
   cudaFree(s->b32_row_rec);
   cudaFree(s->b32_col_rec);
+  cudaFree(s->b32_jobs_dev);
   s->b32_row_rec = s->b32_col_rec = nullptr;
+  s->b32_jobs_dev = nullptr;
 }
 
 int b32_forward(spion_ctx* c, TcState* s, const void* Q, const void* K, const void* V, const float* keypad, void* O,

@@ -834,7 +834,7 @@ static int forward_any(spion_ctx* c, const void* Q, const void* K, const void* V
   TcState* s = (TcState*)c->tc;
   if (!s) return SPION_ERR_STATE;
   if (c->nnzb == 0) return SPION_ERR_SHAPE;
-  if (s->b32 && !P_user) return b32_forward(c, s, Q, K, V, keypad, O, lse ? lse : s->lse_ws);
+  if (s->b32 && s->b32_use && !P_user) return b32_forward(c, s, Q, K, V, keypad, O, lse ? lse : s->lse_ws);
   void* P64 = P_user ? (s->super ? s->p64_ws : P_user) : nullptr;
   int rc = fused_forward(c, s, Q, K, V, keypad, O, lse ? lse : s->lse_ws, P64);
   if (rc || !P_user || !s->super) return rc;
@@ -868,7 +868,7 @@ int tc_engine_backward_fused(spion_ctx* c, const void* Q, const void* K, const v
   if (!c->tc) return SPION_ERR_STATE;
   if (c->nnzb == 0) return SPION_ERR_SHAPE;
   TcState* s = (TcState*)c->tc;
-  if (s->b32) return b32_backward(c, s, Q, K, V, O, dO, lse, keypad, dQ, dK, dV);
+  if (s->b32 && s->b32_use) return b32_backward(c, s, Q, K, V, O, dO, lse, keypad, dQ, dK, dV);
   return recompute_backward(c, s, Q, K, V, O, dO, lse, keypad, dQ, dK, dV);
 }
 

@@ -153,7 +153,10 @@ struct TcState {
   void* p64_ws = nullptr; void* ds64_ws = nullptr;     // [BH, nnzb64, 64, 64] bf16 each
   size_t ws_elems = 0;
   // 32-wide masks with head_dim 64: kernels on the mask's own blocks (tc_b32.cu) for the calls without stored P
-  bool b32 = false;
+  bool b32 = false;             // the context's shape has these kernels
+  bool b32_use = false;         // ... and the current mask runs on them (spion_set_block32_path, else chosen per mask)
+  float b32_fill = 0.f;         // selected blocks per gathered job of the current mask (at most 4)
+  int* b32_jobs_dev = nullptr;
   int b32_ctas[3] = {0, 0, 0};  // resident CTAs per SM of the forward / row / column kernel
   int4* b32_row_rec = nullptr;  // [nb] block rows, longest first: {row_ptr, blocks, block row, 0}
   int4* b32_col_rec = nullptr;  // [nb] block columns likewise: {col_ptr, entries, block column, 0}

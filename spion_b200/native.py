@@ -36,7 +36,7 @@ class ProbsHandle:
 
 class BlockSparseAttention(nn.Module):
     def __init__(self, config, dtype=torch.float32, keypad: bool = False, engine: int = _lib.ENGINE_AUTO,
-                 device=None, fused=None, return_probs: bool = True, recompute=None):
+                 device=None, fused=None, return_probs: bool = True, recompute=None, block32: str = "auto"):
         super().__init__()
         self.d = config["head_dim"]
         self.H = config["num_head"]
@@ -54,6 +54,9 @@ class BlockSparseAttention(nn.Module):
         self.handle = _lib.c_void_p(h)
         check(lib.spion_set_engine(self.handle, engine), "spion_set_engine")
         self.engine = engine
+        # 32-wide masks, bf16, head_dim 64, calls without stored probabilities: kernels on the mask's own blocks
+        # ("own"), on 64-wide super-blocks ("super"), or chosen per mask by how full the gathered operands are
+        check(lib.spion_set_block32_path(self.handle, {"auto": 0, "own": 1, "super": 2}[block32]), "spion_set_block32_path")
         self.needs_scratch = bool(lib.spion_needs_scratch(self.handle))
         # fused kernels (S, P, dP, dS stay on chip) where the tensor-core engine covers the shape
         can_fuse = bool(lib.spion_supports_fused(self.handle))

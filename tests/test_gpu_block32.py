@@ -26,7 +26,7 @@ def rel(a, b):
     return float((a.detach().float().cpu() - b).abs().max() / b.abs().max().clamp_min(1e-30))
 
 
-def run(B, H, L, mat, keypad=None, seed=5, merged=False):
+def run(B, H, L, mat, keypad=None, seed=5, merged=False, path="own"):
     """forward + backward through the public module without stored probabilities (the calls the block-32
     kernels serve); returns (O, dQ, dK, dV) as float CPU tensors and the inputs."""
     from spion_b200 import _lib
@@ -34,7 +34,7 @@ def run(B, H, L, mat, keypad=None, seed=5, merged=False):
     d, bs = 64, 32
     Q, K, V, dO = [t.to(torch.bfloat16) for t in synthetic.qkv(seed, B, H, L, d)]
     mod = BlockSparseAttention(cfg(B, H, L, d, bs), dtype=torch.bfloat16, keypad=keypad is not None,
-                               engine=_lib.ENGINE_TCGEN05, recompute=True, return_probs=False)
+                               engine=_lib.ENGINE_TCGEN05, recompute=True, return_probs=False, block32=path)
     assert mod.fused and mod.recompute
 
     def prep(t):
@@ -111,6 +111,21 @@ def test_merged_head_operands():
     (Q, K, V, dO), merged = run(2, 3, 512, mat, seed=21, merged=True)
     for name, a, b in zip(("O", "dQ", "dK", "dV"), packed, merged):
         assert torch.equal(a, b), f"{name}: merged-head operands give different numbers than packed ones"
+
+
+@pytest.mark.parametrize("dens,own", [(0.02, False), (0.3, True)])
+def test_path_chosen_per_mask(dens, own):
+    """With block32="auto" a mask that is little more than its diagonal band (about two blocks per row) stays on
+    the super-blocks, a mask with fuller rows runs on its own blocks; both give the oracle's numbers, and the
+    choice shows in the kernels' stage timers (the two paths report different stage sets)."""
+    B, H, L = 2, 2, 2048
+    mat = synthetic.band_random_mask(2056, L // 32, dens)
+    fill = mat.sum() / np.ceil(mat.sum(1) / 4).sum()
+    assert (fill >= 2.8) == own, fill
+    (Q, K, V, dO), got = run(B, H, L, mat, seed=17, path="auto")
+    O, _, gQ, gK, gV = oatt.sparse_attention(Q.float(), K.float(), V.float(), mat, 32, None, dO.float())
+    for name, a, b in zip(("O", "dQ", "dK", "dV"), got, (O, gQ, gK, gV)):
+        assert rel(a, b) <= REL, f"{name}: {rel(a, b):.3e}"
 
 
 def test_agrees_with_the_super_block_path():
