@@ -311,6 +311,20 @@ int spion_attn_forward_static(const void* Q, const void* K, const void* V, const
                               const int32_t* blk_row, int head_dim, int seq_len, int num_batches,
                               int block_size, int nnzb, int dtype, void* cuda_stream);
 
+/* ------------------------------------------------------------------------------------------
+ * Layer normalisation of the encoder layers around the attention call (the reference uses
+ * torch.nn.LayerNorm: models/model_transformer.py).  [M, N] fp32 rows, N in {64, 128, 256, 512};
+ * biased variance, eps inside the square root.  y / dy are fp32 (is_bf16 == 0) or bf16.  mean, rstd: [M]
+ * (written by the forward, read by the backward).  The backward also returns the weight and bias
+ * gradients [N], summed in a fixed order (deterministic); workspace: spion_layernorm_workspace_floats(N)
+ * floats.  No context: the calls run on the stream given. */
+int spion_layernorm_forward(const float* x, const float* gamma, const float* beta, void* y, int y_is_bf16,
+                            float* mean, float* rstd, long long M, int N, float eps, void* cuda_stream);
+long long spion_layernorm_workspace_floats(int N);
+int spion_layernorm_backward(const float* x, const void* dy, int dy_is_bf16, const float* gamma, const float* mean,
+                             const float* rstd, float* dx, float* dgamma, float* dbeta, float* workspace,
+                             long long M, int N, void* cuda_stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -32,6 +32,11 @@ SIGNATURES = {
     "spion_check_device_status": (c_int, [c_void_p]),
     "spion_set_head_layout": (c_int, [c_void_p, c_int]),
     "spion_set_block32_path": (c_int, [c_void_p, c_int]),
+    "spion_layernorm_forward": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_longlong, c_int,
+                                ctypes.c_float, c_void_p]),
+    "spion_layernorm_workspace_floats": (c_longlong, [c_int]),
+    "spion_layernorm_backward": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                 c_void_p, c_longlong, c_int, c_void_p]),
     "spion_csr_arrays_are_stable": (c_int, [c_void_p, c_int]),
     "spion_selftest_bounded_wait": (c_int, [c_void_p, c_longlong]),
     "spion_launch_count": (c_longlong, [c_void_p]),

@@ -1,0 +1,209 @@
+// Layer normalisation over the last dimension of an [M, N] fp32 matrix, forward and backward, for the
+// encoder layers around the attention call (the reference uses torch.nn.LayerNorm:
+// models/model_transformer.py, `self.norm1 / self.norm2 / self.norm`).
+//
+// Why a kernel of its own: the rows are short (N = transformer_dim = 64 in the LRA configurations,
+// config.py) and there are B * L of them (32 768 .. 524 288 per call).  The backward of the framework's
+// operator computes the weight / bias gradients as a column reduction over all rows with a handful of
+// CTAs (it is the largest single kernel of the small-batch training step); here the same pass that forms
+// dX keeps per-lane partial sums of dgamma and dbeta in registers, one partial row per CTA goes to a
+// workspace, and a second small kernel adds the partial rows in a fixed order (deterministic results).
+//
+// HBM-bound by design: forward reads X and writes Y (+ two floats per row); backward reads X and dY and
+// writes dX.  One warp per row, lanes own the columns {2 l, 2 l + 1} + 64 k, rows are taken with stride
+// (warps in the grid).  Y and dY may be bf16 (what the following linear layers consume / produce under
+// mixed precision) or fp32.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int LN_WARPS = 8;                 // warps per CTA
+constexpr int LN_MAX_CTAS = 2048;           // partial rows of the weight / bias gradients
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+template <bool BF16> __device__ __forceinline__ float2 load2(const void* p, size_t i);
+template <> __device__ __forceinline__ float2 load2<false>(const void* p, size_t i) {
+  return *reinterpret_cast<const float2*>(static_cast<const float*>(p) + i);
+}
+template <> __device__ __forceinline__ float2 load2<true>(const void* p, size_t i) {
+  return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(static_cast<const __nv_bfloat16*>(p) + i));
+}
+template <bool BF16> __device__ __forceinline__ void store2(void* p, size_t i, float2 v);
+template <> __device__ __forceinline__ void store2<false>(void* p, size_t i, float2 v) {
+  *reinterpret_cast<float2*>(static_cast<float*>(p) + i) = v;
+}
+template <> __device__ __forceinline__ void store2<true>(void* p, size_t i, float2 v) {
+  *reinterpret_cast<__nv_bfloat162*>(static_cast<__nv_bfloat16*>(p) + i) = __float22bfloat162_rn(v);
+}
+
+// K = N / 64: pairs of columns per lane
+template <int K, bool Y_BF16>
+__global__ void __launch_bounds__(LN_WARPS * 32) ln_fwd_kernel(const float* __restrict__ x, const float* __restrict__ gamma,
+                                                               const float* __restrict__ beta, void* __restrict__ y,
+                                                               float* __restrict__ mean, float* __restrict__ rstd,
+                                                               long long M, float eps) {
+  constexpr int N = 64 * K;
+  const int lane = threadIdx.x & 31;
+  const long long warp0 = (long long)blockIdx.x * LN_WARPS + (threadIdx.x >> 5), nwarps = (long long)gridDim.x * LN_WARPS;
+  float2 g[K], b[K];
+#pragma unroll
+  for (int k = 0; k < K; ++k) {
+    g[k] = *reinterpret_cast<const float2*>(gamma + 64 * k + 2 * lane);
+    b[k] = *reinterpret_cast<const float2*>(beta + 64 * k + 2 * lane);
+  }
+  for (long long r = warp0; r < M; r += nwarps) {
+    float2 v[K];
+    float s = 0.f;
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      v[k] = *reinterpret_cast<const float2*>(x + r * N + 64 * k + 2 * lane);
+      s += v[k].x + v[k].y;
+    }
+    const float mu = warp_sum(s) * (1.0f / N);
+    float q = 0.f;
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const float dx = v[k].x - mu, dy = v[k].y - mu;
+      q += dx * dx + dy * dy;
+    }
+    const float rs = rsqrtf(warp_sum(q) * (1.0f / N) + eps);      // biased variance, as torch.nn.LayerNorm
+#pragma unroll
+    for (int k = 0; k < K; ++k)
+      store2<Y_BF16>(y, (size_t)r * N + 64 * k + 2 * lane,
+                     make_float2((v[k].x - mu) * rs * g[k].x + b[k].x, (v[k].y - mu) * rs * g[k].y + b[k].y));
+    if (lane == 0) { mean[r] = mu; rstd[r] = rs; }
+  }
+}
+
+template <int K, bool DY_BF16>
+__global__ void __launch_bounds__(LN_WARPS * 32) ln_bwd_kernel(const float* __restrict__ x, const void* __restrict__ dy,
+                                                               const float* __restrict__ gamma, const float* __restrict__ mean,
+                                                               const float* __restrict__ rstd, float* __restrict__ dx,
+                                                               float* __restrict__ partial, long long M) {
+  constexpr int N = 64 * K;
+  __shared__ float s_g[LN_WARPS][N], s_b[LN_WARPS][N];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const long long warp0 = (long long)blockIdx.x * LN_WARPS + warp, nwarps = (long long)gridDim.x * LN_WARPS;
+  float2 g[K], ag[K], ab[K];
+#pragma unroll
+  for (int k = 0; k < K; ++k) {
+    g[k] = *reinterpret_cast<const float2*>(gamma + 64 * k + 2 * lane);
+    ag[k] = make_float2(0.f, 0.f);
+    ab[k] = make_float2(0.f, 0.f);
+  }
+  for (long long r = warp0; r < M; r += nwarps) {
+    const float mu = mean[r], rs = rstd[r];
+    float2 xh[K], gy[K];
+    float c1 = 0.f, c2 = 0.f;
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const size_t i = (size_t)r * N + 64 * k + 2 * lane;
+      const float2 xv = *reinterpret_cast<const float2*>(x + i);
+      const float2 d = load2<DY_BF16>(dy, i);
+      xh[k] = make_float2((xv.x - mu) * rs, (xv.y - mu) * rs);
+      gy[k] = make_float2(d.x * g[k].x, d.y * g[k].y);
+      c1 += gy[k].x + gy[k].y;
+      c2 += gy[k].x * xh[k].x + gy[k].y * xh[k].y;
+      ag[k].x += d.x * xh[k].x; ag[k].y += d.y * xh[k].y;
+      ab[k].x += d.x; ab[k].y += d.y;
+    }
+    c1 = warp_sum(c1) * (1.0f / N);
+    c2 = warp_sum(c2) * (1.0f / N);
+#pragma unroll
+    for (int k = 0; k < K; ++k)
+      *reinterpret_cast<float2*>(dx + (size_t)r * N + 64 * k + 2 * lane) =
+          make_float2((gy[k].x - c1 - xh[k].x * c2) * rs, (gy[k].y - c1 - xh[k].y * c2) * rs);
+  }
+  // the CTA's partial row: the warps' sums added in warp order
+#pragma unroll
+  for (int k = 0; k < K; ++k) {
+    *reinterpret_cast<float2*>(&s_g[warp][64 * k + 2 * lane]) = ag[k];
+    *reinterpret_cast<float2*>(&s_b[warp][64 * k + 2 * lane]) = ab[k];
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < N; c += blockDim.x) {
+    float sg = 0.f, sb = 0.f;
+#pragma unroll
+    for (int w = 0; w < LN_WARPS; ++w) { sg += s_g[w][c]; sb += s_b[w][c]; }
+    partial[(size_t)blockIdx.x * 2 * N + c] = sg;
+    partial[(size_t)blockIdx.x * 2 * N + N + c] = sb;
+  }
+}
+
+// dgamma[c] = sum over the partial rows, in row order; likewise dbeta.  One thread per column.
+__global__ void ln_bwd_reduce_kernel(const float* __restrict__ partial, int rows, int N, float* __restrict__ dgamma,
+                                     float* __restrict__ dbeta) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= 2 * N) return;
+  float s = 0.f;
+  for (int r = 0; r < rows; ++r) s += partial[(size_t)r * 2 * N + c];
+  if (c < N) dgamma[c] = s; else dbeta[c - N] = s;
+}
+
+int ln_grid(long long M) {
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+    return -1;
+  long long want = (M + LN_WARPS - 1) / LN_WARPS, cap = (long long)sms * 8;   // 8 CTAs of 8 warps per SM: all warp slots
+  if (cap > LN_MAX_CTAS) cap = LN_MAX_CTAS;
+  return (int)(want < cap ? want : cap);
+}
+
+}  // namespace
+
+// N must be 64, 128, 256 or 512; rows are contiguous.  Returns SPION_ERR_SHAPE otherwise.
+extern "C" int spion_layernorm_forward(const float* x, const float* gamma, const float* beta, void* y, int y_is_bf16,
+                                       float* mean, float* rstd, long long M, int N, float eps, void* cuda_stream) {
+  cudaStream_t stream = (cudaStream_t)cuda_stream;
+  if (!x || !gamma || !beta || !y || !mean || !rstd || M < 1) return SPION_ERR_ARG;
+  const int grid = ln_grid(M);
+  if (grid < 1) return SPION_ERR_CUDA;
+#define SPION_LN_FWD(K)                                                                                              \
+  if (y_is_bf16) ln_fwd_kernel<K, true><<<grid, LN_WARPS * 32, 0, stream>>>(x, gamma, beta, y, mean, rstd, M, eps);  \
+  else ln_fwd_kernel<K, false><<<grid, LN_WARPS * 32, 0, stream>>>(x, gamma, beta, y, mean, rstd, M, eps);
+  switch (N) {
+    case 64: SPION_LN_FWD(1) break;
+    case 128: SPION_LN_FWD(2) break;
+    case 256: SPION_LN_FWD(4) break;
+    case 512: SPION_LN_FWD(8) break;
+    default: return SPION_ERR_SHAPE;
+  }
+#undef SPION_LN_FWD
+  SPION_LAUNCH_CHECK();
+  return SPION_OK;
+}
+
+// Floats the backward needs as workspace for a width of N.
+extern "C" long long spion_layernorm_workspace_floats(int N) { return (long long)LN_MAX_CTAS * 2 * N; }
+
+extern "C" int spion_layernorm_backward(const float* x, const void* dy, int dy_is_bf16, const float* gamma,
+                                        const float* mean, const float* rstd, float* dx, float* dgamma, float* dbeta,
+                                        float* workspace, long long M, int N, void* cuda_stream) {
+  cudaStream_t stream = (cudaStream_t)cuda_stream;
+  if (!x || !dy || !gamma || !mean || !rstd || !dx || !dgamma || !dbeta || !workspace || M < 1) return SPION_ERR_ARG;
+  const int grid = ln_grid(M);
+  if (grid < 1) return SPION_ERR_CUDA;
+#define SPION_LN_BWD(K)                                                                                                 \
+  if (dy_is_bf16) ln_bwd_kernel<K, true><<<grid, LN_WARPS * 32, 0, stream>>>(x, dy, gamma, mean, rstd, dx, workspace, M); \
+  else ln_bwd_kernel<K, false><<<grid, LN_WARPS * 32, 0, stream>>>(x, dy, gamma, mean, rstd, dx, workspace, M);
+  switch (N) {
+    case 64: SPION_LN_BWD(1) break;
+    case 128: SPION_LN_BWD(2) break;
+    case 256: SPION_LN_BWD(4) break;
+    case 512: SPION_LN_BWD(8) break;
+    default: return SPION_ERR_SHAPE;
+  }
+#undef SPION_LN_BWD
+  SPION_LAUNCH_CHECK();
+  ln_bwd_reduce_kernel<<<(2 * N + 127) / 128, 128, 0, stream>>>(workspace, grid, N, dgamma, dbeta);
+  SPION_LAUNCH_CHECK();
+  return SPION_OK;
+}

@@ -39,6 +39,17 @@ def task_config(task: str, batch_size: int, native: bool = True, dtype: str = "f
     return base
 
 
+def make_norm(config, feeds_linear: bool):
+    """LayerNorm of the encoder: the library's kernels when the configuration asks for the native path and the
+    width is one they serve, else torch.nn.LayerNorm (what the reference uses).  feeds_linear: the output only
+    goes into linear layers, so under mixed precision it may be bf16 straight away."""
+    from .layernorm import SUPPORTED_WIDTHS, FusedLayerNorm
+    dim = config["transformer_dim"]
+    if config.get("native") and config.get("fused_layernorm", True) and dim in SUPPORTED_WIDTHS:
+        return FusedLayerNorm(dim, bf16_out=feeds_linear)
+    return nn.LayerNorm(dim)
+
+
 class Embeddings(nn.Module):
     def __init__(self, config):
         super().__init__()
@@ -57,10 +68,10 @@ class TransformerLayer(nn.Module):
     def __init__(self, config):
         super().__init__()
         dim, hid, p = config["transformer_dim"], config["transformer_hidden_dim"], config["dropout_prob"]
-        self.norm1 = nn.LayerNorm(dim)
+        self.norm1 = make_norm(config, True)
         self.mha = Attention(config)
         self.dropout1 = nn.Dropout(p)
-        self.norm2 = nn.LayerNorm(dim)
+        self.norm2 = make_norm(config, True)
         self.mlpblock = nn.Sequential(nn.Linear(dim, hid), nn.GELU(), nn.Dropout(p), nn.Linear(hid, dim), nn.Dropout(p))
 
     def forward(self, X, mask, mat=None):
@@ -74,7 +85,7 @@ class Encoder(nn.Module):
         super().__init__()
         self.embeddings = Embeddings(config)
         self.layers = nn.ModuleList(TransformerLayer(config) for _ in range(config["num_layers"]))
-        self.norm = nn.LayerNorm(config["transformer_dim"])
+        self.norm = make_norm(config, False)
 
     def forward(self, ids, mask, mat_lst=None, is_attn=False):
         from .pattern import mean_attention_map

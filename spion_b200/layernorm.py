@@ -1,0 +1,71 @@
+"""Layer normalisation of the encoder layers through the library's kernels (csrc/layernorm.cu).
+
+Same arithmetic as ``torch.nn.LayerNorm`` over the last dimension (biased variance, eps inside the root;
+the reference's encoder uses that module: models/model_transformer.py).  The input is the fp32 residual
+stream; the output can be bf16, which is what the linear layers that follow consume under mixed precision
+(no separate cast kernels).  The backward forms dX, dweight and dbias in one pass over the rows.
+"""
+from __future__ import annotations
+
+import torch
+from torch import nn
+
+from . import _lib
+from ._lib import check, lib, ptr
+
+SUPPORTED_WIDTHS = (64, 128, 256, 512)
+
+
+class _LayerNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, bias, eps, out_bf16):
+        if not x.is_cuda or x.dtype != torch.float32:
+            raise _lib.SpionError("FusedLayerNorm needs an fp32 CUDA tensor")
+        N = x.shape[-1]
+        xc = x.contiguous()
+        M = xc.numel() // N
+        y = torch.empty(xc.shape, dtype=torch.bfloat16 if out_bf16 else torch.float32, device=x.device)
+        mean = torch.empty(M, dtype=torch.float32, device=x.device)
+        rstd = torch.empty(M, dtype=torch.float32, device=x.device)
+        w, b = weight.float().contiguous(), bias.float().contiguous()
+        check(lib.spion_layernorm_forward(ptr(xc), ptr(w), ptr(b), ptr(y), int(out_bf16), ptr(mean), ptr(rstd), M, N,
+                                          float(eps), _lib.current_stream_ptr()), "spion_layernorm_forward")
+        ctx.save_for_backward(xc, w, mean, rstd)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        xc, w, mean, rstd = ctx.saved_tensors
+        N = xc.shape[-1]
+        M = xc.numel() // N
+        if dy.dtype not in (torch.float32, torch.bfloat16):
+            dy = dy.float()
+        dy = dy.contiguous()
+        dx = torch.empty_like(xc)
+        dw = torch.empty(N, dtype=torch.float32, device=xc.device)
+        db = torch.empty(N, dtype=torch.float32, device=xc.device)
+        ws = torch.empty(int(lib.spion_layernorm_workspace_floats(N)), dtype=torch.float32, device=xc.device)
+        check(lib.spion_layernorm_backward(ptr(xc), ptr(dy), int(dy.dtype == torch.bfloat16), ptr(w), ptr(mean), ptr(rstd),
+                                           ptr(dx), ptr(dw), ptr(db), ptr(ws), M, N, _lib.current_stream_ptr()),
+              "spion_layernorm_backward")
+        return dx, dw, db, None, None
+
+
+class FusedLayerNorm(nn.Module):
+    """Drop-in for ``nn.LayerNorm(dim)`` on fp32 CUDA inputs with dim in SUPPORTED_WIDTHS.
+
+    ``bf16_out=True``: under ``torch.autocast`` the output is bf16 (the dtype the next linear layer casts its
+    input to anyway); outside autocast, or with ``bf16_out=False``, it is fp32."""
+
+    def __init__(self, dim: int, eps: float = 1e-5, bf16_out: bool = False):
+        super().__init__()
+        if dim not in SUPPORTED_WIDTHS:
+            raise ValueError(f"FusedLayerNorm: width {dim} not in {SUPPORTED_WIDTHS}")
+        self.weight = nn.Parameter(torch.ones(dim))
+        self.bias = nn.Parameter(torch.zeros(dim))
+        self.eps = eps
+        self.bf16_out = bf16_out
+
+    def forward(self, x):
+        out_bf16 = self.bf16_out and torch.is_autocast_enabled()
+        return _LayerNormFn.apply(x.float(), self.weight, self.bias, self.eps, out_bf16)

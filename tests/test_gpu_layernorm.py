@@ -1,0 +1,68 @@
+"""The library's layer normalisation (csrc/layernorm.cu) against torch.nn.functional.layer_norm in fp32
+(the operator the reference's encoder uses: models/model_transformer.py): outputs, input gradients and the
+weight / bias gradients, fp32 and bf16 outputs, every supported width, row counts that do not divide the grid."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("N", [64, 128, 256, 512])
+@pytest.mark.parametrize("M", [1, 37, 4096, 70001])
+def test_forward_backward_fp32(M, N):
+    from spion_b200.layernorm import FusedLayerNorm
+    g = torch.Generator().manual_seed(M + N)
+    x = (torch.randn(M, N, generator=g) * 3 + 0.5).cuda().requires_grad_(True)
+    dy = torch.randn(M, N, generator=g).cuda()
+    mod = FusedLayerNorm(N).cuda()
+    with torch.no_grad():
+        mod.weight.copy_(torch.randn(N, generator=g)); mod.bias.copy_(torch.randn(N, generator=g))
+    y = mod(x)
+    y.backward(dy)
+    xr = x.detach().clone().requires_grad_(True)
+    w = mod.weight.detach().clone().requires_grad_(True); b = mod.bias.detach().clone().requires_grad_(True)
+    yr = torch.nn.functional.layer_norm(xr, (N,), w, b, 1e-5)
+    yr.backward(dy)
+    assert float((y.detach() - yr.detach()).abs().max()) <= 2e-5
+    assert float((x.grad - xr.grad).abs().max()) <= 2e-5 * max(1.0, float(xr.grad.abs().max()))
+    # sums over M rows: tolerance relative to the magnitude of the sum
+    assert float((mod.weight.grad - w.grad).abs().max()) <= 1e-4 * max(1.0, float(w.grad.abs().max()))
+    assert float((mod.bias.grad - b.grad).abs().max()) <= 1e-4 * max(1.0, float(b.grad.abs().max()))
+
+
+def test_bf16_output_under_autocast_and_3d_input():
+    from spion_b200.layernorm import FusedLayerNorm
+    B, L, N = 3, 1000, 64
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(B, L, N, generator=g).cuda().requires_grad_(True)
+    mod = FusedLayerNorm(N, bf16_out=True).cuda()
+    lin = torch.nn.Linear(N, 32).cuda()
+    with torch.autocast(device_type="cuda", dtype=torch.bfloat16):
+        y = mod(x)
+        assert y.dtype == torch.bfloat16 and y.shape == x.shape
+        out = lin(y)
+    out.float().sum().backward()
+    xr = x.detach().clone().requires_grad_(True)
+    with torch.autocast(device_type="cuda", dtype=torch.bfloat16):
+        yr = torch.nn.functional.layer_norm(xr, (N,), mod.weight.detach(), mod.bias.detach(), 1e-5)
+        outr = lin(yr)
+    outr.float().sum().backward()
+    assert float((y.float() - yr.float()).abs().max()) <= 2e-2
+    assert float((x.grad - xr.grad).abs().max()) <= 2e-2 * float(xr.grad.abs().max())
+    assert mod(x.detach()).dtype == torch.float32           # outside autocast the output stays fp32
+
+
+def test_results_do_not_depend_on_the_run():
+    """The weight / bias gradients are sums in a fixed order: two runs give identical bits."""
+    from spion_b200.layernorm import FusedLayerNorm
+    g = torch.Generator().manual_seed(9)
+    x = torch.randn(50000, 64, generator=g).cuda()
+    dy = torch.randn(50000, 64, generator=g).cuda()
+    grads = []
+    for _ in range(2):
+        mod = FusedLayerNorm(64).cuda()
+        xx = x.clone().requires_grad_(True)
+        mod(xx).backward(dy)
+        grads.append((mod.weight.grad.clone(), mod.bias.grad.clone(), xx.grad.clone()))
+    for a, b in zip(*grads):
+        assert torch.equal(a, b)
