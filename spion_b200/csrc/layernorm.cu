@@ -138,21 +138,33 @@ __global__ void __launch_bounds__(LN_WARPS * 32) ln_bwd_kernel(const float* __re
   }
 }
 
-// dgamma[c] = sum over the partial rows, in row order; likewise dbeta.  One thread per column.
-__global__ void ln_bwd_reduce_kernel(const float* __restrict__ partial, int rows, int N, float* __restrict__ dgamma,
-                                     float* __restrict__ dbeta) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= 2 * N) return;
+// dgamma[c] = sum over the partial rows; likewise dbeta.  One CTA of 32 warps per 32 columns: warp w adds the
+// rows w, w + 32, ... of its columns (coalesced), then the 32 per-warp sums are added in warp order: the order
+// of the additions is fixed, so the result does not depend on the run.
+__global__ void __launch_bounds__(1024) ln_bwd_reduce_kernel(const float* __restrict__ partial, int rows, int N,
+                                                              float* __restrict__ dgamma, float* __restrict__ dbeta) {
+  __shared__ float s_p[32][33];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + lane;                      // column of the [rows, 2 N] partial matrix
   float s = 0.f;
-  for (int r = 0; r < rows; ++r) s += partial[(size_t)r * 2 * N + c];
-  if (c < N) dgamma[c] = s; else dbeta[c - N] = s;
+  for (int r = warp; r < rows; r += 32) s += partial[(size_t)r * 2 * N + c];
+  s_p[warp][lane] = s;
+  __syncthreads();
+  if (warp == 0) {
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < 32; ++w) t += s_p[w][lane];
+    if (c < N) dgamma[c] = t; else dbeta[c - N] = t;
+  }
 }
 
 int ln_grid(long long M) {
   int dev = 0, sms = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
     return -1;
-  long long want = (M + LN_WARPS - 1) / LN_WARPS, cap = (long long)sms * 8;   // 8 CTAs of 8 warps per SM: all warp slots
+  // at least eight rows per warp (fewer CTAs mean fewer partial rows of the weight / bias gradients to add up);
+  // at most 8 CTAs of 8 warps per SM: all warp slots
+  long long want = (M + LN_WARPS * 8 - 1) / (LN_WARPS * 8), cap = (long long)sms * 8;
   if (cap > LN_MAX_CTAS) cap = LN_MAX_CTAS;
   return (int)(want < cap ? want : cap);
 }
@@ -203,7 +215,7 @@ extern "C" int spion_layernorm_backward(const float* x, const void* dy, int dy_i
   }
 #undef SPION_LN_BWD
   SPION_LAUNCH_CHECK();
-  ln_bwd_reduce_kernel<<<(2 * N + 127) / 128, 128, 0, stream>>>(workspace, grid, N, dgamma, dbeta);
+  ln_bwd_reduce_kernel<<<2 * N / 32, 1024, 0, stream>>>(workspace, grid, N, dgamma, dbeta);
   SPION_LAUNCH_CHECK();
   return SPION_OK;
 }

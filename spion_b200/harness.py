@@ -111,6 +111,7 @@ class Classifier(nn.Module):
         super().__init__()
         self.config = config
         self.dual = bool(config.get("dual", False))
+        self.batch_towers = bool(config.get("batch_towers", True)) and bool(config.get("native"))
         self.amp = bool(config.get("mixed_precision", False))
         self.model = Encoder(config)
         dim, hid = config["transformer_dim"], config["transformer_hidden_dim"]
@@ -119,7 +120,16 @@ class Classifier(nn.Module):
 
     def forward(self, ids, label, mat_lst=None, is_attn=False):
         with torch.autocast(device_type="cuda", dtype=torch.bfloat16, enabled=self.amp):
-            if self.dual:
+            if self.dual and mat_lst is not None and self.batch_towers:
+                # sparse phase: both sequences of a pair go through the shared encoder as one batch of 2 B
+                # (the reference calls the encoder twice, models/model_LRA.py; same weights, same arithmetic
+                # per sequence, half the kernel launches and no second accumulation of the weight gradients)
+                both = torch.cat([ids[0], ids[1]], 0)
+                t, maps = self.model(both, (both != 0).float(), mat_lst, False)
+                nb = ids[0].shape[0]
+                x0, x1 = t[:nb].mean(1), t[nb:].mean(1)
+                scores = self.head(torch.cat([x0, x1, x0 * x1, x0 - x1], dim=-1))
+            elif self.dual:
                 m0, m1 = (ids[0] != 0).float(), (ids[1] != 0).float()        # models/dataset_LRA.py:34
                 t0, maps = self.model(ids[0], m0, mat_lst, is_attn)
                 t1, _ = self.model(ids[1], m1, mat_lst, False)
@@ -244,6 +254,8 @@ class Trainer:
         masks = dp.agree_on_masks(maps, disc)
         mats = torch.stack([m.to(torch.float32) for m in masks], 0)
         self.mat_lst = torch.stack([mats, mats, mats, mats], 0)          # main_conv_ff.py:298-299
+        if self.model.dual and self.model.batch_towers:
+            cfg["batch_size"] = 2 * cfg["batch_size"]                   # the sparse layers see both towers at once
         for layer in self.model.model.layers:
             layer.mha.reconstruct_for_blocksparse(cfg)
         return self.mat_lst

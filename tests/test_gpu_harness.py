@@ -18,9 +18,10 @@ def _cfg(task, batch, L, native, dtype):
     return cfg
 
 
-def _run(task, native, dtype, L=256, batch=4, steps=2):
+def _run(task, native, dtype, L=256, batch=4, steps=2, **overrides):
     from spion_b200 import harness
     cfg = _cfg(task, batch, L, native, dtype)
+    cfg.update(overrides)
     tr = harness.Trainer(cfg, lr=1e-3, seed=3)
     dual = cfg["dual"]
     ids = synthetic.token_ids(5, batch, L).cuda()
@@ -59,5 +60,17 @@ def test_text_shape_bf16_native_with_key_padding():
 
 
 def test_retrieval_dual_tower_bf16():
+    """Sparse steps with both towers as one batch of 2 B (the default of the native path) against one encoder
+    call per tower (what the reference does, models/model_LRA.py): same masks, same losses to bf16 rounding."""
     a, m = _run("retrieval", native=True, dtype="bf16", L=512, batch=2)
     assert m.shape[1] == 2
+    b, mb = _run("retrieval", native=True, dtype="bf16", L=512, batch=2, batch_towers=False)
+    assert torch.equal(m, mb)
+    np.testing.assert_allclose(a, b, rtol=3e-2, atol=3e-2)
+
+
+def test_fused_layernorm_agrees_with_the_framework_operator():
+    a, m = _run("text", native=True, dtype="fp32", L=256, batch=2)
+    b, mb = _run("text", native=True, dtype="fp32", L=256, batch=2, fused_layernorm=False)
+    assert torch.equal(m, mb)
+    np.testing.assert_allclose(a, b, rtol=2e-4, atol=2e-4)
