@@ -396,6 +396,9 @@ REFCUDA_WORKLOADS = {
     # name: (B, H, L, d, bs, density) -- fp32, the reference's own layouts
     "refcuda_config1_L1024": (8, 2, 1024, 32, 32, 0.15),
     "refcuda_L4096_bs64_d05": (4, 2, 4096, 64, 64, 0.05),
+    # dense warm-up path (models/attn.cu: cuBLAS tensor-op GEMMs + its softmax kernels); block = 0 marks it
+    "refcuda_dense_L1024": (8, 2, 1024, 32, 0, 1.0),
+    "refcuda_dense_L4096": (2, 2, 4096, 64, 0, 1.0),
 }
 
 
@@ -412,6 +415,8 @@ def run_refcuda(args, rank, local_rank):
     from spion_b200.attention import Attention
     from spion_b200.pattern import pattern_from_mask
     B, H, L, d, bs, dens = REFCUDA_WORKLOADS[args.workload]
+    if bs == 0:
+        return run_refcuda_dense(args, local_rank, B, H, L, d)
     line = {"metric": "sparse-attn fwd+bwd Mtokens/s at L=%d (reference entry points, fp32)" % L, "unit": "Mtokens/s",
             "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
@@ -478,6 +483,79 @@ def run_refcuda(args, rank, local_rank):
                  "max_abs_difference_of_outputs_and_gradients": diff})
     line["config"]["density"] = float(mat.mean())
     line["config"]["l2_policy"] = "working set %.0f MB" % ((4 * Q.numel() * 4 + 3 * attn.numel() * 4) / 1e6)
+    print(json.dumps(line))
+
+
+def run_refcuda_dense(args, local_rank, B, H, L, d):
+    """The dense warm-up path behind the reference's entry points (models/attn.cu:265-280, called as
+    models/attention_cuda.py:17-74 does): the reference's file compiled unchanged (cuBLAS strided-batched GEMMs
+    with fp16 tensor-op compute, its row softmax kernels) against this library's shim, same buffers."""
+    import ctypes
+    from spion_b200 import synthetic
+    from spion_b200.attention import Attention
+    line = {"metric": "dense-attn fwd+bwd Mtokens/s at L=%d (reference entry points, fp32 storage)" % L, "unit": "Mtokens/s",
+            "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": args.workload, "B": B, "H": H, "L": L, "d_head": d, "block": None, "density": 1.0}}
+    ref_path = os.path.join(ROOT, "oracle", "_ref", "attn.so")
+    if not os.path.exists(ref_path):
+        line.update({"value": None, "reference_cuda": {"unavailable": "oracle/_ref/attn.so was not built "
+                                                                       "(needs the reference checkout at build time)"}})
+        print(json.dumps(line))
+        return
+    dev = torch.device("cuda", local_rank)
+    BH = B * H
+    P = ctypes.c_void_p
+    ref = ctypes.CDLL(ref_path)
+    ref.init.argtypes = [ctypes.c_int] * 3
+    ref.init.restype = P
+    ref.attn_forward.argtypes = [P] * 6
+    ref.attn_backward.argtypes = [P] * 12
+    ref.attn_forward.restype = None
+    ref.attn_backward.restype = None
+    mine = Attention._cuda_compile_module()
+    Q, K, V, dO = [t.to(dev).contiguous() for t in synthetic.qkv(3, B, H, L, d)]
+    Qt = Q.permute(0, 1, 3, 2).contiguous(); Kt = K.permute(0, 1, 3, 2).contiguous(); Vt = V.permute(0, 1, 3, 2).contiguous()
+    dOt = dO.permute(0, 1, 3, 2).contiguous()
+    f32 = dict(dtype=torch.float32, device=dev)
+    attn = torch.empty(BH * L * L, **f32); out = torch.empty(BH * L * d, **f32)
+    s1 = torch.zeros(BH * L * L, **f32); s2 = torch.empty(BH * L * L, **f32); s3 = torch.empty(BH * L * L, **f32)
+    dQ, dK, dV = [torch.empty(BH * L * d, **f32) for _ in range(3)]
+    p = lambda t: P(t.data_ptr())
+
+    def step(lib, handle):
+        lib.attn_forward(handle, p(Qt), p(K), p(Vt), p(attn), p(out))
+        s1.zero_()                                            # the reference's caller zero-fills it on every backward
+        lib.attn_backward(handle, p(Qt), p(Kt), p(V), p(attn), p(dOt), p(s1), p(s2), p(s3), p(dQ), p(dK), p(dV))
+
+    res, outs = {}, {}
+    for name, lib in (("reference_cuda", ref), ("spion_b200", mine)):
+        h = lib.init(d, L, BH)
+        for _ in range(args.warmup):
+            step(lib, h)
+        torch.cuda.synchronize()
+        reps = []
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for _ in range(args.repeats):
+            e0.record()
+            for _ in range(args.steps):
+                step(lib, h)
+            e1.record()
+            torch.cuda.synchronize()
+            reps.append(e0.elapsed_time(e1) / args.steps)
+        ms = statistics.median(reps)
+        res[name] = {"ms_per_step": ms, "min_ms": min(reps), "max_ms": max(reps), "Mtokens_per_s": B * L / (ms * 1e-3) / 1e6}
+        outs[name] = [t.clone() for t in (out, dQ, dK, dV)]
+        if lib is mine:
+            lib.destroy(h)
+    diff = max(float((a - b).abs().max()) for a, b in zip(outs["reference_cuda"], outs["spion_b200"]))
+    line.update({"value": res["spion_b200"]["Mtokens_per_s"], "ms_per_step": res["spion_b200"]["ms_per_step"],
+                 "reference_cuda": res["reference_cuda"], "spion_b200": res["spion_b200"],
+                 "speedup_over_reference_cuda": res["reference_cuda"]["ms_per_step"] / res["spion_b200"]["ms_per_step"],
+                 "max_abs_difference_of_outputs_and_gradients": diff,
+                 "note": "the reference multiplies with fp16 tensor-op compute (CUBLAS_COMPUTE_32F_FAST_16F), this library's "
+                         "dense entry points in fp32 on the FMA pipes: the difference of the results is the reference's rounding"})
+    line["config"]["l2_policy"] = "working set %.0f MB" % ((4 * Q.numel() * 4 + 4 * attn.numel() * 4) / 1e6)
     print(json.dumps(line))
 
 
