@@ -60,8 +60,10 @@ class Embeddings(nn.Module):
         self.drop = nn.Dropout(config["dropout_prob"])
 
     def forward(self, ids):
-        pos = torch.arange(ids.shape[1], device=ids.device)
-        return self.drop(self.tok(ids) + self.pos(pos)[None])
+        # positions 0 .. L-1 are a slice of the table: the same values as the lookup self.pos(arange(L)) of the
+        # reference (models/model_transformer.py), with a plain sum over the batch as backward instead of the
+        # sort-based embedding backward
+        return self.drop(self.tok(ids) + self.pos.weight[:ids.shape[1]][None])
 
 
 class TransformerLayer(nn.Module):
