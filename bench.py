@@ -238,6 +238,9 @@ def run_training(args, rank, world, local_rank):
     dev = torch.device("cuda", local_rank)
     per_rank = batch // world if scaling == "strong" else batch
     cfg = harness.task_config(task, per_rank, native=True, dtype=dt)
+    for kv in args.harness:                                   # e.g. --harness fused_bias_grad=1 batch_towers=0
+        k, v = kv.split("=", 1)
+        cfg[k] = bool(int(v))
     if args.workload == "train_tiny":
         cfg["max_seq_len"] = 512
     cfg["threshold"] = thr
@@ -645,6 +648,8 @@ def main():
                     help="32-wide masks on the tensor-core engine: kernels on the mask's own blocks, on 64-wide super-blocks, or chosen per mask")
     ap.add_argument("--repeats", type=int, default=5, help="how often the timed loop of --steps steps is repeated")
     ap.add_argument("--no-graph", action="store_true", help="training workloads: launch the step eagerly")
+    ap.add_argument("--harness", nargs="*", default=[], metavar="KEY=0|1",
+                    help="training workloads: switches of the harness (fused_layernorm, fused_bias_grad, batch_towers)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-clocks", action="store_true", help="do not sample nvidia-smi (profiler runs)")
     args = ap.parse_args()

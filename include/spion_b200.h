@@ -325,6 +325,12 @@ int spion_layernorm_backward(const float* x, const void* dy, int dy_is_bf16, con
                              const float* rstd, float* dx, float* dgamma, float* dbeta, float* workspace,
                              long long M, int N, void* cuda_stream);
 
+/* Sum of the rows of an [M, N] matrix (fp32, or bf16 with dy_is_bf16 != 0), N in {64, 128, 256, 512}: out [N] fp32.
+ * The bias gradient of a linear layer (torch.nn.Linear in the reference's encoder) as one streaming pass plus a
+ * fixed-order reduction.  workspace: spion_layernorm_workspace_floats(N) floats. */
+int spion_column_sums(const void* dy, int dy_is_bf16, float* out, float* workspace, long long M, int N,
+                      void* cuda_stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -35,6 +35,7 @@ SIGNATURES = {
     "spion_layernorm_forward": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_longlong, c_int,
                                 ctypes.c_float, c_void_p]),
     "spion_layernorm_workspace_floats": (c_longlong, [c_int]),
+    "spion_column_sums": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_longlong, c_int, c_void_p]),
     "spion_layernorm_backward": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                  c_void_p, c_longlong, c_int, c_void_p]),
     "spion_csr_arrays_are_stable": (c_int, [c_void_p, c_int]),

@@ -56,9 +56,14 @@ class Attention(nn.Module):
         self.native_dtype = torch.bfloat16 if config.get("dtype", "fp32") == "bf16" else torch.float32
         self.with_keypad = config["task"] in mask_task
 
-        self.W_q = nn.Linear(self.dim, self.num_head * self.head_dim)
-        self.W_k = nn.Linear(self.dim, self.num_head * self.head_dim)
-        self.W_v = nn.Linear(self.dim, self.num_head * self.head_dim)
+        # same parameters and forward arithmetic as nn.Linear (models/attention.py:55-57); on the native path the
+        # bias gradient of the backward is summed by the library's column-sum kernel
+        Linear = nn.Linear
+        if config.get("native") and config.get("fused_bias_grad", True):
+            from .layernorm import BiasGradLinear as Linear
+        self.W_q = Linear(self.dim, self.num_head * self.head_dim)
+        self.W_k = Linear(self.dim, self.num_head * self.head_dim)
+        self.W_v = Linear(self.dim, self.num_head * self.head_dim)
 
         if not inference and self.native:
             from .native import DenseViaBlocks
@@ -76,7 +81,7 @@ class Attention(nn.Module):
                 raise _lib.SpionError("init() of the dense attention library returned NULL")
             self.attn = Dense(config, attn_cpp, attn_handle)
 
-        self.ff = nn.Linear(self.num_head * self.head_dim, self.dim)
+        self.ff = Linear(self.num_head * self.head_dim, self.dim)
 
     def forward(self, X, mask, mat=None):
         Q = self.split_heads(self.W_q(X))

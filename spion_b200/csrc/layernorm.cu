@@ -158,6 +158,54 @@ __global__ void __launch_bounds__(1024) ln_bwd_reduce_kernel(const float* __rest
   }
 }
 
+// Column sums of an [M, N] matrix (the bias gradient of a linear layer: sum of dY over all rows), first stage:
+// one partial row per CTA, same lane / column mapping and the same fixed-order second stage as above.
+template <int K, bool BF16>
+__global__ void __launch_bounds__(LN_WARPS * 32) colsum_kernel(const void* __restrict__ dy, float* __restrict__ partial,
+                                                                long long M) {
+  constexpr int N = 64 * K;
+  __shared__ float s_b[LN_WARPS][N];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const long long warp0 = (long long)blockIdx.x * LN_WARPS + warp, nwarps = (long long)gridDim.x * LN_WARPS;
+  float2 ab[K];
+#pragma unroll
+  for (int k = 0; k < K; ++k) ab[k] = make_float2(0.f, 0.f);
+  for (long long r = warp0; r < M; r += nwarps) {
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const float2 d = load2<BF16>(dy, (size_t)r * N + 64 * k + 2 * lane);
+      ab[k].x += d.x; ab[k].y += d.y;
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < K; ++k) *reinterpret_cast<float2*>(&s_b[warp][64 * k + 2 * lane]) = ab[k];
+  __syncthreads();
+  for (int c = threadIdx.x; c < N; c += blockDim.x) {
+    float sb = 0.f;
+#pragma unroll
+    for (int w = 0; w < LN_WARPS; ++w) sb += s_b[w][c];
+    partial[(size_t)blockIdx.x * N + c] = sb;
+  }
+}
+
+// out[c] = sum over the partial rows of an [rows, N] matrix, fixed order (see ln_bwd_reduce_kernel)
+__global__ void __launch_bounds__(1024) colsum_reduce_kernel(const float* __restrict__ partial, int rows, int N,
+                                                              float* __restrict__ out) {
+  __shared__ float s_p[32][33];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + lane;
+  float s = 0.f;
+  for (int r = warp; r < rows; r += 32) s += partial[(size_t)r * N + c];
+  s_p[warp][lane] = s;
+  __syncthreads();
+  if (warp == 0) {
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < 32; ++w) t += s_p[w][lane];
+    out[c] = t;
+  }
+}
+
 int ln_grid(long long M) {
   int dev = 0, sms = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
@@ -216,6 +264,31 @@ extern "C" int spion_layernorm_backward(const float* x, const void* dy, int dy_i
 #undef SPION_LN_BWD
   SPION_LAUNCH_CHECK();
   ln_bwd_reduce_kernel<<<2 * N / 32, 1024, 0, stream>>>(workspace, grid, N, dgamma, dbeta);
+  SPION_LAUNCH_CHECK();
+  return SPION_OK;
+}
+
+// Sum of the rows of an [M, N] matrix (fp32 or bf16), N in {64, 128, 256, 512}: out[N] fp32.  The bias gradient of a
+// linear layer.  workspace: spion_layernorm_workspace_floats(N) floats.  Fixed summation order.
+extern "C" int spion_column_sums(const void* dy, int dy_is_bf16, float* out, float* workspace, long long M, int N,
+                                 void* cuda_stream) {
+  cudaStream_t stream = (cudaStream_t)cuda_stream;
+  if (!dy || !out || !workspace || M < 1) return SPION_ERR_ARG;
+  const int grid = ln_grid(M);
+  if (grid < 1) return SPION_ERR_CUDA;
+#define SPION_COLSUM(K)                                                                                   \
+  if (dy_is_bf16) colsum_kernel<K, true><<<grid, LN_WARPS * 32, 0, stream>>>(dy, workspace, M);            \
+  else colsum_kernel<K, false><<<grid, LN_WARPS * 32, 0, stream>>>(dy, workspace, M);
+  switch (N) {
+    case 64: SPION_COLSUM(1) break;
+    case 128: SPION_COLSUM(2) break;
+    case 256: SPION_COLSUM(4) break;
+    case 512: SPION_COLSUM(8) break;
+    default: return SPION_ERR_SHAPE;
+  }
+#undef SPION_COLSUM
+  SPION_LAUNCH_CHECK();
+  colsum_reduce_kernel<<<N / 32, 1024, 0, stream>>>(workspace, grid, N, out);
   SPION_LAUNCH_CHECK();
   return SPION_OK;
 }

@@ -74,7 +74,10 @@ class TransformerLayer(nn.Module):
         self.mha = Attention(config)
         self.dropout1 = nn.Dropout(p)
         self.norm2 = make_norm(config, True)
-        self.mlpblock = nn.Sequential(nn.Linear(dim, hid), nn.GELU(), nn.Dropout(p), nn.Linear(hid, dim), nn.Dropout(p))
+        Linear = nn.Linear
+        if config.get("native") and config.get("fused_bias_grad", True):
+            from .layernorm import BiasGradLinear as Linear
+        self.mlpblock = nn.Sequential(Linear(dim, hid), nn.GELU(), nn.Dropout(p), Linear(hid, dim), nn.Dropout(p))
 
     def forward(self, X, mask, mat=None):
         out, attn = self.mha(self.norm1(X), mask, mat)

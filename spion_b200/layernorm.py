@@ -69,3 +69,48 @@ class FusedLayerNorm(nn.Module):
     def forward(self, x):
         out_bf16 = self.bf16_out and torch.is_autocast_enabled()
         return _LayerNormFn.apply(x.float(), self.weight, self.bias, self.eps, out_bf16)
+
+
+class _LinearFn(torch.autograd.Function):
+    """y = x W^T + b with the framework's GEMMs; the bias gradient (a column sum over all rows, which the
+    framework computes with a slow reduction for bf16 inputs) through spion_column_sums."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias):
+        cd = torch.get_autocast_dtype("cuda") if torch.is_autocast_enabled() else x.dtype
+        xb, wb, bb = x.to(cd), weight.to(cd), bias.to(cd)
+        with torch.autocast(device_type="cuda", enabled=False):
+            y = torch.nn.functional.linear(xb, wb, bb)
+        ctx.save_for_backward(xb, wb)
+        ctx.in_dtypes = (x.dtype, weight.dtype, bias.dtype)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        xb, wb = ctx.saved_tensors
+        xd, wd, bd = ctx.in_dtypes
+        N, K = wb.shape
+        dy2 = dy.reshape(-1, N).contiguous()
+        x2 = xb.reshape(-1, K)
+        dx = (dy2 @ wb).reshape(xb.shape).to(xd)
+        dw = (dy2.t() @ x2).to(wd)
+        M = dy2.shape[0]
+        if N in SUPPORTED_WIDTHS and dy2.dtype in (torch.float32, torch.bfloat16):
+            db = torch.empty(N, dtype=torch.float32, device=dy2.device)
+            ws = torch.empty(int(lib.spion_layernorm_workspace_floats(N)), dtype=torch.float32, device=dy2.device)
+            check(lib.spion_column_sums(ptr(dy2), int(dy2.dtype == torch.bfloat16), ptr(db), ptr(ws), M, N,
+                                        _lib.current_stream_ptr()), "spion_column_sums")
+            db = db.to(bd)
+        else:
+            db = dy2.sum(0).to(bd)
+        return dx, dw, db
+
+
+class BiasGradLinear(nn.Linear):
+    """``nn.Linear`` (same parameters, same forward arithmetic) whose backward sums the bias gradient with the
+    library's column-sum kernel when the output width is one it serves."""
+
+    def forward(self, x):
+        if self.bias is None or not x.is_cuda:
+            return super().forward(x)
+        return _LinearFn.apply(x, self.weight, self.bias)

@@ -66,3 +66,29 @@ def test_results_do_not_depend_on_the_run():
         grads.append((mod.weight.grad.clone(), mod.bias.grad.clone(), xx.grad.clone()))
     for a, b in zip(*grads):
         assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("N", [64, 128, 512])
+def test_linear_with_column_sum_bias_gradient(N, dtype):
+    """BiasGradLinear against nn.Linear with the same parameters: output, dX, dW and the bias gradient (the only
+    part that runs on the library's kernel), in fp32 and under bf16 autocast."""
+    from spion_b200.layernorm import BiasGradLinear
+    g = torch.Generator().manual_seed(N)
+    B, L, K = 3, 1111, 64
+    x = torch.randn(B, L, K, generator=g).cuda()
+    dy = torch.randn(B, L, N, generator=g).cuda()
+    ref = torch.nn.Linear(K, N).cuda()
+    mine = BiasGradLinear(K, N).cuda()
+    mine.load_state_dict(ref.state_dict())
+    outs = []
+    for mod in (ref, mine):
+        xx = x.clone().requires_grad_(True)
+        with torch.autocast(device_type="cuda", dtype=torch.bfloat16, enabled=dtype == torch.bfloat16):
+            y = mod(xx)
+        y.backward(dy.to(y.dtype))
+        outs.append((y.detach().float(), xx.grad, mod.weight.grad, mod.bias.grad))
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    for name, a, b in zip(("y", "dx", "dW", "db"), *outs):
+        scale = max(1.0, float(a.abs().max()))
+        assert float((a - b).abs().max()) <= tol * scale, name
