@@ -235,7 +235,8 @@ k_b32(const __grid_constant__ CUtensorMap tmG0, const __grid_constant__ CUtensor
   tc_fence_after();
   const uint32_t tmem = s_slot;
 
-  // bounded wait of one thread; a failure is recorded in the status word
+  // bounded wait of one thread; a failure is recorded in the status word: the low three bits say what kind of wait
+  // gave up (as in the other tensor-core kernels), bits 4-20 which one of this kernel's waits, bits 24-26 which kernel
   auto wait1 = [&](uint32_t b, uint32_t parity, int code) -> bool {
     if (mbar_wait(b, parity)) return true;
     report(status, code | (0x1000000 << MODE));

@@ -28,8 +28,9 @@ class _LayerNormFn(torch.autograd.Function):
         mean = torch.empty(M, dtype=torch.float32, device=x.device)
         rstd = torch.empty(M, dtype=torch.float32, device=x.device)
         w, b = weight.float().contiguous(), bias.float().contiguous()
-        check(lib.spion_layernorm_forward(ptr(xc), ptr(w), ptr(b), ptr(y), int(out_bf16), ptr(mean), ptr(rstd), M, N,
-                                          float(eps), _lib.current_stream_ptr()), "spion_layernorm_forward")
+        with torch.cuda.device(x.device):                     # the kernels are launched on the current device
+            check(lib.spion_layernorm_forward(ptr(xc), ptr(w), ptr(b), ptr(y), int(out_bf16), ptr(mean), ptr(rstd), M, N,
+                                              float(eps), _lib.current_stream_ptr()), "spion_layernorm_forward")
         ctx.save_for_backward(xc, w, mean, rstd)
         return y
 
@@ -45,9 +46,10 @@ class _LayerNormFn(torch.autograd.Function):
         dw = torch.empty(N, dtype=torch.float32, device=xc.device)
         db = torch.empty(N, dtype=torch.float32, device=xc.device)
         ws = torch.empty(int(lib.spion_layernorm_workspace_floats(N)), dtype=torch.float32, device=xc.device)
-        check(lib.spion_layernorm_backward(ptr(xc), ptr(dy), int(dy.dtype == torch.bfloat16), ptr(w), ptr(mean), ptr(rstd),
-                                           ptr(dx), ptr(dw), ptr(db), ptr(ws), M, N, _lib.current_stream_ptr()),
-              "spion_layernorm_backward")
+        with torch.cuda.device(xc.device):
+            check(lib.spion_layernorm_backward(ptr(xc), ptr(dy), int(dy.dtype == torch.bfloat16), ptr(w), ptr(mean),
+                                               ptr(rstd), ptr(dx), ptr(dw), ptr(db), ptr(ws), M, N,
+                                               _lib.current_stream_ptr()), "spion_layernorm_backward")
         return dx, dw, db, None, None
 
 
@@ -98,8 +100,9 @@ class _LinearFn(torch.autograd.Function):
         if N in SUPPORTED_WIDTHS and dy2.dtype in (torch.float32, torch.bfloat16):
             db = torch.empty(N, dtype=torch.float32, device=dy2.device)
             ws = torch.empty(int(lib.spion_layernorm_workspace_floats(N)), dtype=torch.float32, device=dy2.device)
-            check(lib.spion_column_sums(ptr(dy2), int(dy2.dtype == torch.bfloat16), ptr(db), ptr(ws), M, N,
-                                        _lib.current_stream_ptr()), "spion_column_sums")
+            with torch.cuda.device(dy2.device):
+                check(lib.spion_column_sums(ptr(dy2), int(dy2.dtype == torch.bfloat16), ptr(db), ptr(ws), M, N,
+                                            _lib.current_stream_ptr()), "spion_column_sums")
             db = db.to(bd)
         else:
             db = dy2.sum(0).to(bd)
