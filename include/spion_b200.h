@@ -94,6 +94,9 @@ int spion_set_head_layout(spion_ctx* ctx, int heads);
  *      average (masks with three or more blocks per block row), else 2.
  * Takes effect when the next pattern is set.  No counterpart in the reference. */
 int spion_set_block32_path(spion_ctx* ctx, int path);
+/* Which of the two serves the current pattern: 1 or 2; 0 when the context is not a 32-wide mask on the tcgen05
+ * engine (or no pattern is set). */
+int spion_block32_path_in_use(const spion_ctx* ctx);
 
 /* Failure-path self-test that faults nothing: launches one CTA that waits, with the given limit
  * in clock cycles (at most 2e9), on a barrier nobody arrives on.  The kernel gives up, records the

@@ -32,6 +32,7 @@ SIGNATURES = {
     "spion_check_device_status": (c_int, [c_void_p]),
     "spion_set_head_layout": (c_int, [c_void_p, c_int]),
     "spion_set_block32_path": (c_int, [c_void_p, c_int]),
+    "spion_block32_path_in_use": (c_int, [c_void_p]),
     "spion_layernorm_forward": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_longlong, c_int,
                                 ctypes.c_float, c_void_p]),
     "spion_layernorm_workspace_floats": (c_longlong, [c_int]),

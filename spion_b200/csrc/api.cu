@@ -518,6 +518,11 @@ extern "C" int spion_attn_backward_fused(spion_ctx* c, const void* Q, const void
   return tc_engine_backward_fused(c, Q, K, V, O, dO, lse, keypad, dQ, dK, dV);
 }
 
+extern "C" int spion_block32_path_in_use(const spion_ctx* c) {
+  if (!c) return SPION_ERR_ARG;
+  return use_tc(c) ? tc_engine_block32_path(c) : 0;
+}
+
 extern "C" int spion_mean_map_recompute(spion_ctx* c, const void* Q, const void* K, const float* lse,
                                         const float* keypad, float* A) {
   if (!c || !Q || !K || !lse || !A) return SPION_ERR_ARG;

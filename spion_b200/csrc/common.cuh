@@ -174,3 +174,4 @@ int tc_engine_backward_fused(spion_ctx* c, const void* Q, const void* K, const v
                              const float* lse, const float* keypad, void* dQ, void* dK, void* dV);
 int tc_engine_mean_map(spion_ctx* c, const void* Q, const void* K, const float* lse, const float* keypad, float* A);
 int tc_engine_wait_selftest(spion_ctx* c, long long limit_cycles);
+int tc_engine_block32_path(const spion_ctx* c);   // 1 own blocks, 2 super-blocks, 0: not a 32-wide mask on this engine

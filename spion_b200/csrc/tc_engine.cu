@@ -878,6 +878,12 @@ int tc_engine_mean_map(spion_ctx* c, const void* Q, const void* K, const float* 
   return recompute_mean_map(c, (TcState*)c->tc, Q, K, lse, keypad, A);
 }
 
+int tc_engine_block32_path(const spion_ctx* c) {
+  const TcState* s = (const TcState*)c->tc;
+  if (!s || !s->super) return 0;
+  return (s->b32 && s->b32_use) ? 1 : 2;
+}
+
 int tc_engine_wait_selftest(spion_ctx* c, long long limit_cycles) {
   k_wait_selftest<<<1, 128, 0, c->stream>>>(c->status_dev, limit_cycles);
   SPION_LAUNCH_CHECK();

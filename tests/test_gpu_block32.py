@@ -122,6 +122,11 @@ def test_path_chosen_per_mask(dens, own):
     mat = synthetic.band_random_mask(2056, L // 32, dens)
     fill = mat.sum() / np.ceil(mat.sum(1) / 4).sum()
     assert (fill >= 2.8) == own, fill
+    from spion_b200 import _lib
+    from spion_b200.native import BlockSparseAttention
+    probe = BlockSparseAttention(cfg(B, H, L, 64, 32), dtype=torch.bfloat16, engine=_lib.ENGINE_TCGEN05)
+    probe.set_mask(torch.as_tensor(mat).cuda())
+    assert _lib.lib.spion_block32_path_in_use(probe.handle) == (1 if own else 2)
     (Q, K, V, dO), got = run(B, H, L, mat, seed=17, path="auto")
     O, _, gQ, gK, gV = oatt.sparse_attention(Q.float(), K.float(), V.float(), mat, 32, None, dO.float())
     for name, a, b in zip(("O", "dQ", "dK", "dV"), got, (O, gQ, gK, gV)):
