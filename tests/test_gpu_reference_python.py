@@ -4,8 +4,8 @@ those modules hand to the C entry points: ``Columns`` repeated once per (b,h) ma
 0-dim CUDA tensor that ctypes converts, a zero-filled dP scratch, flattened / permuted copies of the
 operands (models/attention_blockcuda.py:26-63, :72-106; models/attention_cuda.py:17-74).
 
-The checkout is looked for under $SPION_REFERENCE_ROOT; the first test is skipped where the variable is not
-set or the checkout does not exist.
+The checkout is looked for under $SPION_REFERENCE_ROOT (default ~/reference); the first test is skipped where
+it does not exist.
 """
 import ctypes
 import importlib.util
@@ -20,7 +20,7 @@ from oracle import attention as oatt
 from spion_b200 import synthetic
 
 pytestmark = pytest.mark.gpu
-REF_ROOT = os.environ.get("SPION_REFERENCE_ROOT", "")
+REF_ROOT = os.environ.get("SPION_REFERENCE_ROOT", os.path.join(os.path.expanduser("~"), "reference"))
 TOL = 1e-4
 
 
