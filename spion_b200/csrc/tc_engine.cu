@@ -659,6 +659,8 @@ int convert_tiles(spion_ctx* c, TcState* s, bool to64, void* v64, void* v32) {
   return SPION_OK;
 }
 
+int ensure_super_ws(spion_ctx* c, TcState* s);
+
 template <int D>
 int run_backward(spion_ctx* c, TcState* s, const void* Q, const void* K, const void* V, const void* P_user,
                  const void* O, const void* dO, void* dS_user, void* dQ, void* dK, void* dV) {
@@ -667,6 +669,7 @@ int run_backward(spion_ctx* c, TcState* s, const void* Q, const void* K, const v
   void* dS = dS_user;
   int rc;
   if (s->super) {                    // bring the caller's 32-wide tiles into super-tile form
+    if ((rc = ensure_super_ws(c, s))) return rc;
     if ((rc = convert_tiles(c, s, true, s->p64_ws, const_cast<void*>(P_user)))) return rc;
     P = s->p64_ws;
     dS = s->ds64_ws;
@@ -705,6 +708,19 @@ void free_super(TcState* s) {
   s->ws_elems = 0;
 }
 
+// [BH, nnzb64, 64, 64] bf16 workspaces for P and dS in super-tile form
+int ensure_super_ws(spion_ctx* c, TcState* s) {
+  const size_t need = (size_t)c->BH * s->nnzb64 * 4096;
+  if (need <= s->ws_elems) return SPION_OK;
+  cudaFree(s->p64_ws); cudaFree(s->ds64_ws);
+  s->p64_ws = s->ds64_ws = nullptr;
+  s->ws_elems = 0;
+  if (cudaMalloc(&s->p64_ws, need * 2) != cudaSuccess || cudaMalloc(&s->ds64_ws, need * 2) != cudaSuccess)
+    return SPION_ERR_ALLOC;
+  s->ws_elems = need;
+  return SPION_OK;
+}
+
 // derive the super-block structure of a 32-wide mask (set_pattern time; synchronises once)
 int build_super(spion_ctx* c, TcState* s) {
   const int nb64 = c->nb / 2;
@@ -729,13 +745,11 @@ int build_super(spion_ctx* c, TcState* s) {
   SPION_CUDA_TRY(cudaMemcpyAsync(&n, s->nnzb64_dev, 4, cudaMemcpyDeviceToHost, c->stream));
   SPION_CUDA_TRY(cudaStreamSynchronize(c->stream));
   s->nnzb64 = n;
-  const size_t need = (size_t)c->BH * n * 4096;
-  if (need > s->ws_elems) {
-    cudaFree(s->p64_ws); cudaFree(s->ds64_ws);
-    s->p64_ws = s->ds64_ws = nullptr;
-    if (cudaMalloc(&s->p64_ws, need * 2) != cudaSuccess || cudaMalloc(&s->ds64_ws, need * 2) != cudaSuccess)
-      return SPION_ERR_ALLOC;
-    s->ws_elems = need;
+  // The two super-tile workspaces serve the calls that store P (and the stored-path backward).  When the mask runs
+  // on its own blocks they are allocated only if such a call arrives (ensure_super_ws), not here.
+  if (!(s->b32 && s->b32_use)) {
+    int rc = ensure_super_ws(c, s);
+    if (rc) return rc;
   }
   c->launches += 3;
   return SPION_OK;
@@ -778,12 +792,12 @@ int tc_engine_prepare(spion_ctx* c) {
     s->super = c->bs == 32;
     c->tc = s;
   }
-  if (s->super) {
-    int rc = build_super(c, s);
+  if (s->b32) {                      // decides whether the mask runs on its own blocks (before the super-block set-up)
+    int rc = b32_prepare(c, s);
     if (rc) return rc;
   }
-  if (s->b32) {
-    int rc = b32_prepare(c, s);
+  if (s->super) {
+    int rc = build_super(c, s);
     if (rc) return rc;
   }
   const TcView vw = tc_view(c, s);
@@ -835,6 +849,10 @@ static int forward_any(spion_ctx* c, const void* Q, const void* K, const void* V
   if (!s) return SPION_ERR_STATE;
   if (c->nnzb == 0) return SPION_ERR_SHAPE;
   if (s->b32 && s->b32_use && !P_user) return b32_forward(c, s, Q, K, V, keypad, O, lse ? lse : s->lse_ws);
+  if (P_user && s->super) {
+    int rc = ensure_super_ws(c, s);
+    if (rc) return rc;
+  }
   void* P64 = P_user ? (s->super ? s->p64_ws : P_user) : nullptr;
   int rc = fused_forward(c, s, Q, K, V, keypad, O, lse ? lse : s->lse_ws, P64);
   if (rc || !P_user || !s->super) return rc;
