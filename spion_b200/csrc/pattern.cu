@@ -59,6 +59,96 @@ __global__ void __launch_bounds__(256) conv_pool_kernel(const float* __restrict_
   }
 }
 
+// Diagonal filter, block 32 or 64 (the reference's settings: F = 31, main_conv_ff.py:258): the same sums in the
+// same order as conv_pool_kernel, organised so that the filter taps are read once per eight outputs instead of
+// once per output.  A thread computes a run of eight outputs (i0 + k, j0 + k), k = 0..7, along a diagonal of the
+// block: they need the tile diagonal d_m = tile[i0 + m][j0 + m], m = 0 .. F + 6, and output k is
+// ((d_k + d_k+1) + d_k+2) + ... in ascending order -- eight independent fp64 chains.  Runs start at
+// i0 = 0, 8, .., j0 = -7 .. BS - 1 (outputs left of the block are skipped).  The pooled rows are padded by one
+// double so that the row sums (one thread per row) do not collide in shared memory.
+template <int BS, int F>
+__global__ void __launch_bounds__(256) conv_pool_diag_kernel(const float* __restrict__ A, int L, float* __restrict__ pooled) {
+  constexpr int H = F / 2, T = BS + 2 * H, RUN = 8, CS = BS + 1;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  float* tile = reinterpret_cast<float*>(smem_raw);
+  double* cval = reinterpret_cast<double*>(smem_raw + (((size_t)T * T * sizeof(float) + 15) & ~(size_t)15));
+  double* rsum = cval + (size_t)BS * CS;
+  const int bi = blockIdx.y, bj = blockIdx.x, nb = gridDim.x;
+  const int i0g = bi * BS - H, j0g = bj * BS - H;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  // all of a thread's loads are issued before the first store (the tile is read with the latency of one load,
+  // not of one load per row)
+  constexpr int NR = (T + 7) / 8, NCOL = (T + 31) / 32;
+  float v[NR][NCOL];
+#pragma unroll
+  for (int a = 0; a < NR; ++a) {
+    const int ti = warp + 8 * a, gi = i0g + ti;
+#pragma unroll
+    for (int b = 0; b < NCOL; ++b) {
+      const int tj = lane + 32 * b, gj = j0g + tj;
+      v[a][b] = (ti < T && tj < T && gi >= 0 && gi < L && gj >= 0 && gj < L) ? A[(size_t)gi * L + gj] : 0.0f;
+    }
+  }
+#pragma unroll
+  for (int a = 0; a < NR; ++a) {
+    const int ti = warp + 8 * a;
+#pragma unroll
+    for (int b = 0; b < NCOL; ++b) {
+      const int tj = lane + 32 * b;
+      if (ti < T && tj < T) tile[ti * T + tj] = v[a][b];
+    }
+  }
+  __syncthreads();
+  constexpr int RUNS = (BS / RUN) * (BS + RUN - 1);
+  for (int r = threadIdx.x; r < RUNS; r += blockDim.x) {
+    const int i0 = (r / (BS + RUN - 1)) * RUN, j0 = r % (BS + RUN - 1) - (RUN - 1);
+    float d[F + RUN - 1];
+#pragma unroll
+    for (int m = 0; m < F + RUN - 1; ++m)          // taps left or right of the tile belong to skipped outputs only
+      d[m] = (j0 + m >= 0 && j0 + m < T) ? tile[(i0 + m) * T + (j0 + m)] : 0.0f;
+    double c[RUN];
+#pragma unroll
+    for (int k = 0; k < RUN; ++k) c[k] = 0.0;
+    // c[k] = sum_{t = 0 .. F-1} d[k + t], t ascending (oracle: conv_fixed_order); the eight chains interleave
+#pragma unroll
+    for (int t = 0; t < F; ++t) {
+#pragma unroll
+      for (int k = 0; k < RUN; ++k) c[k] = c[k] + (double)d[k + t];
+    }
+#pragma unroll
+    for (int k = 0; k < RUN; ++k) {
+      const int j = j0 + k;
+      if (j >= 0 && j < BS) cval[(i0 + k) * CS + j] = c[k];
+    }
+  }
+  __syncthreads();
+  // r[i] = sum_jj c[i, jj]  (jj ascending), then p = sum_ii r[ii] (ii ascending): pool_fixed_order
+  for (int i = threadIdx.x; i < BS; i += blockDim.x) {
+    double rr = 0.0;
+#pragma unroll 8
+    for (int jj = 0; jj < BS; ++jj) rr = rr + cval[i * CS + jj];
+    rsum[i] = rr;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double p = 0.0;
+#pragma unroll 8
+    for (int ii = 0; ii < BS; ++ii) p = p + rsum[ii];
+    pooled[(size_t)bi * nb + bj] = (float)(p / (double)(BS * BS));
+  }
+}
+
+template <int BS, int F>
+int launch_conv_pool_diag(const float* A, int L, int nb, float* pooled, cudaStream_t st) {
+  constexpr int T = BS + F - 1;
+  const size_t smem = (((size_t)T * T * sizeof(float) + 15) & ~(size_t)15) + ((size_t)BS * (BS + 1) + BS) * sizeof(double);
+  if (smem > 48 * 1024)
+    SPION_CUDA_TRY(cudaFuncSetAttribute(conv_pool_diag_kernel<BS, F>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  conv_pool_diag_kernel<BS, F><<<dim3(nb, nb), 256, smem, st>>>(A, L, pooled);
+  SPION_LAUNCH_CHECK();
+  return SPION_OK;
+}
+
 // ---------------------------------------------------------------- order statistics (one CTA)
 __device__ __forceinline__ uint32_t order_key(float x) {
   uint32_t u = __float_as_uint(x);
@@ -282,10 +372,15 @@ extern "C" int spion_discover_pattern(const float* A, int L, int block_size, int
   size_t smem = (((size_t)T * T * sizeof(float) + 15) & ~(size_t)15) + ((size_t)bs * bs + bs) * sizeof(double);
   // The opt-in above 48 KB belongs to the current device only (a process may drive several), and the
   // call is cheap: make it on every launch that needs it instead of remembering one process-wide size.
-  if (smem > 48 * 1024)
-    SPION_CUDA_TRY(cudaFuncSetAttribute(conv_pool_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  conv_pool_kernel<<<dim3(nb, nb), 256, smem, st>>>(A, L, bs, conv_kind, F, pooled);
-  SPION_LAUNCH_CHECK();
+  if (conv_kind == SPION_CONV_DIAG && F == 31 && (bs == 64 || bs == 32)) {      // the reference's filter: the faster kernel
+    int rc = bs == 64 ? launch_conv_pool_diag<64, 31>(A, L, nb, pooled, st) : launch_conv_pool_diag<32, 31>(A, L, nb, pooled, st);
+    if (rc) return rc;
+  } else {
+    if (smem > 48 * 1024)
+      SPION_CUDA_TRY(cudaFuncSetAttribute(conv_pool_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    conv_pool_kernel<<<dim3(nb, nb), 256, smem, st>>>(A, L, bs, conv_kind, F, pooled);
+    SPION_LAUNCH_CHECK();
+  }
 
   int kcount = 0;
   if (select == SPION_SELECT_TOPK) kcount = (int)((double)(nb * nb) * param - (double)nb);   // main_conv.py:247
