@@ -194,11 +194,12 @@ def time_c_port(Q, K, V, dO, mat, bs, reps=3):
 def time_cpu_oracle(step, want_warmup: int, want_steps: int, budget_s: float = 25.0):
     """Bounded timing of the CPU oracle: up to 3 warm-up and 10 timed steps (what the measurement plan asks for),
     fewer when one step is so long that the whole leg would exceed the budget.  Returns (s per step, warm-up, steps)."""
+    step()                                                   # cold start (thread pool, allocator): not representative
     t0 = time.perf_counter()
     step()
     first = time.perf_counter() - t0
-    warm = 1
-    while warm < min(max(want_warmup, 1), 3) and (warm + 1) * first < 0.3 * budget_s:
+    warm = 2
+    while warm < min(max(want_warmup, 2), 3) and (warm + 1) * first < 0.3 * budget_s:
         step()
         warm += 1
     steps = max(1, min(want_steps, 10, int(0.7 * budget_s / max(first, 1e-9))))
