@@ -149,3 +149,15 @@ def test_agrees_with_the_super_block_path():
     mod.check_device_status()
     for name, a, b in zip(("O", "dQ", "dK", "dV"), own, (out, q.grad, k.grad, v.grad)):
         assert rel(a, b) <= REL, f"{name}: {rel(a, b):.3e}"
+
+
+def test_path_argument_is_checked():
+    from spion_b200 import _lib
+    from spion_b200.native import BlockSparseAttention
+    mod = BlockSparseAttention(cfg(1, 1, 256, 64, 32), dtype=torch.bfloat16)
+    assert _lib.lib.spion_set_block32_path(mod.handle, 3) == -1          # SPION_ERR_ARG
+    assert _lib.lib.spion_set_block32_path(mod.handle, 2) == 0
+    mod.set_mask(torch.ones(8, 8, dtype=torch.uint8, device="cuda"))
+    assert _lib.lib.spion_block32_path_in_use(mod.handle) == 2
+    with pytest.raises(KeyError):
+        BlockSparseAttention(cfg(1, 1, 256, 64, 32), dtype=torch.bfloat16, block32="fastest")

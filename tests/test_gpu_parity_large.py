@@ -72,6 +72,8 @@ REGIMES = [
     (16384, 64, 0.30, 64),     # rows and columns of ~77 blocks, nb = 256
     (16384, 32, 0.02, 64),     # nb = 512; 32-wide blocks on super-blocks at full length
     (4096, 32, 0.05, 32),      # super-blocks with head_dim 32
+    (8192, 32, 0.30, 64),      # 32-wide blocks on their own: rows and columns of ~77 blocks, 20 gathered jobs per unit
+    (4096, 32, 0.10, 64),      # ... rows of ~13 blocks, partially filled last jobs
     (2048, 64, 1.00, 64),      # the warm-up phase's full mask: 32 blocks in every row and column
 ]
 
