@@ -407,6 +407,60 @@ def run_pattern(args, rank, local_rank):
         "cpu_baseline": cpu, "gpu_launches": 3 * args.steps}))
 
 
+def run_meanmap(args, rank, local_rank):
+    """The head / batch mean of the attention map that feeds pattern discovery (models/model_transformer.py:137).
+    meanmap_dense_*: the reduction of a stored [B, H, L, L] fp32 tensor (what the reference-layout warm-up path
+    leaves).  meanmap_recompute_*: the native warm-up path, which stores no probability: the map is rebuilt from
+    Q, K and the forward's log-sum-exp on the tensor cores (spion_mean_map_recompute; full mask)."""
+    if rank != 0:
+        return
+    from spion_b200 import pattern, synthetic
+    dev = torch.device("cuda", local_rank)
+    peaks = load_peaks()
+    dense = args.workload.startswith("meanmap_dense")
+    if dense:
+        B, H, L = 256, 2, 1024                                   # image encoder shape: 2.1 GB of probabilities
+        g = torch.Generator().manual_seed(3)
+        attn = torch.rand(B, H, L, L, generator=g).to(dev)
+        run = lambda: pattern.mean_attention_map(attn)
+        by, cfg = 4.0 * B * H * L * L + 4.0 * L * L, {"B": B, "H": H, "L": L, "stored": "fp32 [B, H, L, L]"}
+    else:
+        from spion_b200.native import DenseViaBlocks
+        B, H, L, d, bs = 32, 2, 4096, 32, 64                     # text encoder shape
+        cfg_m = {"head_dim": d, "num_head": H, "max_seq_len": L, "batch_size": B, "block_size": bs,
+                 "transformer_dim": H * d, "task": "bench"}
+        mod = DenseViaBlocks(cfg_m, dtype=torch.bfloat16)
+        Q, K, V, _ = [t.to(torch.bfloat16).to(dev) for t in synthetic.qkv(5, B, H, L, d)]
+        out, handle = mod(Q, K, V)
+        run = lambda: mod.mean_attention_map(handle)
+        by = 2.0 * 2 * B * H * L * d + 4.0 * B * H * L + 4.0 * L * L       # Q, K, lse in; the map out
+        cfg = {"B": B, "H": H, "L": L, "d_head": d, "block": bs, "stored": "nothing (rebuilt from Q, K, lse)",
+               "flops": 2.0 * B * H * L * L * d}
+    for _ in range(args.warmup):
+        A = run()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        A = run()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    rows = float(A.sum(-1).mean())
+    line = {"metric": "mean attention maps/s at L=%d" % L, "value": 1e3 / ms, "unit": "maps/s", "n_gpus": 1,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32" if dense else "bf16 in, f32 out", "data": "synthetic",
+            "config": dict(cfg, workload=args.workload, mean_row_sum=rows),
+            "roofline": {"bound": "hbm", "achieved": by / (ms * 1e-3) / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": by / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
+                         "algorithmic_bytes_per_launch": by},
+            "gpu_launches": args.steps}
+    if not dense:
+        line["tensor"] = {"TFLOPs": cfg["flops"] / (ms * 1e-3) / 1e12, "peak": peaks["bf16_tflops"],
+                          "frac": cfg["flops"] / (ms * 1e-3) / 1e12 / peaks["bf16_tflops"]}
+    print(json.dumps(line))
+
+
 REFCUDA_WORKLOADS = {
     # name: (B, H, L, d, bs, density) -- fp32, the reference's own layouts
     "refcuda_config1_L1024": (8, 2, 1024, 32, 32, 0.15),
@@ -650,7 +704,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="sweep_L4096_bs64_d05",
                     choices=sorted(WORKLOADS) + sorted(TRAIN_WORKLOADS) + sorted(REFCUDA_WORKLOADS) +
-                    ["pattern_L4096_bs64", "pattern_L1024_bs32", "sweep_table"])
+                    ["pattern_L4096_bs64", "pattern_L1024_bs32", "sweep_table", "meanmap_dense_L1024", "meanmap_recompute_L4096"])
     ap.add_argument("--engine", default="auto", choices=["auto", "simt", "tcgen05", "staged"])
     ap.add_argument("--mode", default="auto", choices=["auto", "fused", "stored", "staged"],
                     help="fused: S, P, dP, dS stay on chip, the backward rebuilds its tiles (tcgen05 engine); "
@@ -691,6 +745,9 @@ def main():
         return
     if args.workload.startswith("pattern_"):
         run_pattern(args, rank, local_rank)
+        return
+    if args.workload.startswith("meanmap_"):
+        run_meanmap(args, rank, local_rank)
         return
     if args.workload == "sweep_table":
         run_sweep_table(args, rank, world, local_rank)

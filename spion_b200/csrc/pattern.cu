@@ -285,8 +285,39 @@ __global__ void __launch_bounds__(1024) select_kernel(const float* __restrict__ 
 
 // ---------------------------------------------------------------- mean over (b,h) of the dense map
 // out[i*L + j] = (1/H) sum_h ( (1/B) sum_b in[b*H + h][...] ), b and h ascending.
-__global__ void mean_map_kernel(const float* __restrict__ attn, int B, int H, int L, int transposed,
-                                float* __restrict__ A) {
+// A thread owns four consecutive memory columns of one row (16-byte loads, 512 contiguous bytes per warp and
+// matrix) and keeps eight matrices' loads in flight; the additions stay in the order above.  L % 128 == 0.
+__global__ void __launch_bounds__(256) mean_map_kernel(const float* __restrict__ attn, int B, int H, int L, int transposed,
+                                                       float* __restrict__ A) {
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;   // 32 x 8
+  const size_t LL = (size_t)L * L;
+  const int row = blockIdx.y * 8 + ty, col = blockIdx.x * 128 + 4 * tx;        // memory coordinates
+  const size_t m = (size_t)row * L + col;
+  float4 acc_h = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int hh = 0; hh < H; ++hh) {
+    float4 acc_b = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+    for (int b = 0; b < B; ++b) {
+      const float4 v = *reinterpret_cast<const float4*>(attn + (size_t)(b * H + hh) * LL + m);
+      acc_b.x += v.x; acc_b.y += v.y; acc_b.z += v.z; acc_b.w += v.w;
+    }
+    acc_h.x += acc_b.x / (float)B; acc_h.y += acc_b.y / (float)B;
+    acc_h.z += acc_b.z / (float)B; acc_h.w += acc_b.w / (float)B;
+  }
+  const float4 r = make_float4(acc_h.x / (float)H, acc_h.y / (float)H, acc_h.z / (float)H, acc_h.w / (float)H);
+  if (transposed) {                                          // memory (row = j, col = i) -> A[i][j]
+    A[(size_t)(col + 0) * L + row] = r.x;
+    A[(size_t)(col + 1) * L + row] = r.y;
+    A[(size_t)(col + 2) * L + row] = r.z;
+    A[(size_t)(col + 3) * L + row] = r.w;
+  } else {
+    *reinterpret_cast<float4*>(A + m) = r;
+  }
+}
+
+// The same for any L that is a multiple of 32 (one value per thread, 32 x 32 tiles through shared memory).
+__global__ void mean_map_kernel32(const float* __restrict__ attn, int B, int H, int L, int transposed,
+                                  float* __restrict__ A) {
   __shared__ float tile[32][33];
   const int tx = threadIdx.x, ty = threadIdx.y;             // 32 x 8
   const size_t LL = (size_t)L * L;
@@ -296,7 +327,8 @@ __global__ void mean_map_kernel(const float* __restrict__ attn, int B, int H, in
     float acc_h = 0.0f;
     for (int hh = 0; hh < H; ++hh) {
       float acc_b = 0.0f;
-      for (int b = 0; b < B; ++b) acc_b += attn[(size_t)(b * H + hh) * LL + m];
+#pragma unroll 8
+      for (int b = 0; b < B; ++b) acc_b += attn[(size_t)(b * H + hh) * LL + m];   // loads of eight matrices in flight; sum in order
       acc_h += acc_b / (float)B;
     }
     tile[rr][tx] = acc_h / (float)H;
@@ -399,8 +431,12 @@ extern "C" int spion_mean_attention_map(const float* attn, int batch, int heads,
                                         void* cuda_stream) {
   if (!attn || !A) return SPION_ERR_ARG;
   if (batch < 1 || heads < 1 || L < 32 || L % 32 != 0) return SPION_ERR_SHAPE;
-  mean_map_kernel<<<dim3(L / 32, L / 32), dim3(32, 8), 0, (cudaStream_t)cuda_stream>>>(attn, batch, heads, L,
-                                                                                        transposed, A);
+  const bool aligned = (((uintptr_t)attn | (uintptr_t)A) & 15u) == 0;          // 16-byte loads and stores
+  if (L % 128 == 0 && aligned)
+    mean_map_kernel<<<dim3(L / 128, L / 8), 256, 0, (cudaStream_t)cuda_stream>>>(attn, batch, heads, L, transposed, A);
+  else
+    mean_map_kernel32<<<dim3(L / 32, L / 32), dim3(32, 8), 0, (cudaStream_t)cuda_stream>>>(attn, batch, heads, L,
+                                                                                            transposed, A);
   SPION_LAUNCH_CHECK();
   return SPION_OK;
 }
