@@ -255,41 +255,89 @@ __global__ void __launch_bounds__(256) softmax_bwd_rows_kernel(const float* __re
   }
 }
 
-// Dense attention stored transposed (value(i,j) at j*L + i): one thread per query row i, so that
-// consecutive threads touch consecutive addresses while walking the keys j.
-__global__ void softmax_fwd_dense_t_kernel(float* __restrict__ S, int L, float scale, const float* __restrict__ keypad,
-                                           float floor_v) {
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+// Dense attention stored transposed (value(i,j) at j*L + i).  A CTA owns 32 consecutive query rows (lane = row, so
+// that a warp touches 128 consecutive bytes per key) and its DENSE_WARPS warps split the keys; the row statistics
+// of the slices meet in shared memory.  Three passes over the CTA's [L x 32] strip (maximum, sum, write), which
+// stays in L2 between them.  Semantics as softmax_fwd_rows_kernel at full density (models/attn.cu:9-36).
+constexpr int DENSE_WARPS = 8;
+
+__global__ void __launch_bounds__(DENSE_WARPS * 32) softmax_fwd_dense_t_kernel(float* __restrict__ S, int L, float scale,
+                                                                               const float* __restrict__ keypad,
+                                                                               float floor_v) {
+  __shared__ float s_red[DENSE_WARPS][32];
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const int i = blockIdx.x * 32 + lane;
   const int bh = blockIdx.y;
-  if (i >= L) return;
-  float* Sb = S + (long long)bh * L * L + i;
+  const bool live = i < L;
+  float* Sb = S + (long long)bh * L * L + (live ? i : 0);
   const float* kp = keypad ? keypad + (long long)bh * L : nullptr;
-  float m = floor_v, sum = 0.f;
-  for (int j = 0; j < L; ++j) {                          // online max / sum
-    float v = Sb[(long long)j * L] * scale;
-    if (kp) v -= kp[j];
-    if (v > m) { sum *= expf(m - v); m = v; }
-    sum += expf(v - m);
+  const int per = (L + DENSE_WARPS - 1) / DENSE_WARPS, j0 = w * per, j1 = min(L, j0 + per);
+  float m = floor_v;
+  if (live) {
+#pragma unroll 4
+    for (int j = j0; j < j1; ++j) {
+      float v = Sb[(long long)j * L] * scale;
+      if (kp) v -= kp[j];
+      m = fmaxf(m, v);
+    }
   }
+  s_red[w][lane] = m;
+  __syncthreads();
+#pragma unroll
+  for (int k = 0; k < DENSE_WARPS; ++k) m = fmaxf(m, s_red[k][lane]);
+  __syncthreads();
+  float sum = 0.f;
+  if (live) {
+#pragma unroll 4
+    for (int j = j0; j < j1; ++j) {
+      float v = Sb[(long long)j * L] * scale;
+      if (kp) v -= kp[j];
+      sum += expf(v - m);
+    }
+  }
+  s_red[w][lane] = sum;
+  __syncthreads();
+  sum = 0.f;
+#pragma unroll
+  for (int k = 0; k < DENSE_WARPS; ++k) sum += s_red[k][lane];      // slices added in slice order
   const float inv = 1.0f / sum;
-  for (int j = 0; j < L; ++j) {
-    float v = Sb[(long long)j * L] * scale;
-    if (kp) v -= kp[j];
-    Sb[(long long)j * L] = expf(v - m) * inv;
+  if (live) {
+#pragma unroll 4
+    for (int j = j0; j < j1; ++j) {
+      float v = Sb[(long long)j * L] * scale;
+      if (kp) v -= kp[j];
+      Sb[(long long)j * L] = expf(v - m) * inv;
+    }
   }
 }
 
-__global__ void softmax_bwd_dense_t_kernel(const float* __restrict__ dP, const float* __restrict__ P,
-                                           float* __restrict__ dS, int L, float scale) {
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+// dS = (dP . P - P rowsum(dP . P)) scale (models/attn.cu:67-87), same decomposition.
+__global__ void __launch_bounds__(DENSE_WARPS * 32) softmax_bwd_dense_t_kernel(const float* __restrict__ dP,
+                                                                               const float* __restrict__ P,
+                                                                               float* __restrict__ dS, int L, float scale) {
+  __shared__ float s_red[DENSE_WARPS][32];
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const int i = blockIdx.x * 32 + lane;
   const int bh = blockIdx.y;
-  if (i >= L) return;
-  const long long o = (long long)bh * L * L + i;
+  const bool live = i < L;
+  const long long o = (long long)bh * L * L + (live ? i : 0);
+  const int per = (L + DENSE_WARPS - 1) / DENSE_WARPS, j0 = w * per, j1 = min(L, j0 + per);
   float s = 0.f;
-  for (int j = 0; j < L; ++j) s += dP[o + (long long)j * L] * P[o + (long long)j * L];
-  for (int j = 0; j < L; ++j) {
-    const float pv = P[o + (long long)j * L];
-    dS[o + (long long)j * L] = (dP[o + (long long)j * L] * pv - pv * s) * scale;
+  if (live) {
+#pragma unroll 4
+    for (int j = j0; j < j1; ++j) s += dP[o + (long long)j * L] * P[o + (long long)j * L];
+  }
+  s_red[w][lane] = s;
+  __syncthreads();
+  s = 0.f;
+#pragma unroll
+  for (int k = 0; k < DENSE_WARPS; ++k) s += s_red[k][lane];
+  if (live) {
+#pragma unroll 4
+    for (int j = j0; j < j1; ++j) {
+      const float pv = P[o + (long long)j * L];
+      dS[o + (long long)j * L] = (dP[o + (long long)j * L] * pv - pv * s) * scale;
+    }
   }
 }
 
@@ -373,14 +421,14 @@ int softmax_bwd_rows(int dtype_p, const float* dP, ValueLayout vdp, const void* 
 
 int softmax_fwd_dense_t(float* S, int BH, int L, float scale, const float* keypad, float floor_v, cudaStream_t st) {
   if (BH > 65535) return SPION_ERR_UNSUPPORTED;
-  softmax_fwd_dense_t_kernel<<<dim3((L + 127) / 128, BH), 128, 0, st>>>(S, L, scale, keypad, floor_v);
+  softmax_fwd_dense_t_kernel<<<dim3((L + 31) / 32, BH), DENSE_WARPS * 32, 0, st>>>(S, L, scale, keypad, floor_v);
   SPION_LAUNCH_CHECK();
   return SPION_OK;
 }
 
 int softmax_bwd_dense_t(const float* dP, const float* P, float* dS, int BH, int L, float scale, cudaStream_t st) {
   if (BH > 65535) return SPION_ERR_UNSUPPORTED;
-  softmax_bwd_dense_t_kernel<<<dim3((L + 127) / 128, BH), 128, 0, st>>>(dP, P, dS, L, scale);
+  softmax_bwd_dense_t_kernel<<<dim3((L + 31) / 32, BH), DENSE_WARPS * 32, 0, st>>>(dP, P, dS, L, scale);
   SPION_LAUNCH_CHECK();
   return SPION_OK;
 }
