@@ -359,7 +359,8 @@ __global__ void __launch_bounds__(256) mean_map_tiles_kernel(const T* __restrict
   for (int e = threadIdx.x; e < n; e += blockDim.x) {
     float acc = 0.f;
     const T* src = P + (size_t)blk * n + e;
-    for (int bh = 0; bh < BH; ++bh) acc += to_f32(src[(size_t)bh * nnzb * n]);
+#pragma unroll 8
+    for (int bh = 0; bh < BH; ++bh) acc += to_f32(src[(size_t)bh * nnzb * n]);   // eight loads in flight; sum in order
     A[(size_t)(r * bs + e / bs) * L + c * bs + e % bs] = acc * inv;
   }
 }
