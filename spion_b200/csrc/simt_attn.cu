@@ -255,6 +255,226 @@ __global__ void __launch_bounds__(256) softmax_bwd_rows_kernel(const float* __re
   }
 }
 
+// ---- rows of 32- or 64-wide blocks in 16-byte pieces: sixteen lanes per element row
+// Lane hl of a row's sixteen owns four consecutive values of one block per step: step `it` covers block it (64-wide)
+// or blocks 2 it and 2 it + 1 (32-wide).  Rows of at most 16 * 4 * ROW_STEPS_* values are read once into registers, all
+// loads of a lane issued before the first use, and written once; longer rows make three (two) passes.  Needs 16-byte
+// aligned value arrays (8 bytes for bf16), which the launchers check; same formulas as the kernels above, other
+// summation order.
+constexpr int ROW_STEPS_FWD = 8, ROW_STEPS_BWD = 4;   // measured: deeper caches cost occupancy in the backward
+
+template <int BS>
+struct RowPiece {
+  const int nblk, hl;
+  __device__ __forceinline__ RowPiece(int nblk_, int hl_) : nblk(nblk_), hl(hl_) {}
+  __device__ __forceinline__ int steps() const { return BS == 64 ? nblk : (nblk + 1) >> 1; }
+  __device__ __forceinline__ int block(int it) const { return BS == 64 ? it : 2 * it + (hl >> 3); }
+  __device__ __forceinline__ bool valid(int it) const { return block(it) < nblk; }
+  __device__ __forceinline__ int col() const { return BS == 64 ? hl * 4 : (hl & 7) * 4; }
+};
+
+// Start of element row ii's values inside one (b,h) matrix and the distance between its slices of consecutive blocks.
+__device__ __forceinline__ void row_base(const ValueLayout& vl, int bs, int rp, int nblk, int ii, long long& base,
+                                         int& kstride) {
+  if (vl.mode == VAL_ELEMCSR) {
+    base = (long long)rp * bs * bs + (long long)ii * nblk * bs;
+    kstride = bs;
+  } else {
+    base = (long long)rp * bs * bs + (long long)ii * bs;
+    kstride = bs * bs;
+  }
+}
+
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
+  const uint2 w = *reinterpret_cast<const uint2*>(p);
+  const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&w.x);
+  const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&w.y);
+  const float2 a = __bfloat1622float2(lo), b = __bfloat1622float2(hi);
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16* p, float4 v) {
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+  uint2 w;
+  w.x = *reinterpret_cast<const unsigned*>(&lo);
+  w.y = *reinterpret_cast<const unsigned*>(&hi);
+  *reinterpret_cast<uint2*>(p) = w;
+}
+__device__ __forceinline__ float half_max(unsigned mask, float v) {
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(mask, v, o));
+  return v;
+}
+__device__ __forceinline__ float half_sum(unsigned mask, float v) {
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) v += __shfl_xor_sync(mask, v, o);
+  return v;
+}
+__device__ __forceinline__ float4 scaled(float4 v, float scale, const float* kp) {
+  v.x *= scale, v.y *= scale, v.z *= scale, v.w *= scale;
+  if (kp) {
+    const float4 k = load4(kp);
+    v.x -= k.x, v.y -= k.y, v.z -= k.z, v.w -= k.w;
+  }
+  return v;
+}
+__device__ __forceinline__ float max4(float m, float4 v) { return fmaxf(fmaxf(m, fmaxf(v.x, v.y)), fmaxf(v.z, v.w)); }
+__device__ __forceinline__ float4 exp4(float4 v, float m) {
+  return make_float4(expf(v.x - m), expf(v.y - m), expf(v.z - m), expf(v.w - m));
+}
+
+template <typename TP, int BS>
+__global__ void __launch_bounds__(256, 4) softmax_fwd_rows16_kernel(const float* S, ValueLayout vin,   // S may alias P
+                                                                    TP* P, ValueLayout vout, Pattern p, int BH, int L,
+                                                                    float scale, const float* __restrict__ keypad,
+                                                                    float floor_v) {
+  const unsigned ctas_per_bh = (unsigned)L >> 4;   // L is a multiple of the block size
+  const int bh = (int)(blockIdx.x / ctas_per_bh), row = (int)(blockIdx.x % ctas_per_bh) * 16 + (threadIdx.x >> 4);
+  const unsigned hmask = 0xffffu << (threadIdx.x & 16);
+  const int r = row / BS, ii = row % BS;
+  const int rp = p.row_ptr[r], nblk = p.row_ptr[r + 1] - rp;
+  const RowPiece<BS> pc(nblk, threadIdx.x & 15);
+  long long ibase, obase;
+  int iks, oks;
+  row_base(vin, BS, rp, nblk, ii, ibase, iks);
+  row_base(vout, BS, rp, nblk, ii, obase, oks);
+  const float* src = S + (long long)bh * vin.bh_stride + ibase + pc.col();
+  TP* dst = P + (long long)bh * vout.bh_stride + obase + pc.col();
+  const float* kp = keypad ? keypad + (long long)bh * L + pc.col() : nullptr;
+  const int nsteps = pc.steps(), nvals = nblk * BS;
+
+  if (nsteps <= ROW_STEPS_FWD) {
+    float4 v[ROW_STEPS_FWD];
+#pragma unroll
+    for (int it = 0; it < ROW_STEPS_FWD; ++it) {
+      if (it >= nsteps) break;
+      if (pc.valid(it)) v[it] = load4(src + pc.block(it) * iks);
+    }
+    float m = floor_v;
+#pragma unroll
+    for (int it = 0; it < ROW_STEPS_FWD; ++it) {
+      if (it >= nsteps) break;
+      if (pc.valid(it)) {
+        v[it] = scaled(v[it], scale, kp ? kp + p.col_idx[rp + pc.block(it)] * BS : nullptr);
+        m = max4(m, v[it]);
+      }
+    }
+    m = half_max(hmask, m);
+    float sum = 0.f;
+#pragma unroll
+    for (int it = 0; it < ROW_STEPS_FWD; ++it) {
+      if (it >= nsteps) break;
+      if (pc.valid(it)) {
+        v[it] = exp4(v[it], m);
+        sum += (v[it].x + v[it].y) + (v[it].z + v[it].w);
+      }
+    }
+    sum = half_sum(hmask, sum) + (float)(L - nvals) * expf(-m);
+    const float inv = 1.0f / sum;
+#pragma unroll
+    for (int it = 0; it < ROW_STEPS_FWD; ++it) {
+      if (it >= nsteps) break;
+      if (pc.valid(it)) {
+        const float4 o = (inv == 0.f) ? make_float4(0.f, 0.f, 0.f, 0.f)
+                                      : make_float4(v[it].x * inv, v[it].y * inv, v[it].z * inv, v[it].w * inv);
+        store4(dst + pc.block(it) * oks, o);
+      }
+    }
+    return;
+  }
+
+  float m = floor_v;
+  for (int it = 0; it < nsteps; ++it)
+    if (pc.valid(it))
+      m = max4(m, scaled(load4(src + pc.block(it) * iks), scale, kp ? kp + p.col_idx[rp + pc.block(it)] * BS : nullptr));
+  m = half_max(hmask, m);
+  float sum = 0.f;
+  for (int it = 0; it < nsteps; ++it)
+    if (pc.valid(it)) {
+      const float4 e = exp4(
+          scaled(load4(src + pc.block(it) * iks), scale, kp ? kp + p.col_idx[rp + pc.block(it)] * BS : nullptr), m);
+      sum += (e.x + e.y) + (e.z + e.w);
+    }
+  sum = half_sum(hmask, sum) + (float)(L - nvals) * expf(-m);
+  const float inv = 1.0f / sum;
+  for (int it = 0; it < nsteps; ++it)
+    if (pc.valid(it)) {
+      const float4 e = exp4(
+          scaled(load4(src + pc.block(it) * iks), scale, kp ? kp + p.col_idx[rp + pc.block(it)] * BS : nullptr), m);
+      store4(dst + pc.block(it) * oks, (inv == 0.f) ? make_float4(0.f, 0.f, 0.f, 0.f)
+                                                      : make_float4(e.x * inv, e.y * inv, e.z * inv, e.w * inv));
+    }
+}
+
+template <typename TP, int BS>
+__global__ void __launch_bounds__(256, 4) softmax_bwd_rows16_kernel(const float* __restrict__ dP, ValueLayout vdp,
+                                                                    const TP* __restrict__ P, ValueLayout vp,
+                                                                    TP* __restrict__ dS, ValueLayout vds, Pattern p,
+                                                                    int BH, int L, float scale) {
+  const unsigned ctas_per_bh = (unsigned)L >> 4;   // L is a multiple of the block size
+  const int bh = (int)(blockIdx.x / ctas_per_bh), row = (int)(blockIdx.x % ctas_per_bh) * 16 + (threadIdx.x >> 4);
+  const unsigned hmask = 0xffffu << (threadIdx.x & 16);
+  const int r = row / BS, ii = row % BS;
+  const int rp = p.row_ptr[r], nblk = p.row_ptr[r + 1] - rp;
+  const RowPiece<BS> pc(nblk, threadIdx.x & 15);
+  long long b1, b2, b3;
+  int k1, k2, k3;
+  row_base(vdp, BS, rp, nblk, ii, b1, k1);
+  row_base(vp, BS, rp, nblk, ii, b2, k2);
+  row_base(vds, BS, rp, nblk, ii, b3, k3);
+  const float* pa = dP + (long long)bh * vdp.bh_stride + b1 + pc.col();
+  const TP* pq = P + (long long)bh * vp.bh_stride + b2 + pc.col();
+  TP* po = dS + (long long)bh * vds.bh_stride + b3 + pc.col();
+  const int nsteps = pc.steps();
+
+  if (nsteps <= ROW_STEPS_BWD) {
+    float4 a[ROW_STEPS_BWD], q[ROW_STEPS_BWD];
+#pragma unroll
+    for (int it = 0; it < ROW_STEPS_BWD; ++it) {
+      if (it >= nsteps) break;
+      if (pc.valid(it)) {
+        a[it] = load4(pa + pc.block(it) * k1);
+        q[it] = load4(pq + pc.block(it) * k2);
+      }
+    }
+    float s = 0.f;
+#pragma unroll
+    for (int it = 0; it < ROW_STEPS_BWD; ++it) {
+      if (it >= nsteps) break;
+      if (pc.valid(it)) {
+        a[it].x *= q[it].x, a[it].y *= q[it].y, a[it].z *= q[it].z, a[it].w *= q[it].w;
+        s += (a[it].x + a[it].y) + (a[it].z + a[it].w);
+      }
+    }
+    s = half_sum(hmask, s);
+#pragma unroll
+    for (int it = 0; it < ROW_STEPS_BWD; ++it) {
+      if (it >= nsteps) break;
+      if (pc.valid(it))
+        store4(po + pc.block(it) * k3,
+               make_float4((a[it].x - q[it].x * s) * scale, (a[it].y - q[it].y * s) * scale,
+                           (a[it].z - q[it].z * s) * scale, (a[it].w - q[it].w * s) * scale));
+    }
+    return;
+  }
+
+  float s = 0.f;
+  for (int it = 0; it < nsteps; ++it)
+    if (pc.valid(it)) {
+      const float4 a = load4(pa + pc.block(it) * k1), q = load4(pq + pc.block(it) * k2);
+      s += (a.x * q.x + a.y * q.y) + (a.z * q.z + a.w * q.w);
+    }
+  s = half_sum(hmask, s);
+  for (int it = 0; it < nsteps; ++it)
+    if (pc.valid(it)) {
+      const float4 a = load4(pa + pc.block(it) * k1), q = load4(pq + pc.block(it) * k2);
+      store4(po + pc.block(it) * k3,
+             make_float4((a.x * q.x - q.x * s) * scale, (a.y * q.y - q.y * s) * scale, (a.z * q.z - q.z * s) * scale,
+                         (a.w * q.w - q.w * s) * scale));
+    }
+}
+
 // Dense attention stored transposed (value(i,j) at j*L + i).  A CTA owns 32 consecutive query rows (lane = row, so
 // that a warp touches 128 consecutive bytes per key) and its DENSE_WARPS warps split the keys; the row statistics
 // of the slices meet in shared memory.  Three passes over the CTA's [L x 32] strip (maximum, sum, write), which
@@ -393,28 +613,73 @@ int simt_spmm(int dtype_val, int dtype_op, bool trans, const void* vals, ValueLa
   return SPION_ERR_UNSUPPORTED;
 }
 
+static bool aligned_to(const void* ptr, size_t n) { return ((uintptr_t)ptr & (n - 1)) == 0; }
+static bool piece_layout(const ValueLayout& vl) { return vl.mode != VAL_DENSE_T && vl.bh_stride % 4 == 0; }
+
+template <int BS>
+static void softmax_fwd_rows16_launch(int dtype_out, const float* S, ValueLayout vin, void* P, ValueLayout vout, Pattern p,
+                                      int BH, int L, float scale, const float* keypad, float floor_v, cudaStream_t st) {
+  const unsigned grid = (unsigned)BH * (unsigned)(L / 16);
+  if (dtype_out == SPION_F32)
+    softmax_fwd_rows16_kernel<float, BS><<<grid, 256, 0, st>>>(S, vin, (float*)P, vout, p, BH, L, scale, keypad,
+                                                               floor_v);
+  else
+    softmax_fwd_rows16_kernel<__nv_bfloat16, BS><<<grid, 256, 0, st>>>(S, vin, (__nv_bfloat16*)P, vout, p, BH, L,
+                                                                       scale, keypad, floor_v);
+}
+
 int softmax_fwd_rows(int dtype_out, const float* S, ValueLayout vin, void* P, ValueLayout vout, Pattern p, int BH, int L,
                      float scale, const float* keypad, float floor_v, cudaStream_t st) {
   const long long rows = (long long)BH * L;
-  const unsigned grid = (unsigned)((rows + 7) / 8);
-  if (dtype_out == SPION_F32)
-    softmax_fwd_rows_kernel<float><<<grid, 256, 0, st>>>(S, vin, (float*)P, vout, p, BH, L, scale, keypad, floor_v);
-  else
-    softmax_fwd_rows_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(S, vin, (__nv_bfloat16*)P, vout, p, BH, L, scale,
-                                                                 keypad, floor_v);
+  const bool pieces = (p.bs == 32 || p.bs == 64) && piece_layout(vin) && piece_layout(vout) && aligned_to(S, 16) &&
+                      aligned_to(P, dtype_out == SPION_F32 ? 16 : 8) && (!keypad || aligned_to(keypad, 16));
+  if (pieces && p.bs == 64) {
+    softmax_fwd_rows16_launch<64>(dtype_out, S, vin, P, vout, p, BH, L, scale, keypad, floor_v, st);
+  } else if (pieces) {
+    softmax_fwd_rows16_launch<32>(dtype_out, S, vin, P, vout, p, BH, L, scale, keypad, floor_v, st);
+  } else {
+    const unsigned grid = (unsigned)((rows + 7) / 8);
+    if (dtype_out == SPION_F32)
+      softmax_fwd_rows_kernel<float><<<grid, 256, 0, st>>>(S, vin, (float*)P, vout, p, BH, L, scale, keypad, floor_v);
+    else
+      softmax_fwd_rows_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(S, vin, (__nv_bfloat16*)P, vout, p, BH, L, scale,
+                                                                   keypad, floor_v);
+  }
   SPION_LAUNCH_CHECK();
   return SPION_OK;
+}
+
+template <int BS>
+static void softmax_bwd_rows16_launch(int dtype_p, const float* dP, ValueLayout vdp, const void* P, ValueLayout vp,
+                                      void* dS, ValueLayout vds, Pattern p, int BH, int L, float scale, cudaStream_t st) {
+  const unsigned grid = (unsigned)BH * (unsigned)(L / 16);
+  if (dtype_p == SPION_F32)
+    softmax_bwd_rows16_kernel<float, BS><<<grid, 256, 0, st>>>(dP, vdp, (const float*)P, vp, (float*)dS, vds, p, BH, L,
+                                                               scale);
+  else
+    softmax_bwd_rows16_kernel<__nv_bfloat16, BS><<<grid, 256, 0, st>>>(dP, vdp, (const __nv_bfloat16*)P, vp,
+                                                                       (__nv_bfloat16*)dS, vds, p, BH, L, scale);
 }
 
 int softmax_bwd_rows(int dtype_p, const float* dP, ValueLayout vdp, const void* P, ValueLayout vp, void* dS,
                      ValueLayout vds, Pattern p, int BH, int L, float scale, cudaStream_t st) {
   const long long rows = (long long)BH * L;
-  const unsigned grid = (unsigned)((rows + 7) / 8);
-  if (dtype_p == SPION_F32)
-    softmax_bwd_rows_kernel<float><<<grid, 256, 0, st>>>(dP, vdp, (const float*)P, vp, (float*)dS, vds, p, BH, L, scale);
-  else
-    softmax_bwd_rows_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(dP, vdp, (const __nv_bfloat16*)P, vp,
-                                                                 (__nv_bfloat16*)dS, vds, p, BH, L, scale);
+  const size_t pal = dtype_p == SPION_F32 ? 16 : 8;
+  const bool pieces = (p.bs == 32 || p.bs == 64) && piece_layout(vdp) && piece_layout(vp) && piece_layout(vds) &&
+                      aligned_to(dP, 16) && aligned_to(P, pal) && aligned_to(dS, pal);
+  if (pieces && p.bs == 64) {
+    softmax_bwd_rows16_launch<64>(dtype_p, dP, vdp, P, vp, dS, vds, p, BH, L, scale, st);
+  } else if (pieces) {
+    softmax_bwd_rows16_launch<32>(dtype_p, dP, vdp, P, vp, dS, vds, p, BH, L, scale, st);
+  } else {
+    const unsigned grid = (unsigned)((rows + 7) / 8);
+    if (dtype_p == SPION_F32)
+      softmax_bwd_rows_kernel<float><<<grid, 256, 0, st>>>(dP, vdp, (const float*)P, vp, (float*)dS, vds, p, BH, L,
+                                                           scale);
+    else
+      softmax_bwd_rows_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(dP, vdp, (const __nv_bfloat16*)P, vp,
+                                                                   (__nv_bfloat16*)dS, vds, p, BH, L, scale);
+  }
   SPION_LAUNCH_CHECK();
   return SPION_OK;
 }
