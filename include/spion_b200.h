@@ -334,6 +334,16 @@ int spion_layernorm_backward(const float* x, const void* dy, int dy_is_bf16, con
 int spion_column_sums(const void* dy, int dy_is_bf16, float* out, float* workspace, long long M, int N,
                       void* cuda_stream);
 
+/* Weight gradient of a token embedding with a small table (torch.nn.Embedding(vocab_size, embedding_dim) in the
+ * reference's encoder, models/model_transformer.py; vocab_size 256 - 512 in its tasks):
+ *   dW[v, :] = sum over tokens t with ids[t] == v of g[t, :]
+ * ids [T] int64, g [T, N] fp32 (or bf16 with g_is_bf16 != 0), both 16-byte aligned; dW [V, N] fp32 is overwritten;
+ * ids outside [0, V) are skipped.  N in {32, 64, 128, 256}, V * N <= 24576 (the table is kept in shared memory).
+ * workspace: spion_embedding_workspace_floats(T, V, N) floats.  Fixed summation order: same bits on every run. */
+long long spion_embedding_workspace_floats(long long T, int V, int N);
+int spion_embedding_backward(const long long* ids, const void* g, int g_is_bf16, long long T, int V, int N,
+                             float* dW, float* workspace, void* cuda_stream);
+
 #ifdef __cplusplus
 }
 #endif

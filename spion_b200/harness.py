@@ -53,7 +53,10 @@ def make_norm(config, feeds_linear: bool):
 class Embeddings(nn.Module):
     def __init__(self, config):
         super().__init__()
-        self.tok = nn.Embedding(config["vocab_size"], config["embedding_dim"])
+        Embedding = nn.Embedding
+        if config.get("native") and config.get("fused_embedding_grad", True):
+            from .layernorm import TokenEmbedding as Embedding      # same parameter and forward; own weight gradient
+        self.tok = Embedding(config["vocab_size"], config["embedding_dim"])
         self.pos = nn.Embedding(config["max_seq_len"], config["embedding_dim"])
         nn.init.normal_(self.tok.weight, std=0.02)
         nn.init.normal_(self.pos.weight, std=0.02)

@@ -117,3 +117,48 @@ class BiasGradLinear(nn.Linear):
         if self.bias is None or not x.is_cuda:
             return super().forward(x)
         return _LinearFn.apply(x, self.weight, self.bias)
+
+
+class _EmbeddingFn(torch.autograd.Function):
+    """Rows of a small table by token id; the weight gradient (a scatter-sum the framework forms by sorting the
+    ids) through spion_embedding_backward: table in shared memory, fixed summation order."""
+
+    @staticmethod
+    def forward(ctx, ids, weight):
+        ctx.save_for_backward(ids)
+        ctx.table = (weight.shape, weight.dtype)
+        return torch.nn.functional.embedding(ids, weight)
+
+    @staticmethod
+    def backward(ctx, g):
+        (ids,) = ctx.saved_tensors
+        (V, N), wd = ctx.table
+        g2 = g.reshape(-1, N).contiguous()
+        idc = ids.reshape(-1).contiguous()
+        if idc.data_ptr() % 16:                               # views at odd offsets: the kernel copies 16-byte pieces
+            idc = idc.clone()
+        if g2.data_ptr() % 16:
+            g2 = g2.clone()
+        T = idc.numel()
+        ws = torch.empty(int(lib.spion_embedding_workspace_floats(T, V, N)), dtype=torch.float32, device=g2.device)
+        dW = torch.empty(V, N, dtype=torch.float32, device=g2.device)
+        with torch.cuda.device(g2.device):
+            check(lib.spion_embedding_backward(ptr(idc), ptr(g2), int(g2.dtype == torch.bfloat16), T, V, N, ptr(dW), ptr(ws),
+                                               _lib.current_stream_ptr()), "spion_embedding_backward")
+        return None, dW.to(wd)
+
+
+class TokenEmbedding(nn.Embedding):
+    """``nn.Embedding`` (same parameter, same forward) whose weight gradient comes from the library's kernel when
+    the table is small enough for it (vocab_size * embedding_dim <= 24576, width 32 / 64 / 128 / 256)."""
+
+    def served(self, ids) -> bool:
+        V, N = self.weight.shape
+        return (ids.is_cuda and ids.dtype == torch.int64 and self.padding_idx is None and self.max_norm is None
+                and not self.sparse and not self.scale_grad_by_freq and N in (32, 64, 128, 256) and V * N <= 24576
+                and V * N * 4 + 3 * (128 * N * 4 + 1024) <= 227 * 1024 and self.weight.dtype == torch.float32)
+
+    def forward(self, ids):
+        if not self.served(ids):
+            return super().forward(ids)
+        return _EmbeddingFn.apply(ids, self.weight)

@@ -92,3 +92,47 @@ def test_linear_with_column_sum_bias_gradient(N, dtype):
     for name, a, b in zip(("y", "dx", "dW", "db"), *outs):
         scale = max(1.0, float(a.abs().max()))
         assert float((a - b).abs().max()) <= tol * scale, name
+
+
+@pytest.mark.parametrize("V,N,B,L,dtype", [
+    (256, 64, 16, 4096, torch.float32),      # the retrieval / text tasks' table
+    (256, 64, 3, 1000, torch.float32),       # tokens not a multiple of the staged batch
+    (512, 32, 1, 777, torch.float32),        # odd token count: the last id goes by a plain load
+    (48, 128, 5, 301, torch.bfloat16),
+    (64, 256, 2, 515, torch.float32),
+])
+def test_token_embedding_weight_gradient(V, N, B, L, dtype):
+    """TokenEmbedding against nn.Embedding with the same table: forward bits, weight gradient against an fp64
+    scatter-sum (1e-5 of the largest entry for fp32 rows), identical bits on a second run.  Half of the tokens are
+    id 0 in runs, as padded sequences have them."""
+    from spion_b200.layernorm import TokenEmbedding
+    g = torch.Generator().manual_seed(V + N)
+    ids = torch.randint(0, V, (B, L), generator=g)
+    ids[:, L // 2:] = 0
+    ids = ids.cuda()
+    dy = torch.randn(B, L, N, generator=g).cuda().to(dtype)
+    ref = torch.nn.Embedding(V, N).cuda()
+    mine = TokenEmbedding(V, N).cuda()
+    mine.load_state_dict(ref.state_dict())
+    assert mine.served(ids)
+    assert torch.equal(mine(ids), ref(ids))
+    grads = []
+    for _ in range(2):
+        mine.weight.grad = None
+        y = mine(ids)
+        y.backward(dy.to(y.dtype))
+        grads.append(mine.weight.grad.clone())
+    assert torch.equal(grads[0], grads[1])
+    want = torch.zeros(V, N, dtype=torch.float64, device="cuda")
+    want.index_add_(0, ids.reshape(-1), dy.to(torch.float32).double().reshape(-1, N))
+    err = float((grads[0].double() - want).abs().max())
+    assert err <= 1e-5 * max(1.0, float(want.abs().max()))
+
+
+def test_token_embedding_falls_back_for_large_tables():
+    from spion_b200.layernorm import TokenEmbedding
+    mod = TokenEmbedding(30000, 64).cuda()
+    ids = torch.randint(0, 30000, (2, 128)).cuda()
+    assert not mod.served(ids)
+    mod(ids).sum().backward()
+    assert mod.weight.grad is not None
