@@ -11,7 +11,7 @@
 namespace {
 
 constexpr int EMB_THREADS = 512;                   // 16 warps
-constexpr int EMB_BATCH = 128;                     // tokens per staged batch
+constexpr int EMB_BATCH_BYTES = 32 * 1024;          // gradient rows of one staged batch (32 - 128 tokens)
 constexpr int EMB_STAGES = 3;                      // batches in flight or in use
 constexpr int EMB_MAX_TABLE_FLOATS = 24 * 1024;    // 96 KB of shared memory for the table
 
@@ -22,19 +22,25 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int PENDING>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(PENDING)); }
 
-// Shared memory: table [V][N] fp32, then EMB_STAGES stages of { gradient rows [EMB_BATCH][N], ids [EMB_BATCH] }.
+// Shared memory: table [V][N] fp32, then EMB_STAGES stages of { gradient rows [batch][N], ids [batch] }.
 // The batch of a stage arrives by 16-byte asynchronous copies issued by all threads, EMB_STAGES - 1 batches ahead.
 // Warp w owns the 32 columns (w % (N/32)) * 32 ... of the table rows whose id % groups == w / (N/32), groups =
 // 16 / (N/32): a table element is only ever touched by one thread, in token order.  A warp reads the 32 ids of a
 // sub-batch at once, votes on the ones that are its own and walks those; a run of equal ids is summed in a register
 // before it goes to the table (padding tokens come in long runs).
+__host__ __device__ inline int emb_batch(int N, int esize) {   // tokens per staged batch: a multiple of 32
+  const int b = EMB_BATCH_BYTES / (N * esize);
+  return b > 128 ? 128 : (b < 32 ? 32 : b / 32 * 32);
+}
+
 template <typename TG>
 __global__ void __launch_bounds__(EMB_THREADS) embedding_bwd_kernel(const long long* __restrict__ ids,
                                                                     const TG* __restrict__ g, long long T, int V,
                                                                     int N, float* __restrict__ partial) {
+  const int batch = emb_batch(N, (int)sizeof(TG));
   extern __shared__ __align__(16) unsigned char smem_raw[];
   float* table = reinterpret_cast<float*>(smem_raw);
-  const size_t stage_bytes = (size_t)EMB_BATCH * N * sizeof(TG) + EMB_BATCH * sizeof(long long);
+  const size_t stage_bytes = (size_t)batch * N * sizeof(TG) + batch * sizeof(long long);
   unsigned char* stages = smem_raw + (size_t)V * N * sizeof(float);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int col_parts = N / 32, groups = (EMB_THREADS / 32) / col_parts;
@@ -43,18 +49,18 @@ __global__ void __launch_bounds__(EMB_THREADS) embedding_bwd_kernel(const long l
   for (int i = threadIdx.x; i < V * N; i += EMB_THREADS) table[i] = 0.f;
 
   // this CTA's tokens: whole batches, so that every copy starts on a 16-byte boundary
-  const long long batches = (T + EMB_BATCH - 1) / EMB_BATCH;
+  const long long batches = (T + batch - 1) / batch;
   const long long per = (batches + gridDim.x - 1) / gridDim.x;
   const long long b0 = (long long)blockIdx.x * per, b1 = min(batches, b0 + per);
 
   auto fetch = [&](long long b) {
     unsigned char* st = stages + (size_t)((b - b0) % EMB_STAGES) * stage_bytes;
-    const long long t0 = b * EMB_BATCH;
-    const int ntok = (int)min((long long)EMB_BATCH, T - t0);
+    const long long t0 = b * batch;
+    const int ntok = (int)min((long long)batch, T - t0);
     const int row_pieces = N * (int)sizeof(TG) / 16;
     const unsigned char* src = reinterpret_cast<const unsigned char*>(g + t0 * N);
     for (int i = threadIdx.x; i < ntok * row_pieces; i += EMB_THREADS) cp_async16(st + (size_t)i * 16, src + (size_t)i * 16);
-    unsigned char* sid = st + (size_t)EMB_BATCH * N * sizeof(TG);
+    unsigned char* sid = st + (size_t)batch * N * sizeof(TG);
     const unsigned char* isrc = reinterpret_cast<const unsigned char*>(ids + t0);
     for (int i = threadIdx.x; i < ntok / 2; i += EMB_THREADS) cp_async16(sid + (size_t)i * 16, isrc + (size_t)i * 16);
     if ((ntok & 1) && threadIdx.x == 0)   // odd tail: the last id by a plain load
@@ -74,18 +80,14 @@ __global__ void __launch_bounds__(EMB_THREADS) embedding_bwd_kernel(const long l
     __syncthreads();                      // batch b has landed for every thread (and the table is zeroed)
     const unsigned char* st = stages + (size_t)((b - b0) % EMB_STAGES) * stage_bytes;
     const TG* gs = reinterpret_cast<const TG*>(st);
-    const long long* sid = reinterpret_cast<const long long*>(st + (size_t)EMB_BATCH * N * sizeof(TG));
-    const int ntok = (int)min((long long)EMB_BATCH, T - b * EMB_BATCH);
+    const long long* sid = reinterpret_cast<const long long*>(st + (size_t)batch * N * sizeof(TG));
+    const int ntok = (int)min((long long)batch, T - b * batch);
     for (int s = 0; s < ntok; s += 32) {
       long long raw = -1;
       if (s + lane < ntok) raw = sid[s + lane];
-      const bool mine = raw >= 0 && raw < V && (int)(raw % groups) == grp;
+      const bool mine = raw >= 0 && raw < V && ((int)raw & (groups - 1)) == grp;   // groups is a power of two
       unsigned m = __ballot_sync(0xffffffffu, mine);
-      while (m) {
-        const int k = __ffs(m) - 1;
-        m &= m - 1;
-        const int id = (int)__shfl_sync(0xffffffffu, (int)raw, k);
-        const float v = to_f32(gs[(s + k) * N + col]);
+      auto add = [&](int id, float v) {
         if (id == cur) {
           acc += v;
         } else {
@@ -93,6 +95,17 @@ __global__ void __launch_bounds__(EMB_THREADS) embedding_bwd_kernel(const long l
           cur = id;
           acc = v;
         }
+      };
+      while (m) {                          // two tokens per turn: their loads do not wait for each other
+        const int k0 = __ffs(m) - 1;
+        m &= m - 1;
+        const int k1 = m ? __ffs(m) - 1 : k0;
+        const bool two = m != 0;
+        m &= m - 1;
+        const int id0 = __shfl_sync(0xffffffffu, (int)raw, k0), id1 = __shfl_sync(0xffffffffu, (int)raw, k1);
+        const float v0 = to_f32(gs[(s + k0) * N + col]), v1 = to_f32(gs[(s + k1) * N + col]);
+        add(id0, v0);
+        if (two) add(id1, v1);
       }
     }
     __syncthreads();                      // the stage may be overwritten by the next fetch
@@ -124,14 +137,15 @@ __global__ void __launch_bounds__(256) embedding_bwd_reduce_kernel(const float* 
 }
 
 size_t emb_smem(int V, int N, int g_is_bf16) {
-  return (size_t)V * N * sizeof(float) + EMB_STAGES * ((size_t)EMB_BATCH * N * (g_is_bf16 ? 2 : 4) + EMB_BATCH * sizeof(long long));
+  const int batch = emb_batch(N, g_is_bf16 ? 2 : 4);
+  return (size_t)V * N * sizeof(float) + EMB_STAGES * ((size_t)batch * N * (g_is_bf16 ? 2 : 4) + batch * sizeof(long long));
 }
 
 int emb_grid(long long T) {
   int dev = 0, sms = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return -1;
   if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return -1;
-  const long long want = (T + 2 * EMB_BATCH - 1) / (2 * EMB_BATCH);   // at least two batches per CTA
+  const long long want = (T + 255) / 256;   // at least 256 tokens per CTA
   return (int)std::max<long long>(1, std::min<long long>(sms, want));
 }
 
@@ -145,7 +159,8 @@ extern "C" long long spion_embedding_workspace_floats(long long T, int V, int N)
 }
 
 // dW [V, N] fp32 = scatter-sum of the gradient rows g [T, N] (fp32 or bf16, 16-byte aligned) by token id (int64,
-// 16-byte aligned; ids outside [0, V) are skipped).  N in {32, 64, 128, 256}, V * N <= 24576 and table plus three staged batches of 128 rows within 227 KB of shared memory.  Overwrites dW.
+// 16-byte aligned; ids outside [0, V) are skipped).  N in {32, 64, 128, 256}, V * N <= 24576 (table plus three
+// staged batches of at most 32 KB of rows within the shared memory of an SM).  Overwrites dW.
 // Fixed summation order.
 extern "C" int spion_embedding_backward(const long long* ids, const void* g, int g_is_bf16, long long T, int V, int N,
                                         float* dW, float* workspace, void* cuda_stream) {

@@ -156,7 +156,7 @@ class TokenEmbedding(nn.Embedding):
         V, N = self.weight.shape
         return (ids.is_cuda and ids.dtype == torch.int64 and self.padding_idx is None and self.max_norm is None
                 and not self.sparse and not self.scale_grad_by_freq and N in (32, 64, 128, 256) and V * N <= 24576
-                and V * N * 4 + 3 * (128 * N * 4 + 1024) <= 227 * 1024 and self.weight.dtype == torch.float32)
+                and self.weight.dtype == torch.float32)
 
     def forward(self, ids):
         if not self.served(ids):
