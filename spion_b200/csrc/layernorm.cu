@@ -59,6 +59,7 @@ __global__ void __launch_bounds__(LN_WARPS * 32) ln_fwd_kernel(const float* __re
     g[k] = *reinterpret_cast<const float2*>(gamma + 64 * k + 2 * lane);
     b[k] = *reinterpret_cast<const float2*>(beta + 64 * k + 2 * lane);
   }
+#pragma unroll 2   // the loads of a second row are issued before the first row's reductions
   for (long long r = warp0; r < M; r += nwarps) {
     float2 v[K];
     float s = 0.f;
@@ -99,6 +100,7 @@ __global__ void __launch_bounds__(LN_WARPS * 32) ln_bwd_kernel(const float* __re
     ag[k] = make_float2(0.f, 0.f);
     ab[k] = make_float2(0.f, 0.f);
   }
+#pragma unroll 2
   for (long long r = warp0; r < M; r += nwarps) {
     const float mu = mean[r], rs = rstd[r];
     float2 xh[K], gy[K];
@@ -170,6 +172,7 @@ __global__ void __launch_bounds__(LN_WARPS * 32) colsum_kernel(const void* __res
   float2 ab[K];
 #pragma unroll
   for (int k = 0; k < K; ++k) ab[k] = make_float2(0.f, 0.f);
+#pragma unroll 4
   for (long long r = warp0; r < M; r += nwarps) {
 #pragma unroll
     for (int k = 0; k < K; ++k) {

@@ -258,7 +258,7 @@ __global__ void __launch_bounds__(256) softmax_bwd_rows_kernel(const float* __re
 // ---- rows of 32- or 64-wide blocks in 16-byte pieces: sixteen lanes per element row
 // Lane hl of a row's sixteen owns four consecutive values of one block per step: step `it` covers block it (64-wide)
 // or blocks 2 it and 2 it + 1 (32-wide).  Rows of at most 16 * 4 * ROW_STEPS_* values are read once into registers, all
-// loads of a lane issued before the first use, and written once; longer rows make three (two) passes.  Needs 16-byte
+// loads of a lane issued before the first use, and written once; longer rows make two passes.  Needs 16-byte
 // aligned value arrays (8 bytes for bf16), which the launchers check; same formulas as the kernels above, other
 // summation order.
 constexpr int ROW_STEPS_FWD = 8, ROW_STEPS_BWD = 4;   // measured: deeper caches cost occupancy in the backward
@@ -384,27 +384,45 @@ __global__ void __launch_bounds__(256, 4) softmax_fwd_rows16_kernel(const float*
     return;
   }
 
-  float m = floor_v;
-  for (int it = 0; it < nsteps; ++it)
-    if (pc.valid(it))
-      m = max4(m, scaled(load4(src + pc.block(it) * iks), scale, kp ? kp + p.col_idx[rp + pc.block(it)] * BS : nullptr));
-  m = half_max(hmask, m);
-  float sum = 0.f;
-  for (int it = 0; it < nsteps; ++it)
-    if (pc.valid(it)) {
-      const float4 e = exp4(
-          scaled(load4(src + pc.block(it) * iks), scale, kp ? kp + p.col_idx[rp + pc.block(it)] * BS : nullptr), m);
-      sum += (e.x + e.y) + (e.z + e.w);
-    }
-  sum = half_sum(hmask, sum) + (float)(L - nvals) * expf(-m);
+  // Longer rows, two passes with the loads of four steps in flight: (1) per lane the running maximum and the sum of
+  // exponentials relative to it (rescaled when the maximum rises), joined over the sixteen lanes; (2) P.
+  auto value = [&](int it) {
+    return scaled(load4(src + pc.block(it) * iks), scale, kp ? kp + p.col_idx[rp + pc.block(it)] * BS : nullptr);
+  };
+  float m = floor_v, sum = 0.f;
+  for (int it0 = 0; it0 < nsteps; it0 += 4) {
+    float4 v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (it0 + u < nsteps && pc.valid(it0 + u)) v[u] = value(it0 + u);
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (it0 + u < nsteps && pc.valid(it0 + u)) {
+        const float vm = max4(m, v[u]);
+        if (vm > m) {
+          sum *= expf(m - vm);
+          m = vm;
+        }
+        const float4 e = exp4(v[u], m);
+        sum += (e.x + e.y) + (e.z + e.w);
+      }
+  }
+  const float mrow = half_max(hmask, m);
+  sum = half_sum(hmask, sum * expf(m - mrow)) + (float)(L - nvals) * expf(-mrow);
   const float inv = 1.0f / sum;
-  for (int it = 0; it < nsteps; ++it)
-    if (pc.valid(it)) {
-      const float4 e = exp4(
-          scaled(load4(src + pc.block(it) * iks), scale, kp ? kp + p.col_idx[rp + pc.block(it)] * BS : nullptr), m);
-      store4(dst + pc.block(it) * oks, (inv == 0.f) ? make_float4(0.f, 0.f, 0.f, 0.f)
-                                                      : make_float4(e.x * inv, e.y * inv, e.z * inv, e.w * inv));
-    }
+  for (int it0 = 0; it0 < nsteps; it0 += 4) {
+    float4 v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (it0 + u < nsteps && pc.valid(it0 + u)) v[u] = value(it0 + u);
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (it0 + u < nsteps && pc.valid(it0 + u)) {
+        const float4 e = exp4(v[u], mrow);
+        store4(dst + pc.block(it0 + u) * oks, (inv == 0.f) ? make_float4(0.f, 0.f, 0.f, 0.f)
+                                                             : make_float4(e.x * inv, e.y * inv, e.z * inv, e.w * inv));
+      }
+  }
 }
 
 template <typename TP, int BS>
