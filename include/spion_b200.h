@@ -328,6 +328,19 @@ int spion_layernorm_backward(const float* x, const void* dy, int dy_is_bf16, con
                              const float* rstd, float* dx, float* dgamma, float* dbeta, float* workspace,
                              long long M, int N, void* cuda_stream);
 
+/* Residual connection + normalisation in one pass (X = branch + X; norm(X) in the reference's encoder layer,
+ * models/model_transformer.py): sum_out = x + res (x fp32; res fp32, or bf16 with res_is_bf16 != 0),
+ * y = LayerNorm(sum_out); mean / rstd as spion_layernorm_forward.  sum_out must not alias x or res. */
+int spion_add_layernorm_forward(const float* x, const void* res, int res_is_bf16, float* sum_out, const float* gamma,
+                                const float* beta, void* y, int y_is_bf16, float* mean, float* rstd, long long M, int N,
+                                float eps, void* cuda_stream);
+/* Its backward: x is the saved sum; dx = (gradient through the normalisation) + dskip, where dskip (may be NULL) is
+ * the gradient the sum receives from its other consumers; dx is the gradient of both addends, dx_bf16 (may be NULL)
+ * receives a bf16 copy of it.  dgamma, dbeta, workspace as spion_layernorm_backward. */
+int spion_add_layernorm_backward(const float* x, const void* dy, int dy_is_bf16, const float* gamma, const float* mean,
+                                 const float* rstd, const float* dskip, float* dx, void* dx_bf16, float* dgamma,
+                                 float* dbeta, float* workspace, long long M, int N, void* cuda_stream);
+
 /* Sum of the rows of an [M, N] matrix (fp32, or bf16 with dy_is_bf16 != 0), N in {64, 128, 256, 512}: out [N] fp32.
  * The bias gradient of a linear layer (torch.nn.Linear in the reference's encoder) as one streaming pass plus a
  * fixed-order reduction.  workspace: spion_layernorm_workspace_floats(N) floats. */

@@ -49,7 +49,10 @@ template <int K, bool Y_BF16>
 __global__ void __launch_bounds__(LN_WARPS * 32) ln_fwd_kernel(const float* __restrict__ x, const float* __restrict__ gamma,
                                                                const float* __restrict__ beta, void* __restrict__ y,
                                                                float* __restrict__ mean, float* __restrict__ rstd,
-                                                               long long M, float eps) {
+                                                               long long M, float eps, const void* __restrict__ res,
+                                                               int res_is_bf16, float* __restrict__ sum_out) {
+  // res != nullptr: the row that is normalised is x + res (a residual connection: x the fp32 stream, res the
+  // branch output, fp32 or bf16), and it is also written to sum_out
   constexpr int N = 64 * K;
   const int lane = threadIdx.x & 31;
   const long long warp0 = (long long)blockIdx.x * LN_WARPS + (threadIdx.x >> 5), nwarps = (long long)gridDim.x * LN_WARPS;
@@ -65,7 +68,13 @@ __global__ void __launch_bounds__(LN_WARPS * 32) ln_fwd_kernel(const float* __re
     float s = 0.f;
 #pragma unroll
     for (int k = 0; k < K; ++k) {
-      v[k] = *reinterpret_cast<const float2*>(x + r * N + 64 * k + 2 * lane);
+      const size_t i = (size_t)r * N + 64 * k + 2 * lane;
+      v[k] = *reinterpret_cast<const float2*>(x + i);
+      if (res) {
+        const float2 a = res_is_bf16 ? load2<true>(res, i) : load2<false>(res, i);
+        v[k].x += a.x; v[k].y += a.y;
+        *reinterpret_cast<float2*>(sum_out + i) = v[k];
+      }
       s += v[k].x + v[k].y;
     }
     const float mu = warp_sum(s) * (1.0f / N);
@@ -88,7 +97,11 @@ template <int K, bool DY_BF16>
 __global__ void __launch_bounds__(LN_WARPS * 32) ln_bwd_kernel(const float* __restrict__ x, const void* __restrict__ dy,
                                                                const float* __restrict__ gamma, const float* __restrict__ mean,
                                                                const float* __restrict__ rstd, float* __restrict__ dx,
-                                                               float* __restrict__ partial, long long M) {
+                                                               float* __restrict__ partial, long long M,
+                                                               const float* __restrict__ dskip,
+                                                               __nv_bfloat16* __restrict__ dx_bf16) {
+  // dskip != nullptr: dx = (gradient through the normalisation) + dskip, the gradient that reaches the same row
+  // through the residual connection; dx_bf16 != nullptr: a bf16 copy of dx (the gradient of a bf16 branch output)
   constexpr int N = 64 * K;
   __shared__ float s_g[LN_WARPS][N], s_b[LN_WARPS][N];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -120,9 +133,16 @@ __global__ void __launch_bounds__(LN_WARPS * 32) ln_bwd_kernel(const float* __re
     c1 = warp_sum(c1) * (1.0f / N);
     c2 = warp_sum(c2) * (1.0f / N);
 #pragma unroll
-    for (int k = 0; k < K; ++k)
-      *reinterpret_cast<float2*>(dx + (size_t)r * N + 64 * k + 2 * lane) =
-          make_float2((gy[k].x - c1 - xh[k].x * c2) * rs, (gy[k].y - c1 - xh[k].y * c2) * rs);
+    for (int k = 0; k < K; ++k) {
+      const size_t i = (size_t)r * N + 64 * k + 2 * lane;
+      float2 o = make_float2((gy[k].x - c1 - xh[k].x * c2) * rs, (gy[k].y - c1 - xh[k].y * c2) * rs);
+      if (dskip) {
+        const float2 a = *reinterpret_cast<const float2*>(dskip + i);
+        o.x += a.x; o.y += a.y;
+      }
+      *reinterpret_cast<float2*>(dx + i) = o;
+      if (dx_bf16) store2<true>(dx_bf16, i, o);
+    }
   }
   // the CTA's partial row: the warps' sums added in warp order
 #pragma unroll
@@ -222,16 +242,19 @@ int ln_grid(long long M) {
 
 }  // namespace
 
-// N must be 64, 128, 256 or 512; rows are contiguous.  Returns SPION_ERR_SHAPE otherwise.
-extern "C" int spion_layernorm_forward(const float* x, const float* gamma, const float* beta, void* y, int y_is_bf16,
-                                       float* mean, float* rstd, long long M, int N, float eps, void* cuda_stream) {
-  cudaStream_t stream = (cudaStream_t)cuda_stream;
-  if (!x || !gamma || !beta || !y || !mean || !rstd || M < 1) return SPION_ERR_ARG;
+namespace {
+
+int ln_forward(const float* x, const void* res, int res_is_bf16, float* sum_out, const float* gamma, const float* beta,
+               void* y, int y_is_bf16, float* mean, float* rstd, long long M, int N, float eps, cudaStream_t stream) {
   const int grid = ln_grid(M);
   if (grid < 1) return SPION_ERR_CUDA;
-#define SPION_LN_FWD(K)                                                                                              \
-  if (y_is_bf16) ln_fwd_kernel<K, true><<<grid, LN_WARPS * 32, 0, stream>>>(x, gamma, beta, y, mean, rstd, M, eps);  \
-  else ln_fwd_kernel<K, false><<<grid, LN_WARPS * 32, 0, stream>>>(x, gamma, beta, y, mean, rstd, M, eps);
+#define SPION_LN_FWD(K)                                                                                               \
+  if (y_is_bf16)                                                                                                      \
+    ln_fwd_kernel<K, true><<<grid, LN_WARPS * 32, 0, stream>>>(x, gamma, beta, y, mean, rstd, M, eps, res, res_is_bf16, \
+                                                               sum_out);                                              \
+  else                                                                                                                \
+    ln_fwd_kernel<K, false><<<grid, LN_WARPS * 32, 0, stream>>>(x, gamma, beta, y, mean, rstd, M, eps, res,            \
+                                                                res_is_bf16, sum_out);
   switch (N) {
     case 64: SPION_LN_FWD(1) break;
     case 128: SPION_LN_FWD(2) break;
@@ -244,19 +267,18 @@ extern "C" int spion_layernorm_forward(const float* x, const float* gamma, const
   return SPION_OK;
 }
 
-// Floats the backward needs as workspace for a width of N.
-extern "C" long long spion_layernorm_workspace_floats(int N) { return (long long)LN_MAX_CTAS * 2 * N; }
-
-extern "C" int spion_layernorm_backward(const float* x, const void* dy, int dy_is_bf16, const float* gamma,
-                                        const float* mean, const float* rstd, float* dx, float* dgamma, float* dbeta,
-                                        float* workspace, long long M, int N, void* cuda_stream) {
-  cudaStream_t stream = (cudaStream_t)cuda_stream;
-  if (!x || !dy || !gamma || !mean || !rstd || !dx || !dgamma || !dbeta || !workspace || M < 1) return SPION_ERR_ARG;
+int ln_backward(const float* x, const void* dy, int dy_is_bf16, const float* gamma, const float* mean, const float* rstd,
+                const float* dskip, float* dx, __nv_bfloat16* dx_bf16, float* dgamma, float* dbeta, float* workspace,
+                long long M, int N, cudaStream_t stream) {
   const int grid = ln_grid(M);
   if (grid < 1) return SPION_ERR_CUDA;
-#define SPION_LN_BWD(K)                                                                                                 \
-  if (dy_is_bf16) ln_bwd_kernel<K, true><<<grid, LN_WARPS * 32, 0, stream>>>(x, dy, gamma, mean, rstd, dx, workspace, M); \
-  else ln_bwd_kernel<K, false><<<grid, LN_WARPS * 32, 0, stream>>>(x, dy, gamma, mean, rstd, dx, workspace, M);
+#define SPION_LN_BWD(K)                                                                                              \
+  if (dy_is_bf16)                                                                                                    \
+    ln_bwd_kernel<K, true><<<grid, LN_WARPS * 32, 0, stream>>>(x, dy, gamma, mean, rstd, dx, workspace, M, dskip,    \
+                                                               dx_bf16);                                             \
+  else                                                                                                               \
+    ln_bwd_kernel<K, false><<<grid, LN_WARPS * 32, 0, stream>>>(x, dy, gamma, mean, rstd, dx, workspace, M, dskip,   \
+                                                                dx_bf16);
   switch (N) {
     case 64: SPION_LN_BWD(1) break;
     case 128: SPION_LN_BWD(2) break;
@@ -269,6 +291,47 @@ extern "C" int spion_layernorm_backward(const float* x, const void* dy, int dy_i
   ln_bwd_reduce_kernel<<<2 * N / 32, 1024, 0, stream>>>(workspace, grid, N, dgamma, dbeta);
   SPION_LAUNCH_CHECK();
   return SPION_OK;
+}
+
+}  // namespace
+
+// N must be 64, 128, 256 or 512; rows are contiguous.  Returns SPION_ERR_SHAPE otherwise.
+extern "C" int spion_layernorm_forward(const float* x, const float* gamma, const float* beta, void* y, int y_is_bf16,
+                                       float* mean, float* rstd, long long M, int N, float eps, void* cuda_stream) {
+  if (!x || !gamma || !beta || !y || !mean || !rstd || M < 1) return SPION_ERR_ARG;
+  return ln_forward(x, nullptr, 0, nullptr, gamma, beta, y, y_is_bf16, mean, rstd, M, N, eps, (cudaStream_t)cuda_stream);
+}
+
+// Residual connection and normalisation in one pass: sum_out = x + res (res fp32 or bf16), y = LayerNorm(sum_out).
+extern "C" int spion_add_layernorm_forward(const float* x, const void* res, int res_is_bf16, float* sum_out,
+                                           const float* gamma, const float* beta, void* y, int y_is_bf16, float* mean,
+                                           float* rstd, long long M, int N, float eps, void* cuda_stream) {
+  if (!x || !res || !sum_out || !gamma || !beta || !y || !mean || !rstd || M < 1) return SPION_ERR_ARG;
+  return ln_forward(x, res, res_is_bf16, sum_out, gamma, beta, y, y_is_bf16, mean, rstd, M, N, eps,
+                    (cudaStream_t)cuda_stream);
+}
+
+// Floats the backward needs as workspace for a width of N.
+extern "C" long long spion_layernorm_workspace_floats(int N) { return (long long)LN_MAX_CTAS * 2 * N; }
+
+extern "C" int spion_layernorm_backward(const float* x, const void* dy, int dy_is_bf16, const float* gamma,
+                                        const float* mean, const float* rstd, float* dx, float* dgamma, float* dbeta,
+                                        float* workspace, long long M, int N, void* cuda_stream) {
+  if (!x || !dy || !gamma || !mean || !rstd || !dx || !dgamma || !dbeta || !workspace || M < 1) return SPION_ERR_ARG;
+  return ln_backward(x, dy, dy_is_bf16, gamma, mean, rstd, nullptr, dx, nullptr, dgamma, dbeta, workspace, M, N,
+                     (cudaStream_t)cuda_stream);
+}
+
+// Backward of spion_add_layernorm_forward: x is the saved sum; dx = (gradient through the normalisation) + dskip, where
+// dskip (may be NULL) is the gradient the sum receives from its other consumers (the next residual connection).
+// dx is the gradient of both addends; dx_bf16 (may be NULL) receives a bf16 copy for a bf16 addend.
+extern "C" int spion_add_layernorm_backward(const float* x, const void* dy, int dy_is_bf16, const float* gamma,
+                                            const float* mean, const float* rstd, const float* dskip, float* dx,
+                                            void* dx_bf16, float* dgamma, float* dbeta, float* workspace, long long M,
+                                            int N, void* cuda_stream) {
+  if (!x || !dy || !gamma || !mean || !rstd || !dx || !dgamma || !dbeta || !workspace || M < 1) return SPION_ERR_ARG;
+  return ln_backward(x, dy, dy_is_bf16, gamma, mean, rstd, dskip, dx, (__nv_bfloat16*)dx_bf16, dgamma, dbeta, workspace, M,
+                     N, (cudaStream_t)cuda_stream);
 }
 
 // Sum of the rows of an [M, N] matrix (fp32 or bf16), N in {64, 128, 256, 512}: out[N] fp32.  The bias gradient of a

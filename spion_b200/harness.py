@@ -87,6 +87,15 @@ class TransformerLayer(nn.Module):
         X = self.dropout1(out) + X
         return self.mlpblock(self.norm2(X)) + X, attn
 
+    def forward_add_norm(self, X, Xn, mask, mat, next_norm):
+        """The same layer with each residual addition done inside the normalisation that follows it
+        (FusedLayerNorm.add_norm): ``Xn`` is ``self.norm1(X)``, already formed by the previous stage; returns the
+        layer's output together with ``next_norm`` of it (the next layer's norm1, or the encoder's final norm)."""
+        out, attn = self.mha(Xn, mask, mat)
+        X, n2 = self.norm2.add_norm(X, self.dropout1(out))
+        X, nn_ = next_norm.add_norm(X, self.mlpblock(n2))
+        return X, nn_, attn
+
 
 class Encoder(nn.Module):
     def __init__(self, config):
@@ -94,11 +103,20 @@ class Encoder(nn.Module):
         self.embeddings = Embeddings(config)
         self.layers = nn.ModuleList(TransformerLayer(config) for _ in range(config["num_layers"]))
         self.norm = make_norm(config, False)
+        from .layernorm import FusedLayerNorm
+        self.add_norm = bool(config.get("fused_add_norm", True)) and isinstance(self.norm, FusedLayerNorm)
 
     def forward(self, ids, mask, mat_lst=None, is_attn=False):
         from .pattern import mean_attention_map
         X = self.embeddings(ids)
         maps = []
+        if self.add_norm and mat_lst is not None:
+            # sparse phase: residual additions inside the normalisation kernels
+            Xn = self.layers[0].norm1(X)
+            for i, layer in enumerate(self.layers):
+                nxt = self.layers[i + 1].norm1 if i + 1 < len(self.layers) else self.norm
+                X, Xn, _ = layer.forward_add_norm(X, Xn, mask, mat_lst[0][i], nxt)
+            return Xn * mask[:, :, None], maps
         for i, layer in enumerate(self.layers):
             if mat_lst is None:
                 X, attn = layer(X, mask)

@@ -53,6 +53,55 @@ class _LayerNormFn(torch.autograd.Function):
         return dx, dw, db, None, None
 
 
+class _AddLayerNormFn(torch.autograd.Function):
+    """(x + res, LayerNorm(x + res)) in one pass; the backward adds the gradient that arrives at the sum from its
+    other consumers (the next residual connection) to the one through the normalisation in the same kernel."""
+
+    @staticmethod
+    def forward(ctx, x, res, weight, bias, eps, out_bf16):
+        if not x.is_cuda or x.dtype != torch.float32 or res.dtype not in (torch.float32, torch.bfloat16):
+            raise _lib.SpionError("add_norm needs an fp32 CUDA stream and an fp32 or bf16 branch output")
+        N = x.shape[-1]
+        xc, rc = x.contiguous(), res.contiguous()
+        M = xc.numel() // N
+        s = torch.empty_like(xc)
+        y = torch.empty(xc.shape, dtype=torch.bfloat16 if out_bf16 else torch.float32, device=x.device)
+        mean = torch.empty(M, dtype=torch.float32, device=x.device)
+        rstd = torch.empty(M, dtype=torch.float32, device=x.device)
+        w, b = weight.float().contiguous(), bias.float().contiguous()
+        with torch.cuda.device(x.device):
+            check(lib.spion_add_layernorm_forward(ptr(xc), ptr(rc), int(rc.dtype == torch.bfloat16), ptr(s), ptr(w), ptr(b),
+                                                  ptr(y), int(out_bf16), ptr(mean), ptr(rstd), M, N, float(eps),
+                                                  _lib.current_stream_ptr()), "spion_add_layernorm_forward")
+        ctx.save_for_backward(s, w, mean, rstd)
+        ctx.res_bf16 = rc.dtype == torch.bfloat16
+        ctx.set_materialize_grads(False)                          # an unused output arrives as None, not as zeros
+        return s, y
+
+    @staticmethod
+    def backward(ctx, ds, dy):
+        s, w, mean, rstd = ctx.saved_tensors
+        N = s.shape[-1]
+        M = s.numel() // N
+        if dy is None:                                             # the normalised output was not used
+            dy = torch.zeros_like(s)
+        if dy.dtype not in (torch.float32, torch.bfloat16):
+            dy = dy.float()
+        dy = dy.contiguous()
+        if ds is not None:
+            ds = ds.float().contiguous()
+        dx = torch.empty_like(s)
+        dres = torch.empty(s.shape, dtype=torch.bfloat16, device=s.device) if ctx.res_bf16 else None
+        dw = torch.empty(N, dtype=torch.float32, device=s.device)
+        db = torch.empty(N, dtype=torch.float32, device=s.device)
+        ws = torch.empty(int(lib.spion_layernorm_workspace_floats(N)), dtype=torch.float32, device=s.device)
+        with torch.cuda.device(s.device):
+            check(lib.spion_add_layernorm_backward(ptr(s), ptr(dy), int(dy.dtype == torch.bfloat16), ptr(w), ptr(mean),
+                                                   ptr(rstd), ptr(ds), ptr(dx), ptr(dres), ptr(dw), ptr(db), ptr(ws), M, N,
+                                                   _lib.current_stream_ptr()), "spion_add_layernorm_backward")
+        return dx, (dres if ctx.res_bf16 else dx), dw, db, None, None
+
+
 class FusedLayerNorm(nn.Module):
     """Drop-in for ``nn.LayerNorm(dim)`` on fp32 CUDA inputs with dim in SUPPORTED_WIDTHS.
 
@@ -71,6 +120,14 @@ class FusedLayerNorm(nn.Module):
     def forward(self, x):
         out_bf16 = self.bf16_out and torch.is_autocast_enabled()
         return _LayerNormFn.apply(x.float(), self.weight, self.bias, self.eps, out_bf16)
+
+    def add_norm(self, x, res):
+        """``s = x + res`` (x: the fp32 residual stream, res: a branch output, fp32 or bf16) and ``self(s)`` in one
+        pass; returns ``(s, self(s))``."""
+        out_bf16 = self.bf16_out and torch.is_autocast_enabled()
+        if res.dtype not in (torch.float32, torch.bfloat16):
+            res = res.float()
+        return _AddLayerNormFn.apply(x.float(), res, self.weight, self.bias, self.eps, out_bf16)
 
 
 class _LinearFn(torch.autograd.Function):

@@ -74,3 +74,14 @@ def test_fused_layernorm_agrees_with_the_framework_operator():
     b, mb = _run("text", native=True, dtype="fp32", L=256, batch=2, fused_layernorm=False)
     assert torch.equal(m, mb)
     np.testing.assert_allclose(a, b, rtol=2e-4, atol=2e-4)
+
+
+@pytest.mark.parametrize("dtype", ["fp32", "bf16"])
+def test_residual_additions_inside_the_normalisation(dtype):
+    """Sparse steps with each residual addition done by the normalisation kernel that follows it (the default of
+    the native path) against separate additions: same masks, same losses (fp32: the same arithmetic per element)."""
+    a, m = _run("text", native=True, dtype=dtype, L=256, batch=2)
+    b, mb = _run("text", native=True, dtype=dtype, L=256, batch=2, fused_add_norm=False)
+    assert torch.equal(m, mb)
+    tol = 2e-5 if dtype == "fp32" else 3e-2
+    np.testing.assert_allclose(a, b, rtol=tol, atol=tol)

@@ -136,3 +136,40 @@ def test_token_embedding_falls_back_for_large_tables():
     assert not mod.served(ids)
     mod(ids).sum().backward()
     assert mod.weight.grad is not None
+
+
+@pytest.mark.parametrize("res_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("N", [64, 256])
+def test_add_norm_matches_separate_addition_and_normalisation(N, res_dtype):
+    """FusedLayerNorm.add_norm(x, res) = (x + res, norm(x + res)), forward bits and every gradient, when the sum
+    also feeds a later consumer (the next residual connection) and when it does not."""
+    from spion_b200.layernorm import FusedLayerNorm
+    g = torch.Generator().manual_seed(N)
+    M = 3333
+    x0 = torch.randn(M, N, generator=g).cuda()
+    r0 = torch.randn(M, N, generator=g).cuda().to(res_dtype)
+    dy = torch.randn(M, N, generator=g).cuda()
+    dskip = torch.randn(M, N, generator=g).cuda()
+    for use_sum in (True, False):
+        outs = []
+        for fused in (False, True):
+            mod = FusedLayerNorm(N).cuda()
+            with torch.no_grad():
+                mod.weight.copy_(torch.linspace(0.5, 1.5, N)); mod.bias.copy_(torch.linspace(-1, 1, N))
+            x = x0.clone().requires_grad_(True)
+            r = r0.clone().requires_grad_(True)
+            if fused:
+                s, y = mod.add_norm(x, r)
+            else:
+                s = r + x
+                y = mod(s)
+            loss = (y * dy).sum() + ((s * dskip).sum() if use_sum else 0.0)
+            loss.backward()
+            outs.append((s.detach(), y.detach(), x.grad, r.grad.float(), mod.weight.grad, mod.bias.grad))
+        for name, a, b in zip(("sum", "y", "dx", "dres", "dweight", "dbias"), *outs):
+            if name in ("sum", "y"):
+                assert torch.equal(a, b), name
+            else:
+                scale = max(1.0, float(a.abs().max()))
+                tol = 1e-5 if (name != "dres" or res_dtype == torch.float32) else 8e-3
+                assert float((a - b).abs().max()) <= tol * scale, (name, use_sum)
