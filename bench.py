@@ -43,6 +43,7 @@ WORKLOADS = {
     "sweep_L16384_bs64_d02": (8, 8, 16384, 64, 64, 0.02, "bf16"),
     "config1_L1024_fp32": (8, 2, 1024, 32, 32, 0.15, "fp32"),
     "image_L1024_fp32_B256": (256, 2, 1024, 32, 32, 0.15, "fp32"),   # attention layer of the image-shaped training step
+    "retrieval_L4096_d32_B128": (128, 2, 4096, 32, 64, 0.10, "bf16"),  # ... of the retrieval-shaped step (64 pairs)
     "tiny": (2, 2, 512, 64, 64, 0.25, "bf16"),
 }
 

@@ -87,6 +87,8 @@ def make_block_function(config, attn_cpp, attn_handle, with_keypad: bool):
             ctx.save_for_backward(q, key, value, attn, offsets, columns, sum_mat)
             ctx.nnz = nnz
             ctx.mark_non_differentiable(attn)
+            # without this the engine hands the backward a zero-filled gradient of the size of the probabilities
+            ctx.set_materialize_grads(False)
             return out, attn
 
         @staticmethod

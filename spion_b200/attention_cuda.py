@@ -44,6 +44,8 @@ def make_dense_function(config, attn_cpp, attn_handle, with_keypad: bool):
             ctx.save_for_backward(qt, key, value, attn_t)
             attn = attn_t.permute(0, 1, 3, 2)
             ctx.mark_non_differentiable(attn)
+            # without this the engine hands the backward a zero-filled gradient of the size of the probabilities
+            ctx.set_materialize_grads(False)
             return out_t.permute(0, 1, 3, 2), attn
 
         @staticmethod

@@ -240,6 +240,8 @@ def _make_function(mod: BlockSparseAttention):
             if P is None:
                 P = torch.empty(0, dtype=mod.dtype, device=dev)
             ctx.mark_non_differentiable(P)
+            # without this the engine hands the backward a zero-filled gradient of the size of the probabilities
+            ctx.set_materialize_grads(False)
             return O, P
 
         @staticmethod
@@ -284,6 +286,8 @@ def _make_function(mod: BlockSparseAttention):
                   "spion_attn_forward_ex")
             ctx.save_for_backward(q, k, v, P, O)
             ctx.mark_non_differentiable(P)
+            # without this the engine hands the backward a zero-filled gradient of the size of the probabilities
+            ctx.set_materialize_grads(False)
             return O, P
 
         @staticmethod
