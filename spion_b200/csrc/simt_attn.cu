@@ -311,17 +311,26 @@ __device__ __forceinline__ float half_sum(unsigned mask, float v) {
   for (int o = 8; o > 0; o >>= 1) v += __shfl_xor_sync(mask, v, o);
   return v;
 }
-__device__ __forceinline__ float4 scaled(float4 v, float scale, const float* kp) {
-  v.x *= scale, v.y *= scale, v.z *= scale, v.w *= scale;
+// The forward works in base-2 units (one multiply and one ex2 per value instead of a full-range expf; the issue
+// slots were the kernel's second limit after the bytes in flight): v2 = S * (scale * log2 e) - keypad * log2 e.
+constexpr float ROW_LOG2E = 1.4426950408889634f;
+__device__ __forceinline__ float ex2f(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float4 scaled(float4 v, float scale2, const float* kp) {
+  v.x *= scale2, v.y *= scale2, v.z *= scale2, v.w *= scale2;
   if (kp) {
     const float4 k = load4(kp);
-    v.x -= k.x, v.y -= k.y, v.z -= k.z, v.w -= k.w;
+    v.x = fmaf(-k.x, ROW_LOG2E, v.x), v.y = fmaf(-k.y, ROW_LOG2E, v.y);
+    v.z = fmaf(-k.z, ROW_LOG2E, v.z), v.w = fmaf(-k.w, ROW_LOG2E, v.w);
   }
   return v;
 }
 __device__ __forceinline__ float max4(float m, float4 v) { return fmaxf(fmaxf(m, fmaxf(v.x, v.y)), fmaxf(v.z, v.w)); }
 __device__ __forceinline__ float4 exp4(float4 v, float m) {
-  return make_float4(expf(v.x - m), expf(v.y - m), expf(v.z - m), expf(v.w - m));
+  return make_float4(ex2f(v.x - m), ex2f(v.y - m), ex2f(v.z - m), ex2f(v.w - m));
 }
 
 template <typename TP, int BS>
@@ -343,6 +352,7 @@ __global__ void __launch_bounds__(256, 4) softmax_fwd_rows16_kernel(const float*
   TP* dst = P + (long long)bh * vout.bh_stride + obase + pc.col();
   const float* kp = keypad ? keypad + (long long)bh * L + pc.col() : nullptr;
   const int nsteps = pc.steps(), nvals = nblk * BS;
+  const float scale2 = scale * ROW_LOG2E, floor2 = floor_v * ROW_LOG2E;
 
   if (nsteps <= ROW_STEPS_FWD) {
     float4 v[ROW_STEPS_FWD];
@@ -351,12 +361,12 @@ __global__ void __launch_bounds__(256, 4) softmax_fwd_rows16_kernel(const float*
       if (it >= nsteps) break;
       if (pc.valid(it)) v[it] = load4(src + pc.block(it) * iks);
     }
-    float m = floor_v;
+    float m = floor2;
 #pragma unroll
     for (int it = 0; it < ROW_STEPS_FWD; ++it) {
       if (it >= nsteps) break;
       if (pc.valid(it)) {
-        v[it] = scaled(v[it], scale, kp ? kp + p.col_idx[rp + pc.block(it)] * BS : nullptr);
+        v[it] = scaled(v[it], scale2, kp ? kp + p.col_idx[rp + pc.block(it)] * BS : nullptr);
         m = max4(m, v[it]);
       }
     }
@@ -370,7 +380,7 @@ __global__ void __launch_bounds__(256, 4) softmax_fwd_rows16_kernel(const float*
         sum += (v[it].x + v[it].y) + (v[it].z + v[it].w);
       }
     }
-    sum = half_sum(hmask, sum) + (float)(L - nvals) * expf(-m);
+    sum = half_sum(hmask, sum) + (float)(L - nvals) * ex2f(-m);
     const float inv = 1.0f / sum;
 #pragma unroll
     for (int it = 0; it < ROW_STEPS_FWD; ++it) {
@@ -387,9 +397,9 @@ __global__ void __launch_bounds__(256, 4) softmax_fwd_rows16_kernel(const float*
   // Longer rows, two passes with the loads of four steps in flight: (1) per lane the running maximum and the sum of
   // exponentials relative to it (rescaled when the maximum rises), joined over the sixteen lanes; (2) P.
   auto value = [&](int it) {
-    return scaled(load4(src + pc.block(it) * iks), scale, kp ? kp + p.col_idx[rp + pc.block(it)] * BS : nullptr);
+    return scaled(load4(src + pc.block(it) * iks), scale2, kp ? kp + p.col_idx[rp + pc.block(it)] * BS : nullptr);
   };
-  float m = floor_v, sum = 0.f;
+  float m = floor2, sum = 0.f;
   for (int it0 = 0; it0 < nsteps; it0 += 4) {
     float4 v[4];
 #pragma unroll
@@ -400,7 +410,7 @@ __global__ void __launch_bounds__(256, 4) softmax_fwd_rows16_kernel(const float*
       if (it0 + u < nsteps && pc.valid(it0 + u)) {
         const float vm = max4(m, v[u]);
         if (vm > m) {
-          sum *= expf(m - vm);
+          sum *= ex2f(m - vm);
           m = vm;
         }
         const float4 e = exp4(v[u], m);
@@ -408,7 +418,7 @@ __global__ void __launch_bounds__(256, 4) softmax_fwd_rows16_kernel(const float*
       }
   }
   const float mrow = half_max(hmask, m);
-  sum = half_sum(hmask, sum * expf(m - mrow)) + (float)(L - nvals) * expf(-mrow);
+  sum = half_sum(hmask, sum * ex2f(m - mrow)) + (float)(L - nvals) * ex2f(-mrow);
   const float inv = 1.0f / sum;
   for (int it0 = 0; it0 < nsteps; it0 += 4) {
     float4 v[4];
