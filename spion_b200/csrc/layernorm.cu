@@ -229,6 +229,124 @@ __global__ void __launch_bounds__(1024) colsum_reduce_kernel(const float* __rest
   }
 }
 
+// ---- backward and column sums of widths 64 and 128 with 16-byte loads: N / 4 lanes per row, so a warp works on
+// 32 / (N / 4) rows at once (twice the bytes in flight per warp of the kernels above at N = 64).  Lane j of a row owns
+// columns 4 j .. 4 j + 3.  Same formulas; the per-row sums are formed in another order, the weight / bias gradients go
+// through the same fixed-order second stage.  (The forward measured slower in this form and keeps one warp per row.)
+__device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 ld4(const __nv_bfloat16* p) {
+  const uint2 w = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w.y));
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void st4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void st4(__nv_bfloat16* p, float4 v) {
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+  uint2 w;
+  w.x = *reinterpret_cast<const unsigned*>(&lo);
+  w.y = *reinterpret_cast<const unsigned*>(&hi);
+  *reinterpret_cast<uint2*>(p) = w;
+}
+template <int LPR>
+__device__ __forceinline__ float row_sum(float v) {   // over the LPR lanes of a row (all 32 lanes take part)
+#pragma unroll
+  for (int o = LPR / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+template <int N, typename TD>
+__global__ void __launch_bounds__(LN_WARPS * 32) ln_bwd4_kernel(const float* __restrict__ x, const TD* __restrict__ dy,
+                                                                const float* __restrict__ gamma, const float* __restrict__ mean,
+                                                                const float* __restrict__ rstd, float* __restrict__ dx,
+                                                                float* __restrict__ partial, long long M,
+                                                                const float* __restrict__ dskip,
+                                                                __nv_bfloat16* __restrict__ dx_bf16) {
+  constexpr int LPR = N / 4, RPW = 32 / LPR;
+  __shared__ float s_g[LN_WARPS * RPW][N], s_b[LN_WARPS * RPW][N];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, j = lane % LPR, sub = lane / LPR;
+  const long long warp0 = (long long)blockIdx.x * LN_WARPS + warp, nwarps = (long long)gridDim.x * LN_WARPS;
+  const float4 g = ld4(gamma + 4 * j);
+  float4 ag = make_float4(0.f, 0.f, 0.f, 0.f), ab = ag;
+#pragma unroll 2
+  for (long long r0 = warp0 * RPW; r0 < M; r0 += nwarps * RPW) {
+    const long long r = r0 + sub;
+    const bool live = r < M;
+    const long long rr = live ? r : 0;
+    const size_t i = (size_t)rr * N + 4 * j;
+    const float mu = mean[rr], rs = rstd[rr];
+    const float4 xv = ld4(x + i);
+    float4 d = ld4(dy + i);
+    if (!live) d = make_float4(0.f, 0.f, 0.f, 0.f);
+    const float4 xh = make_float4((xv.x - mu) * rs, (xv.y - mu) * rs, (xv.z - mu) * rs, (xv.w - mu) * rs);
+    const float4 gy = make_float4(d.x * g.x, d.y * g.y, d.z * g.z, d.w * g.w);
+    ag.x += d.x * xh.x, ag.y += d.y * xh.y, ag.z += d.z * xh.z, ag.w += d.w * xh.w;
+    ab.x += d.x, ab.y += d.y, ab.z += d.z, ab.w += d.w;
+    const float c1 = row_sum<LPR>((gy.x + gy.y) + (gy.z + gy.w)) * (1.0f / N);
+    const float c2 = row_sum<LPR>((gy.x * xh.x + gy.y * xh.y) + (gy.z * xh.z + gy.w * xh.w)) * (1.0f / N);
+    if (live) {
+      float4 o = make_float4((gy.x - c1 - xh.x * c2) * rs, (gy.y - c1 - xh.y * c2) * rs, (gy.z - c1 - xh.z * c2) * rs,
+                             (gy.w - c1 - xh.w * c2) * rs);
+      if (dskip) {
+        const float4 a = ld4(dskip + i);
+        o.x += a.x, o.y += a.y, o.z += a.z, o.w += a.w;
+      }
+      st4(dx + i, o);
+      if (dx_bf16) st4(dx_bf16 + i, o);
+    }
+  }
+  // the CTA's partial row: the sums of its (warp, sub-row) groups added in that order
+  st4(&s_g[warp * RPW + sub][4 * j], ag);
+  st4(&s_b[warp * RPW + sub][4 * j], ab);
+  __syncthreads();
+  for (int c = threadIdx.x; c < N; c += blockDim.x) {
+    float sg = 0.f, sb = 0.f;
+#pragma unroll
+    for (int w = 0; w < LN_WARPS * RPW; ++w) { sg += s_g[w][c]; sb += s_b[w][c]; }
+    partial[(size_t)blockIdx.x * 2 * N + c] = sg;
+    partial[(size_t)blockIdx.x * 2 * N + N + c] = sb;
+  }
+}
+
+// Column sums with 16-byte loads: a row of N values takes LPR = N * sizeof(T) / 16 lanes (8 or 16 for N = 64, 16 or 32
+// for N = 128), a warp reads 32 / LPR rows per step, four steps in flight.
+template <int N, typename T>
+__global__ void __launch_bounds__(LN_WARPS * 32) colsum4_kernel(const T* __restrict__ dy, float* __restrict__ partial,
+                                                                long long M) {
+  constexpr int PER = 16 / (int)sizeof(T), LPR = N / PER, RPW = 32 / LPR;
+  __shared__ float s_b[LN_WARPS * RPW][N];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, j = lane % LPR, sub = lane / LPR;
+  const long long warp0 = (long long)blockIdx.x * LN_WARPS + warp, nwarps = (long long)gridDim.x * LN_WARPS;
+  float acc[PER];
+#pragma unroll
+  for (int k = 0; k < PER; ++k) acc[k] = 0.f;
+#pragma unroll 4
+  for (long long r = warp0 * RPW + sub; r < M; r += nwarps * RPW) {
+    const T* src = dy + (size_t)r * N + PER * j;
+    if constexpr (PER == 8) {
+      const uint4 w = *reinterpret_cast<const uint4*>(src);
+      const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w.x));
+      const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w.y));
+      const float2 c = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w.z));
+      const float2 d = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w.w));
+      acc[0] += a.x, acc[1] += a.y, acc[2] += b.x, acc[3] += b.y;
+      acc[4] += c.x, acc[5] += c.y, acc[6] += d.x, acc[7] += d.y;
+    } else {
+      const float4 a = ld4(src);
+      acc[0] += a.x, acc[1] += a.y, acc[2] += a.z, acc[3] += a.w;
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < PER; ++k) s_b[warp * RPW + sub][PER * j + k] = acc[k];
+  __syncthreads();
+  for (int c = threadIdx.x; c < N; c += blockDim.x) {
+    float sb = 0.f;
+#pragma unroll
+    for (int w = 0; w < LN_WARPS * RPW; ++w) sb += s_b[w][c];
+    partial[(size_t)blockIdx.x * N + c] = sb;
+  }
+}
+
 int ln_grid(long long M) {
   int dev = 0, sms = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
@@ -243,6 +361,10 @@ int ln_grid(long long M) {
 }  // namespace
 
 namespace {
+
+// every pointer given (null ones aside) on a 16-byte boundary: what the kernels with 16-byte loads need
+template <typename... P>
+bool aligned16(const P*... p) { return ((... | (uintptr_t)p) & 15) == 0; }
 
 int ln_forward(const float* x, const void* res, int res_is_bf16, float* sum_out, const float* gamma, const float* beta,
                void* y, int y_is_bf16, float* mean, float* rstd, long long M, int N, float eps, cudaStream_t stream) {
@@ -272,6 +394,24 @@ int ln_backward(const float* x, const void* dy, int dy_is_bf16, const float* gam
                 long long M, int N, cudaStream_t stream) {
   const int grid = ln_grid(M);
   if (grid < 1) return SPION_ERR_CUDA;
+  if ((N == 64 || N == 128) && aligned16(x, dy, dx, dskip, dx_bf16, gamma)) {
+    if (N == 64 && dy_is_bf16)
+      ln_bwd4_kernel<64, __nv_bfloat16><<<grid, LN_WARPS * 32, 0, stream>>>(x, (const __nv_bfloat16*)dy, gamma, mean, rstd, dx,
+                                                                            workspace, M, dskip, dx_bf16);
+    else if (N == 64)
+      ln_bwd4_kernel<64, float><<<grid, LN_WARPS * 32, 0, stream>>>(x, (const float*)dy, gamma, mean, rstd, dx, workspace, M,
+                                                                    dskip, dx_bf16);
+    else if (dy_is_bf16)
+      ln_bwd4_kernel<128, __nv_bfloat16><<<grid, LN_WARPS * 32, 0, stream>>>(x, (const __nv_bfloat16*)dy, gamma, mean, rstd,
+                                                                             dx, workspace, M, dskip, dx_bf16);
+    else
+      ln_bwd4_kernel<128, float><<<grid, LN_WARPS * 32, 0, stream>>>(x, (const float*)dy, gamma, mean, rstd, dx, workspace, M,
+                                                                     dskip, dx_bf16);
+    SPION_LAUNCH_CHECK();
+    ln_bwd_reduce_kernel<<<2 * N / 32, 1024, 0, stream>>>(workspace, grid, N, dgamma, dbeta);
+    SPION_LAUNCH_CHECK();
+    return SPION_OK;
+  }
 #define SPION_LN_BWD(K)                                                                                              \
   if (dy_is_bf16)                                                                                                    \
     ln_bwd_kernel<K, true><<<grid, LN_WARPS * 32, 0, stream>>>(x, dy, gamma, mean, rstd, dx, workspace, M, dskip,    \
@@ -342,6 +482,16 @@ extern "C" int spion_column_sums(const void* dy, int dy_is_bf16, float* out, flo
   if (!dy || !out || !workspace || M < 1) return SPION_ERR_ARG;
   const int grid = ln_grid(M);
   if (grid < 1) return SPION_ERR_CUDA;
+  if ((N == 64 || N == 128) && ((uintptr_t)dy & 15) == 0) {
+    if (N == 64 && dy_is_bf16) colsum4_kernel<64, __nv_bfloat16><<<grid, LN_WARPS * 32, 0, stream>>>((const __nv_bfloat16*)dy, workspace, M);
+    else if (N == 64) colsum4_kernel<64, float><<<grid, LN_WARPS * 32, 0, stream>>>((const float*)dy, workspace, M);
+    else if (dy_is_bf16) colsum4_kernel<128, __nv_bfloat16><<<grid, LN_WARPS * 32, 0, stream>>>((const __nv_bfloat16*)dy, workspace, M);
+    else colsum4_kernel<128, float><<<grid, LN_WARPS * 32, 0, stream>>>((const float*)dy, workspace, M);
+    SPION_LAUNCH_CHECK();
+    colsum_reduce_kernel<<<N / 32, 1024, 0, stream>>>(workspace, grid, N, out);
+    SPION_LAUNCH_CHECK();
+    return SPION_OK;
+  }
 #define SPION_COLSUM(K)                                                                                   \
   if (dy_is_bf16) colsum_kernel<K, true><<<grid, LN_WARPS * 32, 0, stream>>>(dy, workspace, M);            \
   else colsum_kernel<K, false><<<grid, LN_WARPS * 32, 0, stream>>>(dy, workspace, M);
