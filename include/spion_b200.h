@@ -354,6 +354,11 @@ int spion_column_sums(const void* dy, int dy_is_bf16, float* out, float* workspa
  * ids outside [0, V) are skipped.  N in {32, 64, 128, 256}, V * N <= 24576 (the table is kept in shared memory).
  * workspace: spion_embedding_workspace_floats(T, V, N) floats.  Fixed summation order: same bits on every run. */
 long long spion_embedding_workspace_floats(long long T, int V, int N);
+/* Token + position embedding of the encoder input in one pass (models/model_transformer.py, Embeddings):
+ * out[t, :] = tok[ids[t], :] + pos[t % L, :] for t in [0, T), T = batch * L; tok [V, N], pos [>= L, N], out [T, N] fp32,
+ * 16-byte aligned, N a multiple of 4; an id outside [0, V) gives the position row alone. */
+int spion_embedding_forward(const long long* ids, const float* tok, const float* pos, float* out, long long T, int L,
+                            int V, int N, void* cuda_stream);
 int spion_embedding_backward(const long long* ids, const void* g, int g_is_bf16, long long T, int V, int N,
                              float* dW, float* workspace, void* cuda_stream);
 

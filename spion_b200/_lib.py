@@ -42,6 +42,7 @@ SIGNATURES = {
     "spion_add_layernorm_backward": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                          c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_void_p]),
     "spion_embedding_workspace_floats": (c_longlong, [c_longlong, c_int, c_int]),
+    "spion_embedding_forward": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_void_p]),
     "spion_embedding_backward": (c_int, [c_void_p, c_void_p, c_int, c_longlong, c_int, c_int, c_void_p, c_void_p,
                                          c_void_p]),
     "spion_layernorm_backward": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,

@@ -136,6 +136,27 @@ __global__ void __launch_bounds__(256) embedding_bwd_reduce_kernel(const float* 
   }
 }
 
+// out[t, :] = tok[ids[t], :] + pos[t % L, :]: token and position embedding of the encoder input in one pass (the
+// framework gathers, then adds the broadcast position rows in a second kernel).  One thread per four columns; both
+// tables stay in cache, so the kernel is bound by writing out.  ids outside [0, V) give the position row alone.
+__global__ void __launch_bounds__(256) embedding_fwd_kernel(const long long* __restrict__ ids, const float* __restrict__ tok,
+                                                            const float* __restrict__ pos, float* __restrict__ out,
+                                                            long long T, int L, int V, int N) {
+  const int per_row = N >> 2;
+  const long long total = T * per_row;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long t = i / per_row;
+    const int c = (int)(i - t * per_row) * 4;
+    const long long id = ids[t];
+    float4 v = *reinterpret_cast<const float4*>(pos + (size_t)(t % L) * N + c);
+    if (id >= 0 && id < V) {
+      const float4 w = *reinterpret_cast<const float4*>(tok + (size_t)id * N + c);
+      v.x += w.x, v.y += w.y, v.z += w.z, v.w += w.w;
+    }
+    *reinterpret_cast<float4*>(out + (size_t)t * N + c) = v;
+  }
+}
+
 size_t emb_smem(int V, int N, int g_is_bf16) {
   const int batch = emb_batch(N, g_is_bf16 ? 2 : 4);
   return (size_t)V * N * sizeof(float) + EMB_STAGES * ((size_t)batch * N * (g_is_bf16 ? 2 : 4) + batch * sizeof(long long));
@@ -185,6 +206,25 @@ extern "C" int spion_embedding_backward(const long long* ids, const void* g, int
   }
   SPION_LAUNCH_CHECK();
   embedding_bwd_reduce_kernel<<<(V * N + 31) / 32, 256, 0, stream>>>(workspace, grid, V * N, dW);
+  SPION_LAUNCH_CHECK();
+  return SPION_OK;
+}
+
+// out [T, N] fp32 = tok[ids[t]] + pos[t % L] (tok [V, N], pos [>= L, N], all 16-byte aligned, N a multiple of 4):
+// the input of the first encoder layer before dropout (models/model_transformer.py: token embedding plus position
+// embedding of positions 0 .. L-1 for every sequence of the batch; T = batch * L).
+extern "C" int spion_embedding_forward(const long long* ids, const float* tok, const float* pos, float* out, long long T,
+                                       int L, int V, int N, void* cuda_stream) {
+  cudaStream_t stream = (cudaStream_t)cuda_stream;
+  if (!ids || !tok || !pos || !out || T < 1 || L < 1 || V < 1) return SPION_ERR_ARG;
+  if ((((uintptr_t)tok) | ((uintptr_t)pos) | ((uintptr_t)out)) & 15) return SPION_ERR_ARG;
+  if (N < 4 || N % 4 != 0) return SPION_ERR_SHAPE;
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+    return SPION_ERR_CUDA;
+  const long long want = (T * (N / 4) + 255) / 256;
+  const int grid = (int)std::max<long long>(1, std::min<long long>(want, (long long)sms * 8));
+  embedding_fwd_kernel<<<grid, 256, 0, stream>>>(ids, tok, pos, out, T, L, V, N);
   SPION_LAUNCH_CHECK();
   return SPION_OK;
 }

@@ -66,6 +66,8 @@ class Embeddings(nn.Module):
         # positions 0 .. L-1 are a slice of the table: the same values as the lookup self.pos(arange(L)) of the
         # reference (models/model_transformer.py), with a plain sum over the batch as backward instead of the
         # sort-based embedding backward
+        if hasattr(self.tok, "with_positions"):
+            return self.drop(self.tok.with_positions(ids, self.pos.weight))         # gather and sum in one kernel
         return self.drop(self.tok(ids) + self.pos.weight[:ids.shape[1]][None])
 
 

@@ -190,19 +190,56 @@ class _EmbeddingFn(torch.autograd.Function):
     def backward(ctx, g):
         (ids,) = ctx.saved_tensors
         (V, N), wd = ctx.table
-        g2 = g.reshape(-1, N).contiguous()
-        idc = ids.reshape(-1).contiguous()
-        if idc.data_ptr() % 16:                               # views at odd offsets: the kernel copies 16-byte pieces
-            idc = idc.clone()
-        if g2.data_ptr() % 16:
-            g2 = g2.clone()
-        T = idc.numel()
-        ws = torch.empty(int(lib.spion_embedding_workspace_floats(T, V, N)), dtype=torch.float32, device=g2.device)
-        dW = torch.empty(V, N, dtype=torch.float32, device=g2.device)
-        with torch.cuda.device(g2.device):
-            check(lib.spion_embedding_backward(ptr(idc), ptr(g2), int(g2.dtype == torch.bfloat16), T, V, N, ptr(dW), ptr(ws),
-                                               _lib.current_stream_ptr()), "spion_embedding_backward")
-        return None, dW.to(wd)
+        return None, _embedding_weight_grad(ids, g, V, N, wd)
+
+
+def _embedding_weight_grad(ids, g, V, N, wd):
+    g2 = g.reshape(-1, N).contiguous()
+    idc = ids.reshape(-1).contiguous()
+    if idc.data_ptr() % 16:                               # views at odd offsets: the kernel copies 16-byte pieces
+        idc = idc.clone()
+    if g2.data_ptr() % 16:
+        g2 = g2.clone()
+    T = idc.numel()
+    ws = torch.empty(int(lib.spion_embedding_workspace_floats(T, V, N)), dtype=torch.float32, device=g2.device)
+    dW = torch.empty(V, N, dtype=torch.float32, device=g2.device)
+    with torch.cuda.device(g2.device):
+        check(lib.spion_embedding_backward(ptr(idc), ptr(g2), int(g2.dtype == torch.bfloat16), T, V, N, ptr(dW), ptr(ws),
+                                           _lib.current_stream_ptr()), "spion_embedding_backward")
+    return dW.to(wd)
+
+
+class _EmbedPosFn(torch.autograd.Function):
+    """tok[ids] + pos[0 .. L-1] for ids [B, L] in one kernel (spion_embedding_forward); backward: the token table's
+    gradient through spion_embedding_backward, the position rows' gradient as the sum over the batch."""
+
+    @staticmethod
+    def forward(ctx, ids, tok, pos):
+        B, L = ids.shape
+        V, N = tok.shape
+        idc = ids.contiguous()
+        out = torch.empty(B, L, N, dtype=torch.float32, device=ids.device)
+        with torch.cuda.device(ids.device):
+            check(lib.spion_embedding_forward(ptr(idc), ptr(tok), ptr(pos), ptr(out), B * L, L, V, N,
+                                              _lib.current_stream_ptr()), "spion_embedding_forward")
+        ctx.save_for_backward(idc)
+        ctx.shapes = (tok.shape, tok.dtype, pos.shape, pos.dtype)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        (ids,) = ctx.saved_tensors
+        (V, N), td, pshape, pd = ctx.shapes
+        B, L = ids.shape
+        g = g.float()
+        dtok = _embedding_weight_grad(ids, g, V, N, td)
+        dpos = torch.zeros(pshape, dtype=torch.float32, device=g.device) if pshape[0] != L else None
+        rows = g.reshape(B, L, N).sum(0)
+        if dpos is None:
+            dpos = rows
+        else:
+            dpos[:L] = rows
+        return None, dtok, dpos.to(pd)
 
 
 class TokenEmbedding(nn.Embedding):
@@ -219,3 +256,15 @@ class TokenEmbedding(nn.Embedding):
         if not self.served(ids):
             return super().forward(ids)
         return _EmbeddingFn.apply(ids, self.weight)
+
+    def with_positions(self, ids, pos_weight):
+        """``self(ids) + pos_weight[:L][None]`` for ids [B, L]: one kernel when the table is served and both tables are
+        fp32 rows of the same width (a multiple of 4) on 16-byte boundaries, else the framework's operators."""
+        L = ids.shape[-1]
+        ok = (ids.dim() == 2 and self.served(ids) and pos_weight.dtype == torch.float32 and pos_weight.is_cuda
+              and pos_weight.shape[1] == self.weight.shape[1] and pos_weight.shape[0] >= L
+              and pos_weight.is_contiguous() and self.weight.is_contiguous()
+              and self.weight.data_ptr() % 16 == 0 and pos_weight.data_ptr() % 16 == 0)
+        if not ok:
+            return self(ids) + pos_weight[:L][None]
+        return _EmbedPosFn.apply(ids, self.weight, pos_weight)

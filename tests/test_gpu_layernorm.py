@@ -173,3 +173,26 @@ def test_add_norm_matches_separate_addition_and_normalisation(N, res_dtype):
                 scale = max(1.0, float(a.abs().max()))
                 tol = 1e-5 if (name != "dres" or res_dtype == torch.float32) else 8e-3
                 assert float((a - b).abs().max()) <= tol * scale, (name, use_sum)
+
+
+@pytest.mark.parametrize("B,L,Lmax", [(3, 512, 512), (2, 300, 1024)])
+def test_token_plus_position_embedding_in_one_kernel(B, L, Lmax):
+    """TokenEmbedding.with_positions against ``tok(ids) + pos.weight[:L][None]``: same bits forward, same gradients of
+    both tables (the position table may have more rows than the sequences use)."""
+    from spion_b200.layernorm import TokenEmbedding
+    V, N = 256, 64
+    g = torch.Generator().manual_seed(L)
+    ids = torch.randint(0, V, (B, L), generator=g).cuda()
+    dy = torch.randn(B, L, N, generator=g).cuda()
+    tok = TokenEmbedding(V, N).cuda()
+    pos = torch.nn.Embedding(Lmax, N).cuda()
+    outs = []
+    for fused in (False, True):
+        tok.weight.grad = None
+        pos.weight.grad = None
+        y = tok.with_positions(ids, pos.weight) if fused else torch.nn.functional.embedding(ids, tok.weight) + pos.weight[:L][None]
+        y.backward(dy)
+        outs.append((y.detach(), tok.weight.grad.clone(), pos.weight.grad.clone()))
+    assert torch.equal(outs[0][0], outs[1][0])
+    for a, b in zip(outs[0][1:], outs[1][1:]):
+        assert float((a - b).abs().max()) <= 1e-5 * max(1.0, float(a.abs().max()))
