@@ -293,6 +293,9 @@ def run_training(args, rank, world, local_rank):
     if use_graph:
         tr.capture_sparse_step(ids, y)
     run_step = (lambda a, b: tr.step_graph(a, b)) if use_graph else (lambda a, b: tr.step(a, b)[0])
+    sampler = ClockSampler(local_rank)
+    if rank == 0 and not args.no_clocks:
+        sampler.start()
     for _ in range(args.warmup):
         run_step(ids, y)
     barrier()
@@ -302,6 +305,12 @@ def run_training(args, rank, world, local_rank):
         run_step(ids, y)
     e1.record()
     barrier()
+    # keep rank 0 under the same load until nvidia-smi has produced a few samples (steps outside the timed region)
+    t_load = time.perf_counter()
+    while rank == 0 and world == 1 and sampler.proc and len(sampler.lines) < 4 and time.perf_counter() - t_load < 3.0:
+        run_step(ids, y)
+        torch.cuda.synchronize()
+    clocks = sampler.stop() if rank == 0 and not args.no_clocks else None
     ms_local = e0.elapsed_time(e1) / args.steps
     t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
     if world > 1:
@@ -359,7 +368,7 @@ def run_training(args, rank, world, local_rank):
                        "l2_policy": "activations of one step exceed L2"},
             "e2e": {"value": tokens / (e2e_ms * 1e-3) / 1e6, "unit": "Mtokens/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": int((2 if dual else 1) * per_rank * L * 8 + per_rank * 8), "d2h_bytes_per_step": 4},
-            "gpu_launches": launches, "loss": lv}))
+            "gpu_launches": launches, "loss": lv, "clocks": clocks}))
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
