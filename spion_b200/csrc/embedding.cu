@@ -10,7 +10,7 @@
 
 namespace {
 
-constexpr int EMB_THREADS = 512;                   // 16 warps
+constexpr int EMB_THREADS = 1024;                  // 32 warps
 constexpr int EMB_BATCH_BYTES = 32 * 1024;          // gradient rows of one staged batch (32 - 128 tokens)
 constexpr int EMB_STAGES = 3;                      // batches in flight or in use
 constexpr int EMB_MAX_TABLE_FLOATS = 24 * 1024;    // 96 KB of shared memory for the table
@@ -25,7 +25,7 @@ __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_gr
 // Shared memory: table [V][N] fp32, then EMB_STAGES stages of { gradient rows [batch][N], ids [batch] }.
 // The batch of a stage arrives by 16-byte asynchronous copies issued by all threads, EMB_STAGES - 1 batches ahead.
 // Warp w owns the 32 columns (w % (N/32)) * 32 ... of the table rows whose id % groups == w / (N/32), groups =
-// 16 / (N/32): a table element is only ever touched by one thread, in token order.  A warp reads the 32 ids of a
+// 32 / (N/32): a table element is only ever touched by one thread, in token order.  A warp reads the 32 ids of a
 // sub-batch at once, votes on the ones that are its own and walks those; a run of equal ids is summed in a register
 // before it goes to the table (padding tokens come in long runs).
 __host__ __device__ inline int emb_batch(int N, int esize) {   // tokens per staged batch: a multiple of 32
