@@ -184,6 +184,13 @@ class Trainer:
         self.mat_lst = None
         self.patterns = None
         self._graph = None
+        # bf16 copies of the linear layers' parameters, refreshed once per optimizer step (mixed precision only)
+        self._shadow = None
+        if config.get("native") and config.get("mixed_precision") and config.get("shadow_weights", True):
+            from .layernorm import BiasGradLinear, register_shadows
+            ps = [p for m in self.model.modules() if isinstance(m, BiasGradLinear) for p in (m.weight, m.bias)]
+            if ps:
+                self._shadow = (ps, register_shadows(ps))
         self.allreduce_events = None     # set to a list to collect (start, end) CUDA events around the gradient all-reduce
 
     def step(self, ids, label, is_attn=False):
@@ -200,7 +207,13 @@ class Trainer:
             self.bucket.allreduce_mean()
         torch.nn.utils.clip_grad_value_(self.model.parameters(), 1.0)   # main_conv_ff.py:186
         self.opt.step()
+        self._refresh_shadows()
         return loss.detach(), maps
+
+    def _refresh_shadows(self):
+        if self._shadow is not None:
+            from .layernorm import refresh_shadows
+            refresh_shadows(*self._shadow)
 
     def capture_sparse_step(self, ids, label, warmup: int = 3):
         """Record one sparse step as CUDA graphs: the step is a few hundred small launches, so replaying it
@@ -240,6 +253,7 @@ class Trainer:
         with torch.cuda.graph(self._graph_opt, capture_error_mode="thread_local"):
             torch.nn.utils.clip_grad_value_(self.model.parameters(), 1.0)
             self.opt.step()
+            self._refresh_shadows()
         return self._graph
 
     def step_graph(self, ids, label):

@@ -130,6 +130,36 @@ class FusedLayerNorm(nn.Module):
         return _AddLayerNormFn.apply(x.float(), res, self.weight, self.bias, self.eps, out_bf16)
 
 
+# Low-precision copies of linear-layer parameters, refreshed by their owner once per optimizer step with one
+# multi-tensor copy (a training loop that casts every weight and bias on every forward spends two small launches per
+# layer on it).  id(parameter) -> (weak reference to the parameter, copy).
+_SHADOWS: dict = {}
+
+
+def register_shadows(params, dtype=torch.bfloat16):
+    """Create ``dtype`` copies of ``params`` that BiasGradLinear uses instead of casting; returns the list of copies.
+    The caller keeps them current with ``refresh_shadows(params, copies)`` after every change of the parameters."""
+    import weakref
+    for k in [k for k, (r, _) in _SHADOWS.items() if r() is None]:
+        del _SHADOWS[k]
+    copies = [p.detach().to(dtype) for p in params]
+    for p, c in zip(params, copies):
+        _SHADOWS[id(p)] = (weakref.ref(p), c)
+    return copies
+
+
+def refresh_shadows(params, copies):
+    with torch.no_grad():
+        torch._foreach_copy_(copies, [p.detach() for p in params])
+
+
+def _shadow_or_cast(p, dtype):
+    e = _SHADOWS.get(id(p))
+    if e is not None and e[0]() is p and e[1].dtype == dtype:
+        return e[1]
+    return p.to(dtype)
+
+
 class _LinearFn(torch.autograd.Function):
     """y = x W^T + b with the framework's GEMMs; the bias gradient (a column sum over all rows, which the
     framework computes with a slow reduction for bf16 inputs) through spion_column_sums."""
@@ -137,7 +167,7 @@ class _LinearFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, bias):
         cd = torch.get_autocast_dtype("cuda") if torch.is_autocast_enabled() else x.dtype
-        xb, wb, bb = x.to(cd), weight.to(cd), bias.to(cd)
+        xb, wb, bb = x.to(cd), _shadow_or_cast(weight, cd), _shadow_or_cast(bias, cd)
         with torch.autocast(device_type="cuda", enabled=False):
             y = torch.nn.functional.linear(xb, wb, bb)
         ctx.save_for_backward(xb, wb)

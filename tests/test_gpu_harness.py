@@ -85,3 +85,12 @@ def test_residual_additions_inside_the_normalisation(dtype):
     assert torch.equal(m, mb)
     tol = 2e-5 if dtype == "fp32" else 3e-2
     np.testing.assert_allclose(a, b, rtol=tol, atol=tol)
+
+
+def test_bf16_parameter_copies_refreshed_once_per_step():
+    """The linear layers read bf16 copies of their parameters that the trainer refreshes after every optimizer step
+    (default of the native mixed-precision path); casting on every forward instead gives the same values."""
+    a, m = _run("text", native=True, dtype="bf16", L=256, batch=2, steps=3)
+    b, mb = _run("text", native=True, dtype="bf16", L=256, batch=2, steps=3, shadow_weights=False)
+    assert torch.equal(m, mb)
+    np.testing.assert_allclose(a, b, rtol=1e-6, atol=1e-6)
